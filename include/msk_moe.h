@@ -1,0 +1,158 @@
+/*
+ * msk_moe.h -- C ABI of the B200 (sm_100a) routed-expert step `muse_moe_w4a16`:
+ * top-k routing, stable token permutation, NVFP4-weight x BF16-activation grouped
+ * SwiGLU experts, deterministic top-k-weighted combine.
+ *
+ * This library is what the reference module's native binding would bind for this
+ * path. The reference boundary it replaces is the pybind trio
+ *     okc_run(w, scratch, x, ids, tw, out, lo, nloc, grid) / okc_set_pdl / okc_attrs
+ * (muse_moe_w4a16/py/00_moe_w4a16.py:208-214, launcher muse_moe_w4a16/cuda/moe.cu:2796-2881),
+ * restated with plain pointers and sizes: no torch types, no exceptions, no host
+ * synchronisation (except where a function says so), every launch on the stream given.
+ *
+ * Conventions
+ *  - every function returns an int status: 0 = ok, negative = rejected on the host
+ *    before any launch (MSK_ERR_*), positive = cudaError_t of a failed launch;
+ *  - all pointers are device pointers unless named host_*; `stream` is a cudaStream_t
+ *    passed as void*;
+ *  - device-side waits are bounded; a kernel that gives up writes a non-zero code to
+ *    word 0 of the workspace (see msk_moe_read_status) and exits, it never traps.
+ */
+#ifndef MSK_MOE_H_
+#define MSK_MOE_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MSK_OK 0
+#define MSK_ERR_NULL (-1)        /* a required pointer is NULL */
+#define MSK_ERR_SHAPE (-2)       /* unsupported shape (see MskMoeCfg) */
+#define MSK_ERR_ALIGN (-3)       /* pointer not 16-byte aligned */
+#define MSK_ERR_WORKSPACE (-4)   /* workspace too small */
+#define MSK_ERR_RANGE (-5)       /* local expert range outside [0, n_experts) */
+#define MSK_ERR_TOO_LARGE (-6)   /* size beyond a stated maximum */
+
+/* Routing score function (msk_moe_route). */
+#define MSK_ROUTE_SOFTMAX_TOPK 0 /* select by logit, weights = softmax over the k selected logits */
+#define MSK_ROUTE_SIGMOID_BIAS 1 /* s = sigmoid(logit * route_scale); select by s + bias; w = s / (sum s + 1e-15) */
+
+/* Shapes and options. Mirrors the reference's `Config` dict (d_hidden, d_expert,
+ * n_experts, local_start, local_count, top_k; muse_moe_w4a16/py/00_moe_w4a16.py:82-90),
+ * which the reference bakes into its CUDA source (moe.cu:144); here they are run-time.
+ * Constraints: hidden % 256 == 0, inter % 256 == 0, 1 <= top_k <= 16,
+ * 1 <= local_count <= 256, n_experts <= 512. */
+typedef struct MskMoeCfg {
+  int32_t hidden;        /* H: d_hidden */
+  int32_t inter;         /* I: d_expert */
+  int32_t n_experts;     /* E: experts over all ranks (range of topk_ids) */
+  int32_t local_start;   /* first expert owned by this rank */
+  int32_t local_count;   /* experts owned by this rank */
+  int32_t top_k;
+  int32_t routing_mode;  /* MSK_ROUTE_* */
+  float route_scale;     /* sigmoid mode: logit multiplier (reference: 1/sqrt(32)) */
+  float post_norm_eps;   /* eps of the post-expert RMS norm (reference: 1e-8) */
+  int32_t num_ctas;      /* persistent grid size; 0 = one CTA per SM of the current device */
+  int32_t split_k13;     /* K splits of the gate/up GEMM; 0 = chosen from n_tokens */
+  int32_t split_k2;      /* K splits of the down GEMM;    0 = chosen from n_tokens */
+  int32_t token_tile;    /* MMA N (tokens per tile): 16/32/64/128; 0 = chosen from n_tokens */
+  int32_t max_tokens;    /* token capacity the workspace is sized for (msk_moe_forward rejects more) */
+} MskMoeCfg;
+
+/* ---- prepare-time repack (lossless; replaces the four layouts built by
+ *      muse_moe_w4a16/py/01_build_pack.py:95-238 and py/02_prepare.py:24-57) ---- */
+
+/* Bytes of the two packed weight buffers for local_count experts. */
+int msk_moe_packed_bytes(const MskMoeCfg* cfg, size_t* host_w13_bytes, size_t* host_w2_bytes);
+
+/* w13: uint8 [local_count, 2I, H/2] (two E2M1 codes per byte, low nibble = even k; rows
+ * [gate 0..I-1; up I..2I-1]); w13_sf: E4M3 bytes [local_count, 2I, H/16];
+ * w2: uint8 [local_count, H, I/2]; w2_sf: [local_count, H, I/16].
+ * Output: tiles of 128 rows x 256 K, each 16 KiB of bit-permuted codes followed by
+ * 2 KiB of scale bytes, ordered [expert][row tile][gate|up][k stage] for w13 and
+ * [expert][row tile][k stage] for w2. Bit and byte permutation only. */
+int msk_moe_repack(const MskMoeCfg* cfg, const void* w13, const void* w13_sf, const void* w2, const void* w2_sf,
+                   void* packed13, void* packed2, void* stream);
+
+/* Exact inverse of msk_moe_repack (for the losslessness test and state export). */
+int msk_moe_unpack(const MskMoeCfg* cfg, const void* packed13, const void* packed2, void* w13, void* w13_sf,
+                   void* w2, void* w2_sf, void* stream);
+
+/* Dequantise packed tiles to BF16 matrices carrying e2m1*e4m3 (no global scale):
+ * dq13 [local_count, 2I, H], dq2 [local_count, H, I]. Runs the same device decode
+ * routine as the GEMM kernel; test hook for muse_moe_w4a16/cuda/moe.cu:293-310. */
+int msk_moe_dequant_packed(const MskMoeCfg* cfg, const void* packed13, const void* packed2, void* dq13, void* dq2,
+                           void* stream);
+
+/* ---- routing (caller side of the reference: muse_decode_layer/py/04_triton_kernels.py:525-556,
+ *      muse_prefill_layer/cuda/prefill.cu:1620-1705) ---- */
+
+/* logits[t, e] = sum_h float(x[t, h]) * router_w[e, h], FP32, fixed summation order
+ * (precedent: muse_decode_layer/cuda/router_fp32.cu:4-40). x: bf16 [T, H]; router_w: fp32 [E, H]. */
+int msk_moe_router_logits(const MskMoeCfg* cfg, const void* x, const float* router_w, float* logits, int n_tokens,
+                          void* stream);
+
+/* Top-k of fp32 logits [T, E]; ties go to the lowest expert index. bias may be NULL
+ * (softmax mode ignores it). Writes ids int32 [T, k] (global ids, descending score) and
+ * weights fp32 [T, k]. */
+int msk_moe_route(const MskMoeCfg* cfg, const float* logits, const float* bias, int32_t* topk_ids,
+                  float* topk_weights, int n_tokens, void* stream);
+
+/* Stable counting sort of the (token, slot) entries by local expert
+ * (muse_moe_w4a16/cuda/moe.cu:315-433). Entries whose id is outside
+ * [local_start, local_start + local_count) or negative are dropped.
+ *   cnt  int32 [local_count]       tokens per local expert
+ *   off  int32 [local_count + 1]   exclusive prefix of cnt; off[local_count] = routed entries
+ *   perm int32 [T * k]             perm[q] = entry index t*k+slot, ordered by (expert, entry)
+ *   inv  int32 [T * k]             inv[entry] = q, or -1 when the entry is not local */
+int msk_moe_sort(const MskMoeCfg* cfg, const int32_t* topk_ids, int n_tokens, int32_t* cnt, int32_t* off,
+                 int32_t* perm, int32_t* inv, void* stream);
+
+/* ---- the routed-expert step (replaces okc_run, muse_moe_w4a16/cuda/moe.cu:2796-2881) ---- */
+
+/* Scratch needed by msk_moe_forward for up to cfg->max_tokens tokens. The carving depends
+ * on cfg->max_tokens only, so every call must pass the cfg the workspace was sized with. */
+int msk_moe_workspace_bytes(const MskMoeCfg* cfg, size_t* host_bytes);
+
+/* Zero the control words of a fresh workspace (status, split-K tickets). Once, after allocation. */
+int msk_moe_workspace_init(const MskMoeCfg* cfg, void* workspace, size_t workspace_bytes, void* stream);
+
+/* out[t, :] = bf16( sum_{slot, local} w[t,slot] * post(y[t,slot]) ),
+ *   y = (bf16(silu(x W13g^T gs13) * (x W13u^T gs13))) W2^T gs2,
+ *   post(y) = y                                  when post_norm_w == NULL
+ *           = y(1+w) * rsqrt(mean((y(1+w))^2)+eps)  otherwise
+ * (muse_moe_w4a16/cuda/moe.cu:440-478, 2604-2766). x: bf16 [T, H]; topk_ids int32 [T, k]
+ * (global ids); topk_weights fp32 [T, k]; gs13/gs2 fp32 [local_count]; post_norm_w bf16 [H]
+ * or NULL; out bf16 [T, H], fully overwritten (zeros for tokens without a local route).
+ * Launches: sort, gate/up GEMM, down GEMM, combine. No host sync; capturable in a CUDA graph. */
+int msk_moe_forward(const MskMoeCfg* cfg, const void* packed13, const void* packed2, const float* gs13,
+                    const float* gs2, const void* post_norm_w, const void* x, const int32_t* topk_ids,
+                    const float* topk_weights, void* out, void* workspace, size_t workspace_bytes, int n_tokens,
+                    void* stream);
+
+/* Views into the workspace after msk_moe_forward (device pointers, for parity tests):
+ * which: 0 cnt, 1 off, 2 perm, 3 inv, 4 inter (bf16 [R, I]), 5 y (fp32 [R, H]). */
+int msk_moe_workspace_view(const MskMoeCfg* cfg, void* workspace, int which, void** host_ptr);
+
+/* Copies workspace word 0 to *host_status after synchronising `stream`. 0 = no device-side
+ * wait gave up. Not for the timed path. */
+int msk_moe_read_status(const void* workspace, int* host_status, void* stream);
+
+/* Registers / static + dynamic shared memory / local memory per kernel, as the reference's
+ * okc_attrs() reports (muse_moe_w4a16/cuda/moe.cu:2789-2794). which: 0 sort, 1 route,
+ * 2 gate/up GEMM, 3 down GEMM, 4 combine. host_out: int[4] = regs, static smem, max dyn smem, local. */
+int msk_moe_attrs(int which, int token_tile, int* host_out);
+
+/* HBM streaming probe: every CTA pulls its share of `bytes` from `src` through a ring of
+ * bulk async copies, as the GEMM kernel's weight producer does, and adds a checksum to
+ * sink[0] (twin of muse_moe_w4a16/cuda/moe_bw.cu). */
+int msk_bw_probe(const void* src, size_t bytes, int stages, int stage_bytes, int num_ctas, uint32_t* sink,
+                 void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MSK_MOE_H_ */

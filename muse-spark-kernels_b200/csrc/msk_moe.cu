@@ -1,0 +1,656 @@
+// C ABI of the routed-expert step (declarations and contracts: include/msk_moe.h).
+// Host side: argument validation, workspace carving, plan choice and launches; no torch
+// headers, no allocation, no synchronisation except msk_moe_read_status.
+#include <algorithm>
+#include <cmath>
+#include <cstdint>
+#include <cstring>
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include "../../include/msk_moe.h"
+#include "route_sort.cuh"
+#include "gemm.cuh"
+
+namespace msk {
+
+// ------------------------------------------------------------ repack kernels
+// Tile order inside a packed buffer: ((expert * tiles_per_expert) + row_tile') * n_stages + ks,
+// where for w13 row_tile' = 2*j + (0 gate | 1 up) and the source rows are gu*I + j*128 + r;
+// for w2 row_tile' = row tile and the source rows are row_tile*128 + r.
+struct RepackGeom {
+  int rows_total;       // source rows per expert (2I or H)
+  int K;                // source K
+  int tiles_per_expert; // rows_total / 128
+  int n_stages;         // K / 256
+  int interleave_I;     // I for w13 (gate/up interleave), 0 for w2
+};
+
+__device__ __forceinline__ int source_row(const RepackGeom& g, int tile_in_expert, int r) {
+  if (g.interleave_I > 0) {
+    const int j = tile_in_expert >> 1, gu = tile_in_expert & 1;
+    return gu * g.interleave_I + j * 128 + r;
+  }
+  return tile_in_expert * 128 + r;
+}
+
+// One thread per 16 output bytes (a code chunk or a row's scale bytes).
+template <bool INVERSE>
+__global__ void __launch_bounds__(256) repack_kernel(uint8_t* codes, uint8_t* sf, uint8_t* packed, RepackGeom g,
+                                                     long long n_tiles) {
+  const long long gid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const long long per_tile = 128 * 9;  // 8 code chunks + 1 scale chunk per row
+  if (gid >= n_tiles * per_tile) return;
+  const long long tile = gid / per_tile;
+  const int rem = static_cast<int>(gid % per_tile);
+  const int part = rem / 128, r = rem % 128;  // part 0..7 = code chunk, 8 = scales
+  const int ks = static_cast<int>(tile % g.n_stages);
+  const long long t2 = tile / g.n_stages;
+  const int tile_in_expert = static_cast<int>(t2 % g.tiles_per_expert);
+  const long long e = t2 / g.tiles_per_expert;
+  const long long srow = e * g.rows_total + source_row(g, tile_in_expert, r);
+  uint8_t* ptile = packed + tile * TILE_BYTES;
+  if (part < 8) {
+    uint4* src = reinterpret_cast<uint4*>(codes + srow * (g.K / 2) + ks * (KS / 2) + part * 16);
+    uint4* dst = reinterpret_cast<uint4*>(ptile + (part * 128 + r) * 16);
+    if (!INVERSE) {
+      const uint4 v = *src;
+      *dst = make_uint4(pack_word(v.x), pack_word(v.y), pack_word(v.z), pack_word(v.w));
+    } else {
+      const uint4 v = *dst;
+      *src = make_uint4(unpack_word(v.x), unpack_word(v.y), unpack_word(v.z), unpack_word(v.w));
+    }
+  } else {
+    uint4* src = reinterpret_cast<uint4*>(sf + srow * (g.K / 16) + ks * (KS / 16));
+    uint4* dst = reinterpret_cast<uint4*>(ptile + TILE_CODE_BYTES + r * 16);
+    if (!INVERSE) *dst = *src; else *src = *dst;
+  }
+}
+
+// Packed tiles -> BF16 e2m1*e4m3 matrices, through the decode routine of the GEMM kernel
+// (values carry the 2^-62 factor in registers; multiplied back by 2^62 here, exact).
+__global__ void __launch_bounds__(128) dequant_packed_kernel(const uint8_t* packed, __nv_bfloat16* out, RepackGeom g,
+                                                             long long n_tiles) {
+  __shared__ uint32_t lut[256];
+  for (int i = threadIdx.x; i < 256; i += 128) lut[i] = e4m3_scale_bf16x2(static_cast<uint32_t>(i));
+  __syncthreads();
+  const long long tile = blockIdx.x;
+  if (tile >= n_tiles) return;
+  const int r = threadIdx.x;
+  const int ks = static_cast<int>(tile % g.n_stages);
+  const long long t2 = tile / g.n_stages;
+  const int tile_in_expert = static_cast<int>(t2 % g.tiles_per_expert);
+  const long long e = t2 / g.tiles_per_expert;
+  const long long srow = e * g.rows_total + source_row(g, tile_in_expert, r);
+  const uint8_t* ptile = packed + tile * TILE_BYTES;
+  const uint4 sfw = *reinterpret_cast<const uint4*>(ptile + TILE_CODE_BYTES + r * 16);
+  const uint32_t sfa[4] = {sfw.x, sfw.y, sfw.z, sfw.w};
+  __nv_bfloat16* orow = out + srow * g.K + ks * KS;
+  const uint32_t two62 = 0x5E805E80u;  // bf16x2 of 2^62
+  for (int chunk = 0; chunk < 8; ++chunk) {
+    const uint4 q = *reinterpret_cast<const uint4*>(ptile + (chunk * 128 + r) * 16);
+    const uint32_t qa[4] = {q.x, q.y, q.z, q.w};
+    const uint32_t sw = sfa[chunk >> 1] >> ((chunk & 1) * 16);
+    for (int i = 0; i < 4; ++i) {
+      const uint32_t s = lut[(i < 2 ? sw : (sw >> 8)) & 0xFFu];
+      uint32_t rr[4];
+      decode_codes(qa[i], rr[0], rr[1], rr[2], rr[3]);
+      for (int j = 0; j < 4; ++j) {
+        const uint32_t v = hmul2_bf16(hmul2_bf16(rr[j], s), two62);
+        *reinterpret_cast<uint32_t*>(orow + chunk * 32 + i * 8 + j * 2) = v;
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------- combine
+// One block per token: out[t] = bf16( sum over slots in index order of
+// w[t,s] * norm_s * y[inv[t,s]] ), norm_s = rsqrt(mean(y^2) + eps) when the post-expert
+// norm is on (y already carries 1 + post_norm_w), else 1
+// (muse_moe_w4a16/cuda/moe.cu:2604-2766; muse_decode_layer/py/04_triton_kernels.py:616-632).
+// The block sum of squares is a fixed shuffle tree followed by a fixed-order sum of the
+// eight warp partials, so the result does not depend on scheduling.
+constexpr int COMBINE_THREADS = 256;
+constexpr int COMBINE_MAX_PER_THREAD = 32;  // H <= 8192
+
+__global__ void __launch_bounds__(COMBINE_THREADS) combine_kernel(const float* __restrict__ y,
+                                                                  const int32_t* __restrict__ inv,
+                                                                  const float* __restrict__ tw,
+                                                                  __nv_bfloat16* __restrict__ out, int H, int k,
+                                                                  int post_norm, float eps) {
+  __shared__ float wsum[COMBINE_THREADS / 32];
+  const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int n4 = H / 4;  // float4 per row; thread tid owns indices i*256 + tid
+  float4 acc[COMBINE_MAX_PER_THREAD / 4];
+#pragma unroll
+  for (int i = 0; i < COMBINE_MAX_PER_THREAD / 4; ++i) acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int s = 0; s < k; ++s) {
+    const int q = inv[static_cast<size_t>(t) * k + s];
+    if (q < 0) continue;  // uniform over the block
+    const float4* row = reinterpret_cast<const float4*>(y + static_cast<size_t>(q) * H);
+    float4 v[COMBINE_MAX_PER_THREAD / 4];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < COMBINE_MAX_PER_THREAD / 4; ++i) {
+      if (i * COMBINE_THREADS + tid < n4) {
+        v[i] = row[i * COMBINE_THREADS + tid];
+        ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
+      }
+    }
+    float scale = tw[static_cast<size_t>(t) * k + s];
+    if (post_norm) {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      __syncthreads();  // wsum of the previous slot fully read
+      if (lane == 0) wsum[warp] = ss;
+      __syncthreads();
+      float tot = 0.f;
+#pragma unroll
+      for (int w = 0; w < COMBINE_THREADS / 32; ++w) tot += wsum[w];
+      scale *= rsqrtf(tot / static_cast<float>(H) + eps);
+    }
+#pragma unroll
+    for (int i = 0; i < COMBINE_MAX_PER_THREAD / 4; ++i) {
+      if (i * COMBINE_THREADS + tid < n4) {
+        acc[i].x += v[i].x * scale; acc[i].y += v[i].y * scale;
+        acc[i].z += v[i].z * scale; acc[i].w += v[i].w * scale;
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < COMBINE_MAX_PER_THREAD / 4; ++i) {
+    if (i * COMBINE_THREADS + tid < n4) {
+      __nv_bfloat162 lo = __floats2bfloat162_rn(acc[i].x, acc[i].y);
+      __nv_bfloat162 hi = __floats2bfloat162_rn(acc[i].z, acc[i].w);
+      uint2 pk;
+      pk.x = *reinterpret_cast<uint32_t*>(&lo);
+      pk.y = *reinterpret_cast<uint32_t*>(&hi);
+      *reinterpret_cast<uint2*>(out + static_cast<size_t>(t) * H + (i * COMBINE_THREADS + tid) * 4) = pk;
+    }
+  }
+}
+
+// --------------------------------------------------------------- bw probe
+// Every CTA streams its contiguous share of the buffer through a ring of bulk async
+// copies, one elected thread issuing, one warp consuming (twin of the reference's
+// muse_moe_w4a16/cuda/moe_bw.cu tma_kernel).
+__global__ void __launch_bounds__(64) bw_probe_kernel(const uint8_t* src, unsigned long long bytes, int stages,
+                                                      int stage_bytes, uint32_t* sink) {
+  extern __shared__ __align__(1024) uint8_t psm[];
+  __shared__ uint64_t full[8], empty[8];
+  __shared__ int abort_word;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < stages; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 1); }
+    abort_word = 0;
+    fence_mbar_init();
+  }
+  __syncthreads();
+  const unsigned long long n_chunks = bytes / stage_bytes;
+  const unsigned long long per = (n_chunks + gridDim.x - 1) / gridDim.x;
+  const unsigned long long c0 = per * blockIdx.x, c1 = min(n_chunks, c0 + per);
+  if (warp == 0) {
+    if (lane == 0) {
+      const uint64_t pol = policy_evict_first();
+      uint32_t it = 0;
+      for (unsigned long long c = c0; c < c1; ++c, ++it) {
+        const uint32_t slot = it % stages, par = (it / stages) & 1u;
+        if (!mbar_wait(&empty[slot], par ^ 1u, &abort_word)) break;
+        mbar_arrive_expect_tx(&full[slot], stage_bytes);
+        bulk_g2s(psm + static_cast<size_t>(slot) * stage_bytes, src + c * stage_bytes, stage_bytes, &full[slot], pol);
+      }
+    }
+  } else {
+    uint32_t it = 0, sum = 0;
+    for (unsigned long long c = c0; c < c1; ++c, ++it) {
+      const uint32_t slot = it % stages, par = (it / stages) & 1u;
+      if (!mbar_wait(&full[slot], par, &abort_word)) break;
+      sum += *reinterpret_cast<const uint32_t*>(psm + static_cast<size_t>(slot) * stage_bytes + lane * 16);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty[slot]);
+    }
+    if (sum == 0x9E3779B9u) atomicAdd(sink, sum);  // keeps the reads alive
+  }
+  __syncthreads();
+  if (abort_word != 0) {
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
+    if (threadIdx.x == 0) atomicExch(reinterpret_cast<int*>(sink) + 1, MSK_DEV_ERR_TIMEOUT);
+  }
+}
+
+// ------------------------------------------------------------ host helpers
+static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+static inline size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+static int check_cfg(const MskMoeCfg* c) {
+  if (c == nullptr) return MSK_ERR_NULL;
+  if (c->hidden <= 0 || c->inter <= 0 || c->hidden % 256 != 0 || c->inter % 256 != 0) return MSK_ERR_SHAPE;
+  if (c->hidden > COMBINE_THREADS * COMBINE_MAX_PER_THREAD) return MSK_ERR_SHAPE;  // combine keeps a row in registers
+  if (c->max_tokens < 0) return MSK_ERR_SHAPE;
+  if (c->top_k < 1 || c->top_k > MAX_TOP_K) return MSK_ERR_SHAPE;
+  if (c->local_count < 1 || c->local_count > MAX_LOCAL_EXPERTS) return MSK_ERR_SHAPE;
+  if (c->n_experts < 1 || c->n_experts > MAX_EXPERTS) return MSK_ERR_SHAPE;
+  if (c->local_start < 0 || c->local_start + c->local_count > c->n_experts) return MSK_ERR_RANGE;
+  return MSK_OK;
+}
+
+static int sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+struct Plan {
+  int N;         // token tile
+  int s13, s2;   // K splits
+  int grid;
+};
+
+// Expected number of token tiles for T tokens spread uniformly over the local experts.
+static double expected_tiles(const MskMoeCfg* c, int T, int N) {
+  const double routes = static_cast<double>(T) * c->top_k * c->local_count / c->n_experts;
+  const double active = c->local_count * (1.0 - std::pow(1.0 - 1.0 / c->local_count, routes));
+  return std::max(active, routes / N);
+}
+
+static int pick_split(double units, int n_stages, int grid) {
+  int best = 1;
+  double best_cost = 1e30;
+  for (int s = 1; s <= std::min(n_stages, 8); ++s) {
+    const double waves = std::ceil(units * s / grid);
+    const double cost = waves * (std::ceil(static_cast<double>(n_stages) / s) + 0.35) + (s > 1 ? 0.5 : 0.0);
+    if (cost < best_cost - 1e-9) { best_cost = cost; best = s; }
+  }
+  return best;
+}
+
+static Plan make_plan(const MskMoeCfg* c, int T) {
+  Plan p;
+  p.grid = c->num_ctas > 0 ? c->num_ctas : sm_count();
+  if (c->token_tile > 0) {
+    p.N = c->token_tile;
+  } else {
+    const double rpe = static_cast<double>(T) * c->top_k / c->n_experts;  // mean tokens per expert
+    p.N = rpe <= 8 ? 16 : rpe <= 16 ? 32 : rpe <= 32 ? 64 : 128;
+  }
+  const double tiles = expected_tiles(c, T, p.N);
+  p.s13 = c->split_k13 > 0 ? c->split_k13 : pick_split(tiles * (c->inter / 128), c->hidden / KS, p.grid);
+  p.s2 = c->split_k2 > 0 ? c->split_k2 : pick_split(tiles * (c->hidden / 256), c->inter / KS, p.grid);
+  p.s13 = std::min(p.s13, c->hidden / KS);
+  p.s2 = std::min(p.s2, c->inter / KS);
+  return p;
+}
+
+// Workspace carving. Everything is sized for max_tokens with the worst plan.
+struct Carve {
+  size_t status, cnt, off, perm, inv, tickets, inter, y, partial, total;
+};
+constexpr size_t MAX_SPLIT = 8;
+
+static size_t max_tiles(const MskMoeCfg* c, int T) {
+  // ceil(cnt/16) summed over experts <= R/16 + local_count
+  const size_t R = static_cast<size_t>(T) * c->top_k;
+  return R / 16 + c->local_count;
+}
+
+static size_t partial_floats(const MskMoeCfg* c, int T) {
+  // split-K is only planned while it pays: bounded by the units of a 4-wave launch; beyond
+  // that make_plan picks 1. Size for the largest product (base units * splits * 2 * 128 * N)
+  // any plan can ask for.
+  size_t worst = 0;
+  const int Ns[4] = {16, 32, 64, 128};
+  for (int N : Ns) {
+    const size_t tiles = static_cast<size_t>(T) * c->top_k / N + c->local_count;
+    const size_t pairs = std::max(c->inter / 128, c->hidden / 256);
+    worst = std::max(worst, tiles * pairs * MAX_SPLIT * 2 * 128 * static_cast<size_t>(N));
+  }
+  // cap: a launch with that many units never splits (pick_split sees many waves)
+  const size_t cap = static_cast<size_t>(64) << 20;  // 64 Mi floats = 256 MiB
+  return std::min(worst, cap);
+}
+
+static Carve carve(const MskMoeCfg* c, int T) {
+  Carve k;
+  const size_t R = static_cast<size_t>(T) * c->top_k;
+  size_t o = 0;
+  k.status = o; o += 256;
+  k.cnt = o; o += round_up(static_cast<size_t>(c->local_count) * 4, 256);
+  k.off = o; o += round_up(static_cast<size_t>(c->local_count + 1) * 4, 256);
+  k.perm = o; o += round_up(R * 4, 256);
+  k.inv = o; o += round_up(R * 4, 256);
+  const size_t pairs = std::max(c->inter / 128, c->hidden / 256);
+  k.tickets = o; o += round_up(max_tiles(c, T) * pairs * 4, 256);
+  k.inter = o; o += round_up(R * c->inter * 2, 256);
+  k.y = o; o += round_up(R * c->hidden * 4, 256);
+  k.partial = o; o += round_up(partial_floats(c, T) * 4, 256);
+  k.total = o;
+  return k;
+}
+
+template <int N, int PHASE>
+static int launch_gemm(const GemmParams& p, int grid, cudaStream_t st) {
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(moe_gemm_kernel<N, PHASE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         GemmCfg<N>::SMEM_BYTES);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    attr_set[dev] = true;
+  }
+  moe_gemm_kernel<N, PHASE><<<grid, GEMM_THREADS, GemmCfg<N>::SMEM_BYTES, st>>>(p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+template <int PHASE>
+static int launch_gemm_n(int N, const GemmParams& p, int grid, cudaStream_t st) {
+  switch (N) {
+    case 16: return launch_gemm<16, PHASE>(p, grid, st);
+    case 32: return launch_gemm<32, PHASE>(p, grid, st);
+    case 64: return launch_gemm<64, PHASE>(p, grid, st);
+    case 128: return launch_gemm<128, PHASE>(p, grid, st);
+    default: return MSK_ERR_SHAPE;
+  }
+}
+
+static RepackGeom geom13(const MskMoeCfg* c) {
+  return RepackGeom{2 * c->inter, c->hidden, 2 * c->inter / 128, c->hidden / KS, c->inter};
+}
+static RepackGeom geom2(const MskMoeCfg* c) {
+  return RepackGeom{c->hidden, c->inter, c->hidden / 128, c->inter / KS, 0};
+}
+static long long n_tiles_of(const MskMoeCfg* c, const RepackGeom& g) {
+  return static_cast<long long>(c->local_count) * g.tiles_per_expert * g.n_stages;
+}
+
+}  // namespace msk
+
+using namespace msk;
+
+extern "C" {
+
+int msk_moe_packed_bytes(const MskMoeCfg* cfg, size_t* host_w13_bytes, size_t* host_w2_bytes) {
+  const int rc = check_cfg(cfg);
+  if (rc != MSK_OK) return rc;
+  if (host_w13_bytes == nullptr || host_w2_bytes == nullptr) return MSK_ERR_NULL;
+  *host_w13_bytes = static_cast<size_t>(n_tiles_of(cfg, geom13(cfg))) * TILE_BYTES;
+  *host_w2_bytes = static_cast<size_t>(n_tiles_of(cfg, geom2(cfg))) * TILE_BYTES;
+  return MSK_OK;
+}
+
+static int repack_common(const MskMoeCfg* cfg, void* w13, void* w13_sf, void* w2, void* w2_sf, void* packed13,
+                         void* packed2, void* stream, bool inverse) {
+  const int rc = check_cfg(cfg);
+  if (rc != MSK_OK) return rc;
+  if (!w13 || !w13_sf || !w2 || !w2_sf || !packed13 || !packed2) return MSK_ERR_NULL;
+  if (!aligned16(w13) || !aligned16(w13_sf) || !aligned16(w2) || !aligned16(w2_sf) || !aligned16(packed13) ||
+      !aligned16(packed2))
+    return MSK_ERR_ALIGN;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const RepackGeom g13 = geom13(cfg), g2 = geom2(cfg);
+  const long long n13 = n_tiles_of(cfg, g13), n2 = n_tiles_of(cfg, g2);
+  const long long th13 = n13 * 128 * 9, th2 = n2 * 128 * 9;
+  const unsigned b13 = static_cast<unsigned>((th13 + 255) / 256), b2 = static_cast<unsigned>((th2 + 255) / 256);
+  if (!inverse) {
+    repack_kernel<false><<<b13, 256, 0, st>>>(static_cast<uint8_t*>(w13), static_cast<uint8_t*>(w13_sf),
+                                              static_cast<uint8_t*>(packed13), g13, n13);
+    repack_kernel<false><<<b2, 256, 0, st>>>(static_cast<uint8_t*>(w2), static_cast<uint8_t*>(w2_sf),
+                                             static_cast<uint8_t*>(packed2), g2, n2);
+  } else {
+    repack_kernel<true><<<b13, 256, 0, st>>>(static_cast<uint8_t*>(w13), static_cast<uint8_t*>(w13_sf),
+                                             static_cast<uint8_t*>(packed13), g13, n13);
+    repack_kernel<true><<<b2, 256, 0, st>>>(static_cast<uint8_t*>(w2), static_cast<uint8_t*>(w2_sf),
+                                            static_cast<uint8_t*>(packed2), g2, n2);
+  }
+  return static_cast<int>(cudaGetLastError());
+}
+
+int msk_moe_repack(const MskMoeCfg* cfg, const void* w13, const void* w13_sf, const void* w2, const void* w2_sf,
+                   void* packed13, void* packed2, void* stream) {
+  return repack_common(cfg, const_cast<void*>(w13), const_cast<void*>(w13_sf), const_cast<void*>(w2),
+                       const_cast<void*>(w2_sf), packed13, packed2, stream, false);
+}
+
+int msk_moe_unpack(const MskMoeCfg* cfg, const void* packed13, const void* packed2, void* w13, void* w13_sf,
+                   void* w2, void* w2_sf, void* stream) {
+  return repack_common(cfg, w13, w13_sf, w2, w2_sf, const_cast<void*>(packed13), const_cast<void*>(packed2), stream,
+                       true);
+}
+
+int msk_moe_dequant_packed(const MskMoeCfg* cfg, const void* packed13, const void* packed2, void* dq13, void* dq2,
+                           void* stream) {
+  const int rc = check_cfg(cfg);
+  if (rc != MSK_OK) return rc;
+  if (!packed13 || !packed2 || !dq13 || !dq2) return MSK_ERR_NULL;
+  if (!aligned16(packed13) || !aligned16(packed2) || !aligned16(dq13) || !aligned16(dq2)) return MSK_ERR_ALIGN;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const RepackGeom g13 = geom13(cfg), g2 = geom2(cfg);
+  const long long n13 = n_tiles_of(cfg, g13), n2 = n_tiles_of(cfg, g2);
+  dequant_packed_kernel<<<static_cast<unsigned>(n13), 128, 0, st>>>(static_cast<const uint8_t*>(packed13),
+                                                                    static_cast<__nv_bfloat16*>(dq13), g13, n13);
+  dequant_packed_kernel<<<static_cast<unsigned>(n2), 128, 0, st>>>(static_cast<const uint8_t*>(packed2),
+                                                                   static_cast<__nv_bfloat16*>(dq2), g2, n2);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int msk_moe_router_logits(const MskMoeCfg* cfg, const void* x, const float* router_w, float* logits, int n_tokens,
+                          void* stream) {
+  const int rc = check_cfg(cfg);
+  if (rc != MSK_OK) return rc;
+  if (!x || !router_w || !logits) return MSK_ERR_NULL;
+  if (n_tokens < 0) return MSK_ERR_SHAPE;
+  if (n_tokens == 0) return MSK_OK;
+  dim3 grid(static_cast<unsigned>(n_tokens), static_cast<unsigned>((cfg->n_experts + 7) / 8));
+  router_logits_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), router_w, logits, cfg->hidden, cfg->n_experts);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int msk_moe_route(const MskMoeCfg* cfg, const float* logits, const float* bias, int32_t* topk_ids,
+                  float* topk_weights, int n_tokens, void* stream) {
+  const int rc = check_cfg(cfg);
+  if (rc != MSK_OK) return rc;
+  if (!logits || !topk_ids || !topk_weights) return MSK_ERR_NULL;
+  if (n_tokens < 0 || cfg->top_k > cfg->n_experts) return MSK_ERR_SHAPE;
+  if (n_tokens == 0) return MSK_OK;
+  route_topk_kernel<<<static_cast<unsigned>((n_tokens + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      logits, bias, topk_ids, topk_weights, n_tokens, cfg->n_experts, cfg->top_k, cfg->routing_mode,
+      cfg->route_scale);
+  return static_cast<int>(cudaGetLastError());
+}
+
+static int launch_sort(const MskMoeCfg* cfg, const int32_t* ids, int n_tokens, int32_t* cnt, int32_t* off,
+                       int32_t* perm, int32_t* inv, cudaStream_t st) {
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(sort_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(sizeof(SortSmem)));
+    if (e != cudaSuccess) return static_cast<int>(e);
+    attr_set[dev] = true;
+  }
+  sort_kernel<<<1, SORT_THREADS, sizeof(SortSmem), st>>>(ids, n_tokens * cfg->top_k, cfg->local_start,
+                                                         cfg->local_count, cnt, off, perm, inv);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int msk_moe_sort(const MskMoeCfg* cfg, const int32_t* topk_ids, int n_tokens, int32_t* cnt, int32_t* off,
+                 int32_t* perm, int32_t* inv, void* stream) {
+  const int rc = check_cfg(cfg);
+  if (rc != MSK_OK) return rc;
+  if (!cnt || !off || !perm || !inv) return MSK_ERR_NULL;
+  if (n_tokens < 0) return MSK_ERR_SHAPE;
+  if (n_tokens > 0 && !topk_ids) return MSK_ERR_NULL;
+  return launch_sort(cfg, topk_ids, n_tokens, cnt, off, perm, inv, static_cast<cudaStream_t>(stream));
+}
+
+int msk_moe_workspace_bytes(const MskMoeCfg* cfg, size_t* host_bytes) {
+  const int rc = check_cfg(cfg);
+  if (rc != MSK_OK) return rc;
+  if (!host_bytes) return MSK_ERR_NULL;
+  if (cfg->max_tokens < 1) return MSK_ERR_SHAPE;
+  *host_bytes = carve(cfg, cfg->max_tokens).total;
+  return MSK_OK;
+}
+
+int msk_moe_workspace_init(const MskMoeCfg* cfg, void* workspace, size_t workspace_bytes, void* stream) {
+  const int rc = check_cfg(cfg);
+  if (rc != MSK_OK) return rc;
+  if (!workspace) return MSK_ERR_NULL;
+  if (cfg->max_tokens < 1) return MSK_ERR_SHAPE;
+  const Carve k = carve(cfg, cfg->max_tokens);
+  if (k.total > workspace_bytes) return MSK_ERR_WORKSPACE;
+  // status word, tables and split-K tickets all sit below `inter`
+  return static_cast<int>(cudaMemsetAsync(workspace, 0, k.inter, static_cast<cudaStream_t>(stream)));
+}
+
+int msk_moe_workspace_view(const MskMoeCfg* cfg, void* workspace, int which, void** host_ptr) {
+  const int rc = check_cfg(cfg);
+  if (rc != MSK_OK) return rc;
+  if (!workspace || !host_ptr) return MSK_ERR_NULL;
+  if (cfg->max_tokens < 1) return MSK_ERR_SHAPE;
+  const Carve k = carve(cfg, cfg->max_tokens);
+  uint8_t* b = static_cast<uint8_t*>(workspace);
+  switch (which) {
+    case 0: *host_ptr = b + k.cnt; break;
+    case 1: *host_ptr = b + k.off; break;
+    case 2: *host_ptr = b + k.perm; break;
+    case 3: *host_ptr = b + k.inv; break;
+    case 4: *host_ptr = b + k.inter; break;
+    case 5: *host_ptr = b + k.y; break;
+    default: return MSK_ERR_SHAPE;
+  }
+  return MSK_OK;
+}
+
+int msk_moe_forward(const MskMoeCfg* cfg, const void* packed13, const void* packed2, const float* gs13,
+                    const float* gs2, const void* post_norm_w, const void* x, const int32_t* topk_ids,
+                    const float* topk_weights, void* out, void* workspace, size_t workspace_bytes, int n_tokens,
+                    void* stream) {
+  const int rc = check_cfg(cfg);
+  if (rc != MSK_OK) return rc;
+  if (!packed13 || !packed2 || !gs13 || !gs2 || !workspace) return MSK_ERR_NULL;
+  if (n_tokens < 0) return MSK_ERR_SHAPE;
+  if (n_tokens == 0) return MSK_OK;
+  if (!x || !topk_ids || !topk_weights || !out) return MSK_ERR_NULL;
+  if (!aligned16(packed13) || !aligned16(packed2) || !aligned16(x) || !aligned16(out) || !aligned16(workspace))
+    return MSK_ERR_ALIGN;
+  if (n_tokens > cfg->max_tokens) return MSK_ERR_TOO_LARGE;
+  // offsets depend on the capacity only, so control words keep their place from call to call
+  const Carve k = carve(cfg, cfg->max_tokens);
+  if (k.total > workspace_bytes) return MSK_ERR_WORKSPACE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  uint8_t* b = static_cast<uint8_t*>(workspace);
+  int32_t* status = reinterpret_cast<int32_t*>(b + k.status);
+  int32_t* cnt = reinterpret_cast<int32_t*>(b + k.cnt);
+  int32_t* off = reinterpret_cast<int32_t*>(b + k.off);
+  int32_t* perm = reinterpret_cast<int32_t*>(b + k.perm);
+  int32_t* inv = reinterpret_cast<int32_t*>(b + k.inv);
+  int32_t* tickets = reinterpret_cast<int32_t*>(b + k.tickets);
+  __nv_bfloat16* inter = reinterpret_cast<__nv_bfloat16*>(b + k.inter);
+  float* y = reinterpret_cast<float*>(b + k.y);
+  float* partial = reinterpret_cast<float*>(b + k.partial);
+
+  Plan plan = make_plan(cfg, n_tokens);
+  if (plan.N != 16 && plan.N != 32 && plan.N != 64 && plan.N != 128) return MSK_ERR_SHAPE;
+  if (plan.s13 < 1 || plan.s2 < 1 || plan.s13 > static_cast<int>(MAX_SPLIT) || plan.s2 > static_cast<int>(MAX_SPLIT))
+    return MSK_ERR_SHAPE;
+  // the partial buffer bounds what a split plan may use; fall back to one split beyond it
+  {
+    const size_t tiles = max_tiles(cfg, n_tokens);
+    const size_t need13 = tiles * (cfg->inter / 128) * plan.s13 * 2 * 128 * static_cast<size_t>(plan.N);
+    const size_t need2 = tiles * (cfg->hidden / 256) * plan.s2 * 2 * 128 * static_cast<size_t>(plan.N);
+    const size_t have = partial_floats(cfg, n_tokens);
+    if (plan.s13 > 1 && need13 > have) plan.s13 = 1;
+    if (plan.s2 > 1 && need2 > have) plan.s2 = 1;
+  }
+
+  int e = launch_sort(cfg, topk_ids, n_tokens, cnt, off, perm, inv, st);
+  if (e != 0) return e;
+
+  GemmParams p{};
+  p.cnt = cnt; p.off = off; p.perm = perm; p.partial = partial; p.tickets = tickets; p.status = status;
+  p.nloc = cfg->local_count; p.top_k = cfg->top_k;
+  p.evict_first = plan.N <= 64 ? 1 : 0;
+
+  p.w = static_cast<const uint8_t*>(packed13); p.gs = gs13; p.act = x; p.outp = inter; p.post_norm_w = nullptr;
+  p.K = cfg->hidden; p.out_ld = cfg->inter; p.n_pairs = cfg->inter / 128; p.splits = plan.s13;
+  e = launch_gemm_n<0>(plan.N, p, plan.grid, st);
+  if (e != 0) return e;
+
+  p.w = static_cast<const uint8_t*>(packed2); p.gs = gs2; p.act = inter; p.outp = y;
+  p.post_norm_w = static_cast<const __nv_bfloat16*>(post_norm_w);
+  p.K = cfg->inter; p.out_ld = cfg->hidden; p.n_pairs = cfg->hidden / 256; p.splits = plan.s2;
+  e = launch_gemm_n<1>(plan.N, p, plan.grid, st);
+  if (e != 0) return e;
+
+  combine_kernel<<<static_cast<unsigned>(n_tokens), COMBINE_THREADS, 0, st>>>(
+      y, inv, topk_weights, static_cast<__nv_bfloat16*>(out), cfg->hidden, cfg->top_k, post_norm_w != nullptr ? 1 : 0,
+      cfg->post_norm_eps);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int msk_moe_read_status(const void* workspace, int* host_status, void* stream) {
+  if (!workspace || !host_status) return MSK_ERR_NULL;
+  cudaError_t e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return static_cast<int>(e);
+  e = cudaMemcpy(host_status, workspace, sizeof(int), cudaMemcpyDeviceToHost);
+  return static_cast<int>(e);
+}
+
+int msk_moe_attrs(int which, int token_tile, int* host_out) {
+  if (!host_out) return MSK_ERR_NULL;
+  cudaFuncAttributes a{};
+  cudaError_t e = cudaSuccess;
+  switch (which) {
+    case 0: e = cudaFuncGetAttributes(&a, sort_kernel); break;
+    case 1: e = cudaFuncGetAttributes(&a, route_topk_kernel); break;
+    case 2:
+    case 3: {
+      const bool ph1 = which == 3;
+      switch (token_tile) {
+        case 16: e = ph1 ? cudaFuncGetAttributes(&a, moe_gemm_kernel<16, 1>) : cudaFuncGetAttributes(&a, moe_gemm_kernel<16, 0>); break;
+        case 32: e = ph1 ? cudaFuncGetAttributes(&a, moe_gemm_kernel<32, 1>) : cudaFuncGetAttributes(&a, moe_gemm_kernel<32, 0>); break;
+        case 64: e = ph1 ? cudaFuncGetAttributes(&a, moe_gemm_kernel<64, 1>) : cudaFuncGetAttributes(&a, moe_gemm_kernel<64, 0>); break;
+        case 128: e = ph1 ? cudaFuncGetAttributes(&a, moe_gemm_kernel<128, 1>) : cudaFuncGetAttributes(&a, moe_gemm_kernel<128, 0>); break;
+        default: return MSK_ERR_SHAPE;
+      }
+      break;
+    }
+    case 4: e = cudaFuncGetAttributes(&a, combine_kernel); break;
+    default: return MSK_ERR_SHAPE;
+  }
+  if (e != cudaSuccess) return static_cast<int>(e);
+  host_out[0] = a.numRegs;
+  host_out[1] = static_cast<int>(a.sharedSizeBytes);
+  host_out[2] = a.maxDynamicSharedSizeBytes;
+  host_out[3] = static_cast<int>(a.localSizeBytes);
+  return MSK_OK;
+}
+
+int msk_bw_probe(const void* src, size_t bytes, int stages, int stage_bytes, int num_ctas, uint32_t* sink,
+                 void* stream) {
+  if (!src || !sink) return MSK_ERR_NULL;
+  if (!aligned16(src)) return MSK_ERR_ALIGN;
+  if (stages < 1 || stages > 8 || stage_bytes < 16 || stage_bytes % 16 != 0) return MSK_ERR_SHAPE;
+  const size_t smem = static_cast<size_t>(stages) * stage_bytes;
+  if (smem > 220 * 1024) return MSK_ERR_TOO_LARGE;
+  const int grid = num_ctas > 0 ? num_ctas : sm_count();
+  cudaError_t e = cudaFuncSetAttribute(bw_probe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(smem));
+  if (e != cudaSuccess) return static_cast<int>(e);
+  bw_probe_kernel<<<grid, 64, smem, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint8_t*>(src), static_cast<unsigned long long>(bytes), stages, stage_bytes, sink);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // extern "C"

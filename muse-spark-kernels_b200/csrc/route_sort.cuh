@@ -1,0 +1,216 @@
+// Routing kernels: FP32 router logits, top-k with its two score functions, and the
+// stable counting sort of (token, slot) entries by local expert.
+#pragma once
+#include <cstdint>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+namespace msk {
+
+constexpr int SORT_THREADS = 1024;
+constexpr int SORT_WARPS = SORT_THREADS / 32;
+constexpr int MAX_LOCAL_EXPERTS = 256;
+constexpr int MAX_EXPERTS = 512;
+constexpr int MAX_TOP_K = 16;
+
+// ------------------------------------------------------------------ router
+// One block per (token, 8 experts): each warp owns one expert row and walks H with a
+// fixed lane stride; the lane partials are combined by a fixed shuffle tree, so the
+// sum order depends on H only (precedent: muse_decode_layer/cuda/router_fp32.cu:4-40).
+__global__ void __launch_bounds__(256) router_logits_kernel(const __nv_bfloat16* __restrict__ x,
+                                                            const float* __restrict__ w, float* __restrict__ logits,
+                                                            int H, int E) {
+  const int t = blockIdx.x;
+  const int e = blockIdx.y * 8 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (e >= E) return;
+  const __nv_bfloat16* xr = x + static_cast<size_t>(t) * H;
+  const float* wr = w + static_cast<size_t>(e) * H;
+  float acc = 0.f;
+  for (int h = lane; h < H; h += 32) acc = fmaf(__bfloat162float(xr[h]), wr[h], acc);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if (lane == 0) logits[static_cast<size_t>(t) * E + e] = acc;
+}
+
+// ------------------------------------------------------------------- top-k
+// Monotone map float -> u32 (flip the sign bit of non-negatives, all bits of negatives),
+// the transform the reference uses for its packed arg-max keys
+// (muse_prefill_layer/cuda/prefill.cu:1655-1658, muse_decode_layer/py/07_link_chain.py:101-112).
+__device__ __forceinline__ uint32_t orderable_u32(float f) {
+  const uint32_t u = __float_as_uint(f);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+// One warp per token. key = orderable(score) << 32 | (0xFFFFFFFF - e): the largest key is the
+// highest score, lowest index on ties. k rounds of warp arg-max, the winner is retired.
+// mode 0: score = logit, weights = softmax over the k selected logits.
+// mode 1: s = sigmoid(logit * scale), score = s + bias, weights = s / (sum s + 1e-15)
+//         (muse_decode_layer/py/04_triton_kernels.py:541-552).
+__global__ void __launch_bounds__(256) route_topk_kernel(const float* __restrict__ logits,
+                                                         const float* __restrict__ bias, int32_t* __restrict__ ids,
+                                                         float* __restrict__ wts, int T, int E, int k, int mode,
+                                                         float scale) {
+  const int t = blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (t >= T) return;
+  constexpr int PER = MAX_EXPERTS / 32;
+  uint64_t key[PER];
+  float raw[PER];  // the value the weight is formed from (logit or sigmoid score)
+  const float* row = logits + static_cast<size_t>(t) * E;
+#pragma unroll
+  for (int i = 0; i < PER; ++i) {
+    const int e = i * 32 + lane;
+    key[i] = 0ull;
+    raw[i] = 0.f;
+    if (e < E) {
+      const float l = row[e];
+      float sel = l, r = l;
+      if (mode == 1) {
+        r = 1.0f / (1.0f + expf(-l * scale));
+        sel = r + (bias ? bias[e] : 0.f);
+      }
+      raw[i] = r;
+      key[i] = (static_cast<uint64_t>(orderable_u32(sel)) << 32) | static_cast<uint64_t>(0xFFFFFFFFu - e);
+    }
+  }
+  float my_val = 0.f;  // lane s keeps the value of slot s
+  int my_id = 0;
+  for (int s = 0; s < k; ++s) {
+    uint64_t best = 0ull;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) best = key[i] > best ? key[i] : best;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const uint64_t other = __shfl_xor_sync(0xffffffffu, best, o);
+      best = other > best ? other : best;
+    }
+    const int e = static_cast<int>(0xFFFFFFFFu - static_cast<uint32_t>(best & 0xFFFFFFFFull));
+    float v = 0.f;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+      if (i * 32 + lane == e) {
+        v = raw[i];
+        key[i] = 0ull;
+      }
+    }
+    v = __shfl_sync(0xffffffffu, v, e & 31);
+    if (lane == s) {
+      my_val = v;
+      my_id = e;
+    }
+  }
+  float w;
+  if (mode == 0) {
+    float m = lane < k ? my_val : -INFINITY;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    const float ex = lane < k ? expf(my_val - m) : 0.f;
+    float sum = ex;  // fixed butterfly: same order on every run
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    w = ex / sum;
+  } else {
+    float sum = lane < k ? my_val : 0.f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    w = my_val / (sum + 1e-15f);
+  }
+  if (lane < k) {
+    ids[static_cast<size_t>(t) * k + lane] = my_id;
+    wts[static_cast<size_t>(t) * k + lane] = w;
+  }
+}
+
+// -------------------------------------------------------------------- sort
+// Stable counting sort by local expert in one CTA (what every CTA of the reference
+// kernel does redundantly in muse_moe_w4a16/cuda/moe.cu:315-433; here it runs once and
+// writes global tables). Warp w owns the contiguous entry range [w*chunk, (w+1)*chunk);
+// pass 1 counts per (warp, expert); a scan turns the counts into per-warp bases; pass 2
+// ranks each entry inside its 32-entry step with match_any/popc, so equal experts keep
+// ascending entry order.
+struct SortSmem {
+  int wcnt[SORT_WARPS][MAX_LOCAL_EXPERTS];
+  int tot[MAX_LOCAL_EXPERTS];
+  int wsum[MAX_LOCAL_EXPERTS / 32];
+};
+
+__device__ __forceinline__ int local_expert(int id, int lo, int nloc) {
+  const int l = id - lo;
+  return (id >= 0 && l >= 0 && l < nloc) ? l : -1;
+}
+
+__device__ void sort_entries_block(SortSmem& sm, const int32_t* __restrict__ ids, int n, int lo, int nloc,
+                                   int32_t* __restrict__ cnt, int32_t* __restrict__ off, int32_t* __restrict__ perm,
+                                   int32_t* __restrict__ inv) {
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int chunk = ((n + SORT_WARPS - 1) / SORT_WARPS + 31) & ~31;
+  const int beg = warp * chunk, end = min(n, beg + chunk);
+  for (int i = tid; i < SORT_WARPS * MAX_LOCAL_EXPERTS; i += SORT_THREADS) (&sm.wcnt[0][0])[i] = 0;
+  __syncthreads();
+  for (int base = beg; base < end; base += 32) {
+    const int i = base + lane;
+    const int l = i < end ? local_expert(ids[i], lo, nloc) : -1;
+    const unsigned peers = __match_any_sync(0xffffffffu, l);
+    if (l >= 0 && (peers & ((1u << lane) - 1u)) == 0u) sm.wcnt[warp][l] += __popc(peers);
+    __syncwarp();
+  }
+  __syncthreads();
+  // per expert: exclusive scan over warps; thread e owns expert e
+  if (tid < MAX_LOCAL_EXPERTS) {
+    int acc = 0;
+    if (tid < nloc) {
+      for (int w = 0; w < SORT_WARPS; ++w) {
+        const int c = sm.wcnt[w][tid];
+        sm.wcnt[w][tid] = acc;
+        acc += c;
+      }
+      cnt[tid] = acc;
+    }
+    // exclusive scan of the totals over experts (8 warps x 32)
+    int incl = acc;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += v;
+    }
+    if (lane == 31) sm.wsum[warp] = incl;
+    sm.tot[tid] = incl - acc;  // exclusive within the warp
+  }
+  __syncthreads();
+  if (tid < MAX_LOCAL_EXPERTS) {
+    int wbase = 0;
+    for (int w = 0; w < warp; ++w) wbase += sm.wsum[w];
+    const int ex = sm.tot[tid] + wbase;
+    __syncwarp();
+    sm.tot[tid] = ex;
+    if (tid < nloc) off[tid] = ex;
+    if (tid == nloc - 1) off[nloc] = ex + cnt[tid];
+  }
+  __syncthreads();
+  for (int base = beg; base < end; base += 32) {
+    const int i = base + lane;
+    const int l = i < end ? local_expert(ids[i], lo, nloc) : -1;
+    const unsigned peers = __match_any_sync(0xffffffffu, l);
+    const int rank = __popc(peers & ((1u << lane) - 1u));
+    int q = -1;
+    if (l >= 0) q = sm.tot[l] + sm.wcnt[warp][l] + rank;
+    __syncwarp();
+    if (l >= 0 && rank == 0) sm.wcnt[warp][l] += __popc(peers);
+    __syncwarp();
+    if (i < end) {
+      inv[i] = q;
+      if (q >= 0) perm[q] = i;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(SORT_THREADS) sort_kernel(const int32_t* __restrict__ ids, int n, int lo, int nloc,
+                                                            int32_t* __restrict__ cnt, int32_t* __restrict__ off,
+                                                            int32_t* __restrict__ perm, int32_t* __restrict__ inv) {
+  extern __shared__ __align__(16) unsigned char sort_smem_raw[];
+  SortSmem& sm = *reinterpret_cast<SortSmem*>(sort_smem_raw);
+  sort_entries_block(sm, ids, n, lo, nloc, cnt, off, perm, inv);
+}
+
+}  // namespace msk

@@ -1,0 +1,191 @@
+"""muse_moe_w4a16 for B200: the reference module's two entry points over libmsk_moe.so.
+
+    state = prepare(weights)            # once; may synchronise; lossless repack only
+    out   = kernel_fn(data, state)      # timed path; no host sync; CUDA-graph capturable
+
+`weights` and `data` are the reference's `Weights` / `Inputs` dicts
+(muse_moe_w4a16/py/00_moe_w4a16.py:72-97; prepare: py/02_prepare.py:2, kernel_fn:
+py/03_kernel_fn.py:18-45). Extensions, all optional:
+  weights["router"]       fp32 [E, H]   -> kernel_fn computes logits = x @ router.T in FP32
+  weights["route_bias"]   fp32 [E]      -> selection bias of the sigmoid routing mode
+  data["router_logits"]   fp32 [T, E]   -> kernel_fn runs top-k itself (ids/weights not needed)
+  post_norm_w may be absent             -> plain weighted combine, no post-expert RMS norm
+There is no CPU path: tensors must be CUDA tensors and the native library must load.
+"""
+import ctypes
+
+import torch
+
+from . import _lib
+from ._lib import ROUTE_SIGMOID_BIAS, ROUTE_SOFTMAX_TOPK, MskMoeCfg
+
+__all__ = ["prepare", "kernel_fn", "export_weights", "read_status", "workspace_views", "attrs"]
+
+_MODES = {"softmax_topk": ROUTE_SOFTMAX_TOPK, "sigmoid_bias": ROUTE_SIGMOID_BIAS}
+
+
+def _u8(t):
+    # the decode layer hands the codes over with whatever 1-byte dtype the checkpoint used
+    # (muse_decode_layer/py/03_layer_helpers.py:68), so reinterpret instead of converting
+    return t.contiguous().view(torch.uint8)
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def prepare(weights, *, local_start=0, n_experts=None, top_k=8, max_tokens=8192, routing_mode="softmax_topk",
+            route_scale=0.1767766952966369, post_norm_eps=1e-8, num_ctas=0, split_k13=0, split_k2=0, token_tile=0):
+    """Repack the NVFP4 weights into the tile layout the GEMM kernel streams (bit and byte
+    permutations only, never requantised) and allocate the workspace. Returns `state`."""
+    w13 = _u8(weights["w13"])
+    if not w13.is_cuda:
+        raise RuntimeError("muse_moe_w4a16.prepare: weights must be CUDA tensors (there is no CPU path)")
+    lib = _lib.load()
+    dev = w13.device
+    n_local, two_i, half_h = w13.shape
+    I, H = two_i // 2, half_h * 2
+    w13_sf, w2, w2_sf = _u8(weights["w13_sf"]), _u8(weights["w2"]), _u8(weights["w2_sf"])
+    if tuple(w2.shape) != (n_local, H, I // 2) or tuple(w13_sf.shape) != (n_local, 2 * I, H // 16) \
+            or tuple(w2_sf.shape) != (n_local, H, I // 16):
+        raise RuntimeError("muse_moe_w4a16.prepare: inconsistent weight shapes")
+    if weights["w13_gs"].dtype != torch.float32 or weights["w2_gs"].dtype != torch.float32:
+        raise RuntimeError("muse_moe_w4a16.prepare: global scales must be float32")
+    cfg = MskMoeCfg(hidden=H, inter=I, n_experts=n_experts or n_local, local_start=local_start,
+                    local_count=n_local, top_k=top_k, routing_mode=_MODES[routing_mode], route_scale=route_scale,
+                    post_norm_eps=post_norm_eps, num_ctas=num_ctas, split_k13=split_k13, split_k2=split_k2,
+                    token_tile=token_tile, max_tokens=max_tokens)
+    b13, b2 = ctypes.c_size_t(), ctypes.c_size_t()
+    _lib.check(lib.msk_moe_packed_bytes(ctypes.byref(cfg), ctypes.byref(b13), ctypes.byref(b2)), "msk_moe_packed_bytes")
+    with torch.cuda.device(dev):
+        packed13 = torch.empty(b13.value, dtype=torch.uint8, device=dev)
+        packed2 = torch.empty(b2.value, dtype=torch.uint8, device=dev)
+        _lib.check(lib.msk_moe_repack(ctypes.byref(cfg), _lib.ptr(w13), _lib.ptr(w13_sf), _lib.ptr(w2), _lib.ptr(w2_sf),
+                                      _lib.ptr(packed13), _lib.ptr(packed2), _stream()), "msk_moe_repack")
+        wsb = ctypes.c_size_t()
+        _lib.check(lib.msk_moe_workspace_bytes(ctypes.byref(cfg), ctypes.byref(wsb)), "msk_moe_workspace_bytes")
+        workspace = torch.empty(wsb.value, dtype=torch.uint8, device=dev)
+        _lib.check(lib.msk_moe_workspace_init(ctypes.byref(cfg), _lib.ptr(workspace), wsb.value, _stream()),
+                   "msk_moe_workspace_init")
+        torch.cuda.synchronize(dev)
+    pnw = weights.get("post_norm_w")
+    if pnw is not None and pnw.dtype != torch.bfloat16:
+        raise RuntimeError("muse_moe_w4a16.prepare: post_norm_w must stay bfloat16")
+    state = {
+        "cfg": cfg, "lib": _lib.LibHandle(), "lo": local_start, "cnt": n_local,
+        "packed13": packed13, "packed2": packed2,
+        "gs13": weights["w13_gs"].contiguous(), "gs2": weights["w2_gs"].contiguous(),
+        "post_norm_w": None if pnw is None else pnw.contiguous(),
+        "router": None if weights.get("router") is None else weights["router"].float().contiguous(),
+        "route_bias": None if weights.get("route_bias") is None else weights["route_bias"].float().contiguous(),
+        "workspace": workspace, "workspace_bytes": wsb.value,
+    }
+    return state
+
+
+def _route(data, state, x, T):
+    cfg, lib = state["cfg"], state["lib"].lib
+    if "topk_ids" in data and data["topk_ids"] is not None:
+        ids = data["topk_ids"].to(torch.int32).contiguous()
+        tw = data["topk_weights"].to(torch.float32).contiguous()
+        return ids, tw
+    logits = data.get("router_logits")
+    if logits is None:
+        if state["router"] is None:
+            raise RuntimeError("muse_moe_w4a16.kernel_fn: need topk_ids/topk_weights, router_logits or weights['router']")
+        logits = torch.empty((T, cfg.n_experts), dtype=torch.float32, device=x.device)
+        _lib.check(lib.msk_moe_router_logits(ctypes.byref(cfg), _lib.ptr(x), _lib.ptr(state["router"]),
+                                             _lib.ptr(logits), T, _stream()), "msk_moe_router_logits")
+    logits = logits.to(torch.float32).contiguous()
+    ids = torch.empty((T, cfg.top_k), dtype=torch.int32, device=x.device)
+    tw = torch.empty((T, cfg.top_k), dtype=torch.float32, device=x.device)
+    _lib.check(lib.msk_moe_route(ctypes.byref(cfg), _lib.ptr(logits), _lib.ptr(state["route_bias"]), _lib.ptr(ids),
+                                 _lib.ptr(tw), T, _stream()), "msk_moe_route")
+    return ids, tw
+
+
+def kernel_fn(data, state, return_routing=False):
+    """One routed-expert step. Fresh bf16 [T, H] output per call; launches only."""
+    cfg, lib = state["cfg"], state["lib"].lib
+    x = data["hidden_states"].contiguous()
+    if not x.is_cuda or x.dtype != torch.bfloat16:
+        raise RuntimeError("muse_moe_w4a16.kernel_fn: hidden_states must be a CUDA bfloat16 tensor")
+    T = x.shape[0]
+    dcfg = data.get("config")
+    if dcfg is not None and (dcfg["local_start"] != state["lo"] or dcfg["local_count"] != state["cnt"]):
+        raise RuntimeError("muse_moe_w4a16.kernel_fn: config local range differs from the prepared state")
+    ids, tw = _route(data, state, x, T)
+    out = torch.empty((T, cfg.hidden), dtype=torch.bfloat16, device=x.device)
+    _lib.check(lib.msk_moe_forward(ctypes.byref(cfg), _lib.ptr(state["packed13"]), _lib.ptr(state["packed2"]),
+                                   _lib.ptr(state["gs13"]), _lib.ptr(state["gs2"]), _lib.ptr(state["post_norm_w"]),
+                                   _lib.ptr(x), _lib.ptr(ids), _lib.ptr(tw), _lib.ptr(out),
+                                   _lib.ptr(state["workspace"]), state["workspace_bytes"], T, _stream()),
+               "msk_moe_forward")
+    if return_routing:
+        return out, ids, tw
+    return out
+
+
+def export_weights(state):
+    """Inverse of the prepare-time repack: the original codes and scale bytes, bit for bit."""
+    cfg, lib = state["cfg"], state["lib"].lib
+    dev = state["packed13"].device
+    E, H, I = cfg.local_count, cfg.hidden, cfg.inter
+    w13 = torch.empty((E, 2 * I, H // 2), dtype=torch.uint8, device=dev)
+    w13_sf = torch.empty((E, 2 * I, H // 16), dtype=torch.uint8, device=dev)
+    w2 = torch.empty((E, H, I // 2), dtype=torch.uint8, device=dev)
+    w2_sf = torch.empty((E, H, I // 16), dtype=torch.uint8, device=dev)
+    _lib.check(lib.msk_moe_unpack(ctypes.byref(cfg), _lib.ptr(state["packed13"]), _lib.ptr(state["packed2"]),
+                                  _lib.ptr(w13), _lib.ptr(w13_sf), _lib.ptr(w2), _lib.ptr(w2_sf), _stream()),
+               "msk_moe_unpack")
+    return {"w13": w13, "w13_sf": w13_sf, "w2": w2, "w2_sf": w2_sf}
+
+
+def dequant_packed(state):
+    """BF16 e2m1*e4m3 matrices decoded on the device from the packed tiles (test hook)."""
+    cfg, lib = state["cfg"], state["lib"].lib
+    dev = state["packed13"].device
+    E, H, I = cfg.local_count, cfg.hidden, cfg.inter
+    dq13 = torch.empty((E, 2 * I, H), dtype=torch.bfloat16, device=dev)
+    dq2 = torch.empty((E, H, I), dtype=torch.bfloat16, device=dev)
+    _lib.check(lib.msk_moe_dequant_packed(ctypes.byref(cfg), _lib.ptr(state["packed13"]), _lib.ptr(state["packed2"]),
+                                          _lib.ptr(dq13), _lib.ptr(dq2), _stream()), "msk_moe_dequant_packed")
+    return dq13, dq2
+
+
+def read_status(state):
+    """Device status word (0 = every bounded wait completed). Synchronises; not for the timed path."""
+    out = ctypes.c_int(-1)
+    _lib.check(state["lib"].lib.msk_moe_read_status(_lib.ptr(state["workspace"]), ctypes.byref(out), _stream()),
+               "msk_moe_read_status")
+    return out.value
+
+
+def workspace_views(state, T):
+    """cnt, off, perm, inv, inter, y of the last kernel_fn call with T tokens (copies)."""
+    cfg, lib = state["cfg"], state["lib"].lib
+    ws = state["workspace"]
+    base = ws.data_ptr()
+
+    def view(which, nbytes, dtype):
+        p = ctypes.c_void_p()
+        _lib.check(lib.msk_moe_workspace_view(ctypes.byref(cfg), _lib.ptr(ws), which, ctypes.byref(p)), "workspace_view")
+        o = p.value - base
+        return ws[o:o + nbytes].view(dtype).clone()
+
+    E, k = cfg.local_count, cfg.top_k
+    cnt = view(0, E * 4, torch.int32)
+    off = view(1, (E + 1) * 4, torch.int32)
+    R = int(off[-1].item())
+    perm = view(2, T * k * 4, torch.int32)
+    inv = view(3, T * k * 4, torch.int32)
+    inter = view(4, R * cfg.inter * 2, torch.bfloat16).view(R, cfg.inter)
+    y = view(5, R * cfg.hidden * 4, torch.float32).view(R, cfg.hidden)
+    return {"cnt": cnt, "off": off, "perm": perm, "inv": inv, "inter": inter, "y": y}
+
+
+def attrs(which, token_tile=16):
+    """(registers, static smem, max dynamic smem, local bytes) of a kernel; see msk_moe_attrs."""
+    out = (ctypes.c_int * 4)()
+    _lib.check(_lib.load().msk_moe_attrs(which, token_tile, out), "msk_moe_attrs")
+    return tuple(out)
