@@ -133,6 +133,20 @@ int msk_moe_forward(const MskMoeCfg* cfg, const void* packed13, const void* pack
                     const float* topk_weights, void* out, void* workspace, size_t workspace_bytes, int n_tokens,
                     void* stream);
 
+/* msk_moe_forward with a CUDA event before and after each of its four launches. Waits for the
+ * last one and returns the elapsed milliseconds host_ms[4] = sort, gate/up GEMM, down GEMM,
+ * combine. A measuring entry point: it synchronises and creates its events on first use; the
+ * counterpart of the reference's in-kernel %globaltimer trace (muse_moe_w4a16/cuda/moe.cu:279-284). */
+int msk_moe_forward_timed(const MskMoeCfg* cfg, const void* packed13, const void* packed2, const float* gs13,
+                          const float* gs2, const void* post_norm_w, const void* x, const int32_t* topk_ids,
+                          const float* topk_weights, void* out, void* workspace, size_t workspace_bytes,
+                          int n_tokens, void* stream, float* host_ms);
+
+/* The launch plan msk_moe_forward uses for n_tokens: host_out[4] = token tile N, K splits of the
+ * gate/up GEMM, K splits of the down GEMM, persistent grid size. The reference picks its build by
+ * token count the same way (muse_moe_w4a16/py/03_kernel_fn.py:33-40). */
+int msk_moe_plan(const MskMoeCfg* cfg, int n_tokens, int* host_out);
+
 /* Views into the workspace after msk_moe_forward (device pointers, for parity tests):
  * which: 0 cnt, 1 off, 2 perm, 3 inv, 4 inter (bf16 [R, I]), 5 y (fp32 [R, H]). */
 int msk_moe_workspace_view(const MskMoeCfg* cfg, void* workspace, int which, void** host_ptr);

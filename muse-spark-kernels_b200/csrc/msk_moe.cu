@@ -532,10 +532,11 @@ int msk_moe_workspace_view(const MskMoeCfg* cfg, void* workspace, int which, voi
   return MSK_OK;
 }
 
-int msk_moe_forward(const MskMoeCfg* cfg, const void* packed13, const void* packed2, const float* gs13,
-                    const float* gs2, const void* post_norm_w, const void* x, const int32_t* topk_ids,
-                    const float* topk_weights, void* out, void* workspace, size_t workspace_bytes, int n_tokens,
-                    void* stream) {
+// ev, when given, holds 5 events: recorded before sort, gate/up GEMM, down GEMM, combine and after it.
+static int forward_impl(const MskMoeCfg* cfg, const void* packed13, const void* packed2, const float* gs13,
+                        const float* gs2, const void* post_norm_w, const void* x, const int32_t* topk_ids,
+                        const float* topk_weights, void* out, void* workspace, size_t workspace_bytes, int n_tokens,
+                        void* stream, cudaEvent_t* ev) {
   const int rc = check_cfg(cfg);
   if (rc != MSK_OK) return rc;
   if (!packed13 || !packed2 || !gs13 || !gs2 || !workspace) return MSK_ERR_NULL;
@@ -574,8 +575,10 @@ int msk_moe_forward(const MskMoeCfg* cfg, const void* packed13, const void* pack
     if (plan.s2 > 1 && need2 > have) plan.s2 = 1;
   }
 
+  if (ev) cudaEventRecord(ev[0], st);
   int e = launch_sort(cfg, topk_ids, n_tokens, cnt, off, perm, inv, st);
   if (e != 0) return e;
+  if (ev) cudaEventRecord(ev[1], st);
 
   GemmParams p{};
   p.cnt = cnt; p.off = off; p.perm = perm; p.partial = partial; p.tickets = tickets; p.status = status;
@@ -586,17 +589,66 @@ int msk_moe_forward(const MskMoeCfg* cfg, const void* packed13, const void* pack
   p.K = cfg->hidden; p.out_ld = cfg->inter; p.n_pairs = cfg->inter / 128; p.splits = plan.s13;
   e = launch_gemm_n<0>(plan.N, p, plan.grid, st);
   if (e != 0) return e;
+  if (ev) cudaEventRecord(ev[2], st);
 
   p.w = static_cast<const uint8_t*>(packed2); p.gs = gs2; p.act = inter; p.outp = y;
   p.post_norm_w = static_cast<const __nv_bfloat16*>(post_norm_w);
   p.K = cfg->inter; p.out_ld = cfg->hidden; p.n_pairs = cfg->hidden / 256; p.splits = plan.s2;
   e = launch_gemm_n<1>(plan.N, p, plan.grid, st);
   if (e != 0) return e;
+  if (ev) cudaEventRecord(ev[3], st);
 
   combine_kernel<<<static_cast<unsigned>(n_tokens), COMBINE_THREADS, 0, st>>>(
       y, inv, topk_weights, static_cast<__nv_bfloat16*>(out), cfg->hidden, cfg->top_k, post_norm_w != nullptr ? 1 : 0,
       cfg->post_norm_eps);
+  if (ev) cudaEventRecord(ev[4], st);
   return static_cast<int>(cudaGetLastError());
+}
+
+int msk_moe_forward(const MskMoeCfg* cfg, const void* packed13, const void* packed2, const float* gs13,
+                    const float* gs2, const void* post_norm_w, const void* x, const int32_t* topk_ids,
+                    const float* topk_weights, void* out, void* workspace, size_t workspace_bytes, int n_tokens,
+                    void* stream) {
+  return forward_impl(cfg, packed13, packed2, gs13, gs2, post_norm_w, x, topk_ids, topk_weights, out, workspace,
+                      workspace_bytes, n_tokens, stream, nullptr);
+}
+
+int msk_moe_forward_timed(const MskMoeCfg* cfg, const void* packed13, const void* packed2, const float* gs13,
+                          const float* gs2, const void* post_norm_w, const void* x, const int32_t* topk_ids,
+                          const float* topk_weights, void* out, void* workspace, size_t workspace_bytes,
+                          int n_tokens, void* stream, float* host_ms) {
+  if (!host_ms) return MSK_ERR_NULL;
+  static cudaEvent_t ev[64][5];
+  static bool made[64] = {false};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return MSK_ERR_RANGE;
+  if (!made[dev]) {
+    for (int i = 0; i < 5; ++i) {
+      cudaError_t ce = cudaEventCreate(&ev[dev][i]);
+      if (ce != cudaSuccess) return static_cast<int>(ce);
+    }
+    made[dev] = true;
+  }
+  const int rc = forward_impl(cfg, packed13, packed2, gs13, gs2, post_norm_w, x, topk_ids, topk_weights, out,
+                              workspace, workspace_bytes, n_tokens, stream, ev[dev]);
+  if (rc != 0) return rc;
+  cudaError_t ce = cudaEventSynchronize(ev[dev][4]);
+  if (ce != cudaSuccess) return static_cast<int>(ce);
+  for (int i = 0; i < 4; ++i) {
+    ce = cudaEventElapsedTime(&host_ms[i], ev[dev][i], ev[dev][i + 1]);
+    if (ce != cudaSuccess) return static_cast<int>(ce);
+  }
+  return MSK_OK;
+}
+
+int msk_moe_plan(const MskMoeCfg* cfg, int n_tokens, int* host_out) {
+  const int rc = check_cfg(cfg);
+  if (rc != MSK_OK) return rc;
+  if (!host_out) return MSK_ERR_NULL;
+  if (n_tokens < 1) return MSK_ERR_SHAPE;
+  const Plan plan = make_plan(cfg, n_tokens);
+  host_out[0] = plan.N; host_out[1] = plan.s13; host_out[2] = plan.s2; host_out[3] = plan.grid;
+  return MSK_OK;
 }
 
 int msk_moe_read_status(const void* workspace, int* host_status, void* stream) {

@@ -126,6 +126,30 @@ def kernel_fn(data, state, return_routing=False):
     return out
 
 
+def kernel_fn_timed(data, state):
+    """kernel_fn with CUDA events around each launch of the expert step; synchronises.
+    Returns (out, [ms sort, ms gate/up GEMM, ms down GEMM, ms combine]). Measuring only."""
+    cfg, lib = state["cfg"], state["lib"].lib
+    x = data["hidden_states"].contiguous()
+    T = x.shape[0]
+    ids, tw = _route(data, state, x, T)
+    out = torch.empty((T, cfg.hidden), dtype=torch.bfloat16, device=x.device)
+    ms = (ctypes.c_float * 4)()
+    _lib.check(lib.msk_moe_forward_timed(ctypes.byref(cfg), _lib.ptr(state["packed13"]), _lib.ptr(state["packed2"]),
+                                         _lib.ptr(state["gs13"]), _lib.ptr(state["gs2"]),
+                                         _lib.ptr(state["post_norm_w"]), _lib.ptr(x), _lib.ptr(ids), _lib.ptr(tw),
+                                         _lib.ptr(out), _lib.ptr(state["workspace"]), state["workspace_bytes"], T,
+                                         _stream(), ms), "msk_moe_forward_timed")
+    return out, list(ms)
+
+
+def plan(state, T):
+    """(token tile N, K splits gate/up, K splits down, grid) that kernel_fn uses for T tokens."""
+    out = (ctypes.c_int * 4)()
+    _lib.check(state["lib"].lib.msk_moe_plan(ctypes.byref(state["cfg"]), T, out), "msk_moe_plan")
+    return tuple(out)
+
+
 def export_weights(state):
     """Inverse of the prepare-time repack: the original codes and scale bytes, bit for bit."""
     cfg, lib = state["cfg"], state["lib"].lib

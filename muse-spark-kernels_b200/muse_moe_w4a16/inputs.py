@@ -33,6 +33,23 @@ def make_weights(H, I, n_local, seed, device, post_norm=False):
     return weights
 
 
+def make_weights_random_bytes(H, I, n_local, seed, device):
+    """Valid NVFP4 experts from random codes and scale bytes in the range the quantiser produces
+    for N(0, 0.02) weights (0x63..0x7E). Cheap to build; used where only the cost of the math
+    matters (timing the CPU oracle), not for parity."""
+    gen = torch.Generator(device=device).manual_seed(seed * 7919 + 4)
+
+    def mk(rows, K):
+        codes = torch.randint(0, 256, (n_local, rows, K // 2), generator=gen, device=device, dtype=torch.uint8)
+        sf = torch.randint(0x63, 0x7F, (n_local, rows, K // 16), generator=gen, device=device, dtype=torch.uint8)
+        return codes, sf.view(torch.float8_e4m3fn)
+
+    w13, w13_sf = mk(2 * I, H)
+    w2, w2_sf = mk(H, I)
+    gs = torch.full((n_local,), 2.0e-5, dtype=torch.float32, device=device)
+    return {"w13": w13, "w13_sf": w13_sf, "w13_gs": gs, "w2": w2, "w2_sf": w2_sf, "w2_gs": gs.clone()}
+
+
 def make_logits(T, E, kind, seed, device):
     """FP32 router logits [T, E]. uniform: U(0,1); normal: N(0,1); zipf: N(0,1) + log p_e with
     p_e ~ rank^-1.2 over a seeded permutation of the experts."""
