@@ -60,6 +60,7 @@ typedef struct MskMoeCfg {
   int32_t split_k2;      /* K splits of the down GEMM;    0 = chosen from n_tokens */
   int32_t token_tile;    /* MMA N (tokens per tile): 16/32/64/128; 0 = chosen from n_tokens */
   int32_t max_tokens;    /* token capacity the workspace is sized for (msk_moe_forward rejects more) */
+  int32_t trace;         /* non-zero: the GEMM kernels stamp %globaltimer per CTA into the workspace (view 6) */
 } MskMoeCfg;
 
 /* ---- prepare-time repack (lossless; replaces the four layouts built by
@@ -148,7 +149,8 @@ int msk_moe_forward_timed(const MskMoeCfg* cfg, const void* packed13, const void
 int msk_moe_plan(const MskMoeCfg* cfg, int n_tokens, int* host_out);
 
 /* Views into the workspace after msk_moe_forward (device pointers, for parity tests):
- * which: 0 cnt, 1 off, 2 perm, 3 inv, 4 inter (bf16 [R, I]), 5 y (fp32 [R, H]). */
+ * which: 0 cnt, 1 off, 2 perm, 3 inv, 4 inter (bf16 [R, I]), 5 y (fp32 [R, H]),
+ * 6 trace (uint64 [2 GEMMs][256 CTAs][16 stamps], ns; written when cfg->trace != 0). */
 int msk_moe_workspace_view(const MskMoeCfg* cfg, void* workspace, int which, void** host_ptr);
 
 /* Copies workspace word 0 to *host_status after synchronising `stream`. 0 = no device-side

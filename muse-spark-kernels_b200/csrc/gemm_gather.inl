@@ -1,0 +1,60 @@
+// Role body of moe_gemm_kernel (included inside the kernel): activation gather, warps 2-3.
+// Copies the token rows of the unit (x rows through the permutation for PHASE 0, sorted inter
+// rows for PHASE 1) with 16-byte cp.async into the K-major core-matrix layout of the B operand:
+// element (n, k) at (n/8)*B_SBO + (k/8)*B_LBO + (n%8)*16 + (k%8)*2. Eight lanes write one
+// 128-byte core matrix, so shared-memory writes are conflict free. A stage is published one
+// stage late (after the next one is issued), once its copies have landed and a proxy fence
+// has ordered them before the tensor core's reads.
+    const int gt = tid - 64;                    // 0..63
+    const int n_sub = gt & 7, c_sub = gt >> 3;  // token within an 8-group, chunk within an 8-chunk group
+    uint32_t it = 0;
+    bool ok = true;
+    bool pending = false;  // a committed cp.async group whose barrier has not been signalled
+    uint32_t pending_slot = 0;
+    const size_t act_ld = static_cast<size_t>(p.K);
+    for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
+      const UnitInfo ui = decode_unit(u, tile_start, p, N);
+      const int ks0 = ui.split * per_split, ks1 = min(nst_total, ks0 + per_split);
+      // source row of token n = ng*8 + n_sub, for every 8-group ng
+      const __nv_bfloat16* src[N / 8];
+#pragma unroll
+      for (int ng = 0; ng < N / 8; ++ng) {
+        const int n = ng * 8 + n_sub;
+        src[ng] = nullptr;
+        if (n < ui.rows) {
+          const int r = ui.row0 + n;
+          const size_t row = PHASE == 0 ? static_cast<size_t>(p.perm[r] / p.top_k) : static_cast<size_t>(r);
+          src[ng] = static_cast<const __nv_bfloat16*>(p.act) + row * act_ld;
+        }
+      }
+      for (int ks = ks0; ks < ks1; ++ks, ++it) {
+        const uint32_t slot = it % NST, par = (it / NST) & 1u;
+        if (!mbar_wait(&ctl.b_empty[slot], par ^ 1u, abortw)) { ok = false; break; }
+        uint8_t* dstB = ring + slot * C::STAGE_BYTES + 2 * TILE_BYTES;
+#pragma unroll
+        for (int ng = 0; ng < N / 8; ++ng) {
+          const bool valid = src[ng] != nullptr;
+          const __nv_bfloat16* s = valid ? src[ng] + static_cast<size_t>(ks) * KS : static_cast<const __nv_bfloat16*>(p.act);
+#pragma unroll
+          for (int cg = 0; cg < 4; ++cg) {
+            const int chunk = cg * 8 + c_sub;
+            cp_async16(dstB + ng * B_SBO + chunk * B_LBO + n_sub * 16, s + chunk * 8, valid);
+          }
+        }
+        cp_async_commit();
+        if (pending) {
+          cp_async_wait<1>();
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&ctl.b_full[pending_slot]);
+        }
+        pending = true;
+        pending_slot = slot;
+      }
+    }
+    if (pending) {
+      cp_async_wait<0>();
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&ctl.b_full[pending_slot]);
+    }

@@ -1,0 +1,50 @@
+// Role body of moe_gemm_kernel (included inside the kernel): MMA issuer, warp 1.
+// One A slot (64 K, 32 TMEM columns per tile) is consumed by four K=16 MMAs per tile and
+// handed back with a tcgen05.commit, so several dequant -> MMA -> release hand-offs are in
+// flight at once. The accumulators of consecutive units alternate between NDBUF buffers.
+    constexpr uint32_t idesc = idesc_f16(FMT_BF16, FMT_BF16, 128, N);
+    uint32_t it = 0, unit_i = 0, sc = 0;
+    int tri = 0;
+    bool ok = true;
+    for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x, ++unit_i) {
+      const UnitInfo ui = decode_unit(u, tile_start, p, N);
+      const int ks0 = ui.split * per_split, ks1 = min(nst_total, ks0 + per_split);
+      const uint32_t db = unit_i % NDBUF, duse = unit_i / NDBUF;
+      if (!mbar_wait(&ctl.d_empty[db], (duse & 1u) ^ 1u, abortw)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t d_tmem = tmem + db * (2 * N);
+      for (int ks = ks0; ks < ks1 && ok; ++ks, ++it) {
+        const uint32_t slot = it % NST, par = (it / NST) & 1u;
+        if (!mbar_wait(&ctl.b_full[slot], par, abortw)) { ok = false; break; }
+        const uint32_t b_addr = smem_u32(ring + slot * C::STAGE_BYTES + 2 * TILE_BYTES);
+#pragma unroll
+        for (int sl = 0; sl < 4; ++sl, ++sc) {
+          const uint32_t as = sc % NSLOT, apar = (sc / NSLOT) & 1u;
+          if (!mbar_wait(&ctl.a_full[0][as], apar, abortw) || !mbar_wait(&ctl.a_full[1][as], apar, abortw)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          if (lane == 0) {
+            if (sc == 0) MSK_TR(TR_FIRST_MMA);
+            MSK_TRD(1, tri, 1);
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk) {
+              const int k16 = sl * 4 + kk;
+              const uint64_t bdesc = smem_desc_kmajor_noswz(b_addr + k16 * 256, B_LBO, B_SBO);
+              const uint32_t acc = (ks > ks0 || k16 > 0) ? 1u : 0u;
+              mma_ts(d_tmem, tmem + C::A_BASE + as * 32 + kk * 8, bdesc, idesc, acc);
+              mma_ts(d_tmem + N, tmem + C::A_BASE + C::A_GROUP_COLS + as * 32 + kk * 8, bdesc, idesc, acc);
+            }
+            tc_commit(&ctl.a_empty[as]);
+            MSK_TRD(1, tri, 2);
+          }
+          __syncwarp();
+        }
+        if (!ok) break;
+        if (lane == 0) tc_commit(&ctl.b_empty[slot]);
+        __syncwarp();
+      }
+      if (ok && lane == 0) tc_commit(&ctl.d_full[db]);
+      __syncwarp();
+    }

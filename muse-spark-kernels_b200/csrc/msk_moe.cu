@@ -266,7 +266,9 @@ static int pick_split(double units, int n_stages, int grid) {
   double best_cost = 1e30;
   for (int s = 1; s <= std::min(n_stages, 8); ++s) {
     const double waves = std::ceil(units * s / grid);
-    const double cost = waves * (std::ceil(static_cast<double>(n_stages) / s) + 0.35) + (s > 1 ? 0.5 : 0.0);
+    // per wave: the K stages of one unit plus its fixed cost (pipeline fill, epilogue), in stage times;
+    // splitting adds the partial round trip and the ticket
+    const double cost = waves * (std::ceil(static_cast<double>(n_stages) / s) + 2.0) + (s > 1 ? 3.0 : 0.0);
     if (cost < best_cost - 1e-9) { best_cost = cost; best = s; }
   }
   return best;
@@ -291,9 +293,11 @@ static Plan make_plan(const MskMoeCfg* c, int T) {
 
 // Workspace carving. Everything is sized for max_tokens with the worst plan.
 struct Carve {
-  size_t status, cnt, off, perm, inv, tickets, inter, y, partial, total;
+  size_t status, trace, cnt, off, perm, inv, tickets, inter, y, partial, total;
 };
 constexpr size_t MAX_SPLIT = 8;
+constexpr size_t TRACE_CTAS = 256;
+constexpr size_t TRACE_WORDS = TRACE_CTAS * 16 + 3 * 256;
 
 static size_t max_tiles(const MskMoeCfg* c, int T) {
   // ceil(cnt/16) summed over experts <= R/16 + local_count
@@ -322,6 +326,7 @@ static Carve carve(const MskMoeCfg* c, int T) {
   const size_t R = static_cast<size_t>(T) * c->top_k;
   size_t o = 0;
   k.status = o; o += 256;
+  k.trace = o; o += 2 * TRACE_WORDS * 8;  // two GEMM launches x (CTAs x 16 stamps + 3 x 256 events of CTA 0)
   k.cnt = o; o += round_up(static_cast<size_t>(c->local_count) * 4, 256);
   k.off = o; o += round_up(static_cast<size_t>(c->local_count + 1) * 4, 256);
   k.perm = o; o += round_up(R * 4, 256);
@@ -527,6 +532,7 @@ int msk_moe_workspace_view(const MskMoeCfg* cfg, void* workspace, int which, voi
     case 3: *host_ptr = b + k.inv; break;
     case 4: *host_ptr = b + k.inter; break;
     case 5: *host_ptr = b + k.y; break;
+    case 6: *host_ptr = b + k.trace; break;
     default: return MSK_ERR_SHAPE;
   }
   return MSK_OK;
@@ -583,6 +589,9 @@ static int forward_impl(const MskMoeCfg* cfg, const void* packed13, const void* 
   GemmParams p{};
   p.cnt = cnt; p.off = off; p.perm = perm; p.partial = partial; p.tickets = tickets; p.status = status;
   p.nloc = cfg->local_count; p.top_k = cfg->top_k;
+  unsigned long long* trace = (cfg->trace != 0 && plan.grid <= static_cast<int>(TRACE_CTAS))
+                                  ? reinterpret_cast<unsigned long long*>(b + k.trace) : nullptr;
+  p.trace = trace;
   p.evict_first = plan.N <= 64 ? 1 : 0;
 
   p.w = static_cast<const uint8_t*>(packed13); p.gs = gs13; p.act = x; p.outp = inter; p.post_norm_w = nullptr;
@@ -592,6 +601,7 @@ static int forward_impl(const MskMoeCfg* cfg, const void* packed13, const void* 
   if (ev) cudaEventRecord(ev[2], st);
 
   p.w = static_cast<const uint8_t*>(packed2); p.gs = gs2; p.act = inter; p.outp = y;
+  if (trace) p.trace = trace + TRACE_WORDS;
   p.post_norm_w = static_cast<const __nv_bfloat16*>(post_norm_w);
   p.K = cfg->inter; p.out_ld = cfg->hidden; p.n_pairs = cfg->hidden / 256; p.splits = plan.s2;
   e = launch_gemm_n<1>(plan.N, p, plan.grid, st);

@@ -35,7 +35,8 @@ def _stream():
 
 
 def prepare(weights, *, local_start=0, n_experts=None, top_k=8, max_tokens=8192, routing_mode="softmax_topk",
-            route_scale=0.1767766952966369, post_norm_eps=1e-8, num_ctas=0, split_k13=0, split_k2=0, token_tile=0):
+            route_scale=0.1767766952966369, post_norm_eps=1e-8, num_ctas=0, split_k13=0, split_k2=0, token_tile=0,
+            trace=0):
     """Repack the NVFP4 weights into the tile layout the GEMM kernel streams (bit and byte
     permutations only, never requantised) and allocate the workspace. Returns `state`."""
     w13 = _u8(weights["w13"])
@@ -54,7 +55,7 @@ def prepare(weights, *, local_start=0, n_experts=None, top_k=8, max_tokens=8192,
     cfg = MskMoeCfg(hidden=H, inter=I, n_experts=n_experts or n_local, local_start=local_start,
                     local_count=n_local, top_k=top_k, routing_mode=_MODES[routing_mode], route_scale=route_scale,
                     post_norm_eps=post_norm_eps, num_ctas=num_ctas, split_k13=split_k13, split_k2=split_k2,
-                    token_tile=token_tile, max_tokens=max_tokens)
+                    token_tile=token_tile, max_tokens=max_tokens, trace=trace)
     b13, b2 = ctypes.c_size_t(), ctypes.c_size_t()
     _lib.check(lib.msk_moe_packed_bytes(ctypes.byref(cfg), ctypes.byref(b13), ctypes.byref(b2)), "msk_moe_packed_bytes")
     with torch.cuda.device(dev):
@@ -206,6 +207,20 @@ def workspace_views(state, T):
     inter = view(4, R * cfg.inter * 2, torch.bfloat16).view(R, cfg.inter)
     y = view(5, R * cfg.hidden * 4, torch.float32).view(R, cfg.hidden)
     return {"cnt": cnt, "off": off, "perm": perm, "inv": inv, "inter": inter, "y": y}
+
+
+def trace_stamps(state):
+    """(stamps int64 [2, 256, 16], events int64 [2, 3, 256]) of the last step's two GEMM launches
+    (prepare(trace=1)): per-CTA %globaltimer stamps, and CTA 0's event list per role
+    (dequant thread, MMA issuer, weight producer), each event = ns << 8 | code."""
+    cfg, lib = state["cfg"], state["lib"].lib
+    ws = state["workspace"]
+    p = ctypes.c_void_p()
+    _lib.check(lib.msk_moe_workspace_view(ctypes.byref(cfg), _lib.ptr(ws), 6, ctypes.byref(p)), "workspace_view")
+    o = p.value - ws.data_ptr()
+    words = 256 * 16 + 3 * 256
+    t = ws[o:o + 2 * words * 8].view(torch.int64).view(2, words).clone()
+    return t[:, :256 * 16].reshape(2, 256, 16), t[:, 256 * 16:].reshape(2, 3, 256)
 
 
 def attrs(which, token_tile=16):

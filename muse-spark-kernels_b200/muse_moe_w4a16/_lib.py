@@ -8,7 +8,7 @@ import os
 import threading
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libmsk_moe.so")
+LIB_PATH = os.environ.get("MSK_MOE_LIB", os.path.join(_HERE, "libmsk_moe.so"))  # override: a differently built library
 
 ROUTE_SOFTMAX_TOPK = 0
 ROUTE_SIGMOID_BIAS = 1
@@ -41,6 +41,7 @@ class MskMoeCfg(ctypes.Structure):
         ("split_k2", ctypes.c_int32),
         ("token_tile", ctypes.c_int32),
         ("max_tokens", ctypes.c_int32),
+        ("trace", ctypes.c_int32),
     ]
 
     def __deepcopy__(self, memo):
