@@ -1,0 +1,194 @@
+"""CPU tests: the oracle against the reference-generated golden vectors and hand-computed
+known answers, the quantiser, and the host side of the C ABI (no GPU, no compute calls)."""
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import moe_oracle as orc
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(HERE)
+GOLD = np.load(os.path.join(HERE, "golden", "reference_vectors.npz"))
+
+
+# ------------------------------------------------------------ golden vectors
+def test_nibble_order_matches_reference_split_nibbles():
+    codes, rows = GOLD["nib_codes"], GOLD["nib_rows"]
+    assert np.array_equal(orc.split_nibbles(codes[rows]), GOLD["nib_out"])
+
+
+def test_e4m3_table_matches_reference_lut():
+    lut = GOLD["e4m3_lut"].astype(np.int64) & 0xFFFF           # bf16 bits of value * 2^64
+    vals = orc.e4m3_value(np.arange(256, dtype=np.uint8))
+    want = torch.from_numpy(lut.astype(np.int16)).view(torch.bfloat16).float().numpy()
+    nan = np.isnan(vals)
+    assert list(np.nonzero(nan)[0]) == [0x7F, 0xFF]
+    assert np.array_equal(np.isnan(want), nan)
+    assert np.array_equal(vals[~nan].astype(np.float64) * 2.0 ** 64, want[~nan].astype(np.float64))
+
+
+@pytest.mark.parametrize("bs", [4, 33])
+def test_sort_on_reference_generated_routing(bs):
+    ids = GOLD[f"gen{bs}_ids"]
+    w = GOLD[f"gen{bs}_w"]
+    assert ids.shape == (bs, 8) and np.allclose(w.sum(-1), 1.0, atol=1e-5)
+    cnt, off, perm, inv = orc.sort_routes(ids, 0, 32)  # the reference rank owns experts 0..31
+    flat = ids.reshape(-1)
+    local = (flat >= 0) & (flat < 32)
+    assert cnt.sum() == local.sum() == off[-1]
+    # same answer as a stable sort of the local ids (the bit-exactness target of the kernel)
+    lid = torch.from_numpy(np.where(local, flat, 1 << 20))
+    order = torch.sort(lid, stable=True).indices.numpy()[: int(off[-1])]
+    assert np.array_equal(perm, order)
+    assert np.array_equal(inv[perm], np.arange(len(perm)))
+    assert np.all(inv[~local] == -1)
+    for e in range(32):
+        seg = perm[off[e]:off[e + 1]]
+        assert np.all(flat[seg] == e) and np.all(np.diff(seg) > 0)
+
+
+# --------------------------------------------------------- known-answer tests
+def test_e2m1_codes_known_answers():
+    want = [0, .5, 1, 1.5, 2, 3, 4, 6, -0.0, -.5, -1, -1.5, -2, -3, -4, -6]
+    got = orc.e2m1_value(np.arange(16, dtype=np.uint8))
+    assert np.array_equal(got, np.array(want, dtype=np.float32))
+    assert np.signbit(got[8])
+
+
+@pytest.mark.parametrize("byte,value", [(0x00, 0.0), (0x01, 2.0 ** -9), (0x07, 7 * 2.0 ** -9), (0x08, 2.0 ** -6),
+                                        (0x38, 1.0), (0x40, 2.0), (0x7E, 448.0), (0xB8, -1.0)])
+def test_e4m3_known_answers(byte, value):
+    assert float(orc.e4m3_value(np.uint8(byte))) == value
+
+
+def test_dequant_known_answers_all_codes_times_scales():
+    scales = [0x00, 0x01, 0x07, 0x08, 0x38, 0x40, 0x7E]
+    sv = [0.0, 2.0 ** -9, 7 * 2.0 ** -9, 2.0 ** -6, 1.0, 2.0, 448.0]
+    e2 = [0, .5, 1, 1.5, 2, 3, 4, 6]
+    codes = np.array([[(2 * j) | ((2 * j + 1) << 4) for j in range(8)]] * len(scales), dtype=np.uint8)  # k = 0..15
+    sf = np.array([[s] for s in scales], dtype=np.uint8)
+    for gs in (1.0, 3.0e-5):
+        got = orc.dequant(codes, sf, gs)
+        for r, s in enumerate(sv):
+            for k in range(16):
+                want = np.float32((-1 if k >= 8 else 1) * e2[k % 8] * s) * np.float32(gs)
+                assert got[r, k] == want
+
+
+def test_quantiser_round_trip_and_tie_rule():
+    from muse_moe_w4a16 import quant
+
+    ties = torch.tensor([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, -0.25, -5.0, 7.0, 0.0])
+    codes = quant.e2m1_codes(ties)
+    assert codes.tolist() == [0, 2, 2, 4, 4, 6, 6, 8, 14, 7, 0]  # ties go to the even code
+    g = torch.Generator().manual_seed(0)
+    w = (torch.randn((64, 256), generator=g) * 0.02).to(torch.bfloat16)
+    c, s, gs = quant.quantize_nvfp4(w)
+    assert c.shape == (64, 128) and s.shape == (64, 16)
+    assert abs(float(gs) - float(w.float().abs().max()) / (6 * 448)) < 1e-12
+    dq = orc.dequant(c.numpy(), s.numpy(), float(gs))
+    blk = w.float().view(64, 16, 16).abs().amax(-1).numpy().repeat(16, -1).reshape(64, 256)
+    assert np.all(np.abs(dq - w.float().numpy()) <= 0.26 * blk + 1e-12)  # half an E2M1 step at the block top
+    assert 0x08 <= int(s.min()) and int(s.max()) <= 0x7E                  # normal scale bytes, as the survey found
+
+
+def test_route_topk_tie_rule_and_weights():
+    logits = torch.tensor([[1.0, 3.0, 3.0, -1.0, 3.0, 0.5]])
+    ids, w = orc.route_topk(logits, 3)
+    assert ids.tolist() == [[1, 2, 4]]
+    assert torch.allclose(w, torch.full((1, 3), 1 / 3))
+    ids, w = orc.route_topk(logits, 2, "sigmoid_bias", bias=torch.tensor([0, 0, 0, 5.0, 0, 0]), scale=1.0)
+    assert ids.tolist() == [[3, 1]]
+    s = torch.sigmoid(torch.tensor([-1.0, 3.0]))
+    assert torch.allclose(w[0], s / s.sum())
+
+
+def test_moe_forward_against_dense_evaluation():
+    """The grouped oracle equals a dense per-token evaluation of the same formula."""
+    from muse_moe_w4a16 import inputs
+
+    H, I, E, k, T = 256, 256, 4, 2, 6
+    w = inputs.make_weights(H, I, E, 1, "cpu", post_norm=True)
+    g = torch.Generator().manual_seed(2)
+    x = torch.randn((T, H), generator=g).to(torch.bfloat16)
+    ids, tw = orc.route_topk(torch.randn((T, E), generator=g), k)
+    out, parts = orc.moe_forward(x, ids, tw, w, return_parts=True)
+    ref = torch.zeros((T, H))
+    for t in range(T):
+        for s in range(k):
+            e = int(ids[t, s])
+            y = orc.expert_forward(x[t:t + 1], w["w13"][e], w["w13_sf"][e], w["w13_gs"][e], w["w2"][e], w["w2_sf"][e],
+                                   w["w2_gs"][e])[0]
+            y = y * (1 + w["post_norm_w"].float())
+            y = y * torch.rsqrt(y.pow(2).mean() + 1e-8)
+            ref[t] += tw[t, s] * y
+    assert torch.allclose(parts["out_fp32"], ref, rtol=1e-5, atol=1e-6)
+    # local-range filter: the two halves of the experts sum to the whole (partial sums, EP "filter" mode)
+    lo = {key: (v[:2] if key != "post_norm_w" else v) for key, v in w.items()}
+    hi = {key: (v[2:] if key != "post_norm_w" else v) for key, v in w.items()}
+    _, p0 = orc.moe_forward(x, ids, tw, lo, local_start=0, return_parts=True)
+    _, p1 = orc.moe_forward(x, ids, tw, hi, local_start=2, return_parts=True)
+    assert torch.allclose(p0["out_fp32"] + p1["out_fp32"], parts["out_fp32"], rtol=1e-5, atol=1e-6)
+
+
+# ------------------------------------------------------------ C ABI, host side
+def _declared_symbols():
+    text = open(os.path.join(ROOT, "include", "msk_moe.h")).read()
+    return sorted(set(re.findall(r"^int (msk_\w+)\(", text, flags=re.M)))
+
+
+def test_library_exports_every_declared_symbol():
+    from muse_moe_w4a16 import _lib
+
+    lib = _lib.load()
+    declared = _declared_symbols()
+    assert len(declared) >= 14
+    for name in declared:
+        assert hasattr(lib, name), name
+    assert sorted(_lib.SIGNATURES) == declared  # the binding table and the header agree
+
+
+def test_host_side_validation_rejects_bad_arguments():
+    from muse_moe_w4a16 import _lib
+
+    lib = _lib.load()
+    good = dict(hidden=512, inter=256, n_experts=8, local_start=0, local_count=8, top_k=2, max_tokens=4)
+    cfg = _lib.MskMoeCfg(**good)
+    a, b = ctypes.c_size_t(), ctypes.c_size_t()
+    assert lib.msk_moe_packed_bytes(ctypes.byref(cfg), ctypes.byref(a), ctypes.byref(b)) == 0
+    assert a.value == 8 * (2 * 256 // 128) * (512 // 256) * 18432 and b.value == 8 * (512 // 128) * 1 * 18432
+    assert lib.msk_moe_packed_bytes(None, ctypes.byref(a), ctypes.byref(b)) == -1
+    for bad in (dict(hidden=500), dict(inter=128), dict(top_k=0), dict(top_k=17), dict(local_count=0),
+                dict(local_count=300), dict(n_experts=600)):
+        c = _lib.MskMoeCfg(**{**good, **bad})
+        assert lib.msk_moe_packed_bytes(ctypes.byref(c), ctypes.byref(a), ctypes.byref(b)) == -2, bad
+    c = _lib.MskMoeCfg(**{**good, "local_start": 4})
+    assert lib.msk_moe_packed_bytes(ctypes.byref(c), ctypes.byref(a), ctypes.byref(b)) == -5
+    ws = ctypes.c_size_t()
+    assert lib.msk_moe_workspace_bytes(ctypes.byref(cfg), ctypes.byref(ws)) == 0 and ws.value > 4 * 2 * 512 * 4
+    # forward: NULL pointers, too many tokens, undersized workspace are refused before any launch
+    p = ctypes.c_void_p(0)
+    assert lib.msk_moe_forward(ctypes.byref(cfg), p, p, p, p, p, p, p, p, p, p, 0, 1, p) == -1
+    fake = ctypes.c_void_p(4096)
+    assert lib.msk_moe_forward(ctypes.byref(cfg), fake, fake, fake, fake, None, fake, fake, fake, fake, fake,
+                               ws.value, 5, None) == -6
+    assert lib.msk_moe_forward(ctypes.byref(cfg), fake, fake, fake, fake, None, fake, fake, fake, fake, fake,
+                               16, 4, None) == -4
+    odd = ctypes.c_void_p(4100)
+    assert lib.msk_moe_forward(ctypes.byref(cfg), odd, fake, fake, fake, None, fake, fake, fake, fake, fake,
+                               ws.value, 4, None) == -3
+    plan = (ctypes.c_int * 4)()
+    assert lib.msk_moe_plan(ctypes.byref(cfg), 4, plan) == 0 and plan[0] in (16, 32, 64, 128)
+
+
+def test_module_refuses_cpu_tensors():
+    import muse_moe_w4a16 as moe
+    from muse_moe_w4a16 import inputs
+
+    w = inputs.make_weights(256, 256, 2, 0, "cpu")
+    with pytest.raises(RuntimeError, match="CUDA"):
+        moe.prepare(w)
