@@ -95,8 +95,12 @@ enum : int { TR_START = 0, TR_SETUP, TR_FIRST_BULK, TR_FIRST_RAW, TR_FIRST_AFULL
 // Detailed event list of CTA 0: role r (0 first dequant thread, 1 MMA issuer, 2 weight producer)
 // appends up to 256 stamps, each tagged with a small code in the low 8 bits, after the
 // 256 x 16 per-CTA stamps.
+#ifdef MSK_TRACE_DETAIL
 #define MSK_TRD(role, idx, code) do { if (p.trace != nullptr && blockIdx.x == 0 && (idx) < 256) { \
   p.trace[256 * 16 + (role) * 256 + (idx)] = (globaltimer_ns() << 8) | (code); ++(idx); } } while (0)
+#else
+#define MSK_TRD(role, idx, code) do { (void)(idx); } while (0)
+#endif
 
 struct GemmCtrl {
   uint64_t raw_full[6], raw_empty[6], b_full[6], b_empty[6];

@@ -10,6 +10,7 @@
     const int row = (warp & 3) * 32 + lane;
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t a_tmem = tmem + lane_base + C::A_BASE + g * C::A_GROUP_COLS;
+    const uint32_t lut_s = smem_u32(lut);
     uint32_t it = 0;
     int tri = 0;
     bool ok = true;
@@ -48,10 +49,18 @@
                          : "=r"(q[0]), "=r"(q[1]), "=r"(q[2]), "=r"(q[3])
                          : "r"(tile + (chunk * 128 + row) * 16));
             const uint32_t sw = (chunk & 1) ? (sfa[chunk >> 1] >> 16) : sfa[chunk >> 1];
-            const uint32_t s0 = lut[sw & 0xFFu], s1 = lut[(sw >> 8) & 0xFFu];
+#ifdef MSK_EXP_ARITH_SCALE
+            const uint32_t t16 = ((prmt(sw, 0u, 0x4140u) & 0x007F007Fu) << 4) + 0x5C005C00u;
+            const uint32_t s0 = prmt(t16, 0u, 0x1010u), s1 = prmt(t16, 0u, 0x3232u);
+#else
+            const uint32_t s0 = lds32(lut_s + ((sw << 2) & 0x3FCu)), s1 = lds32(lut_s + ((sw >> 6) & 0x3FCu));
+#endif
             uint32_t* oc = o + c * 16;
 #pragma unroll
             for (int w = 0; w < 4; ++w) {
+#ifdef MSK_EXP_NO_ALU
+              oc[4 * w + 0] = q[w]; oc[4 * w + 1] = q[w] ^ s0; oc[4 * w + 2] = q[w] + s1; oc[4 * w + 3] = q[w] | 1u;
+#else
               uint32_t r0, r1, r2, r3;
               decode_codes(q[w], r0, r1, r2, r3);
               const uint32_t s = w < 2 ? s0 : s1;
@@ -59,6 +68,7 @@
               oc[4 * w + 1] = hmul2_bf16(r1, s);
               oc[4 * w + 2] = hmul2_bf16(r2, s);
               oc[4 * w + 3] = hmul2_bf16(r3, s);
+#endif
             }
           }
           if (tid == 256) MSK_TRD(0, tri, 2);
@@ -67,13 +77,7 @@
           if (!mbar_wait(&ctl.a_empty[as], apar ^ 1u, abortw)) { ok = false; break; }
           tc_fence_after();
           if (tid == 256) MSK_TRD(0, tri, 3);
-          {
-            uint32_t lo[16], hi[16];
-#pragma unroll
-            for (int j = 0; j < 16; ++j) { lo[j] = o[j]; hi[j] = o[16 + j]; }
-            tmem_st16(a_tmem + as * 32, lo);
-            tmem_st16(a_tmem + as * 32 + 16, hi);
-          }
+          tmem_st32(a_tmem + as * 32, o);
           pending = true;
           pending_slot = as;
           if (sc == 0 && tid == 256) MSK_TR(TR_FIRST_AFULL);

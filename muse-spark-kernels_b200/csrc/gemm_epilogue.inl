@@ -61,33 +61,33 @@
         if (PHASE == 0) {
           __nv_bfloat16* outp = static_cast<__nv_bfloat16*>(p.outp);
           const int col = ui.pair * 128 + row;
-          for (int c0 = 0; c0 < N; c0 += 16) {
+          for (int c0 = 0; c0 < N; c0 += 8) {
             if (c0 >= ui.rows) break;
-            float ga[16], up[16];
+            float ga[8], up[8];
             if (p.splits > 1) {
 #pragma unroll
-              for (int j = 0; j < 16; ++j) { ga[j] = 0.f; up[j] = 0.f; }
+              for (int j = 0; j < 8; ++j) { ga[j] = 0.f; up[j] = 0.f; }
               for (int s = 0; s < p.splits; ++s) {
                 const float* ps = part0 + s * part_stride;
                 const float4* pg = reinterpret_cast<const float4*>(ps + static_cast<size_t>(row) * N + c0);
                 const float4* pu = reinterpret_cast<const float4*>(ps + (128 + static_cast<size_t>(row)) * N + c0);
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
+                for (int j = 0; j < 2; ++j) {
                   const float4 a = __ldcg(pg + j), b = __ldcg(pu + j);
                   ga[4 * j] += a.x; ga[4 * j + 1] += a.y; ga[4 * j + 2] += a.z; ga[4 * j + 3] += a.w;
                   up[4 * j] += b.x; up[4 * j + 1] += b.y; up[4 * j + 2] += b.z; up[4 * j + 3] += b.w;
                 }
               }
             } else {
-              uint32_t r0[16], r1[16];
-              tmem_ld16(d_tmem + c0, r0);
-              tmem_ld16(d_tmem + N + c0, r1);
+              uint32_t r0[8], r1[8];
+              tmem_ld8(d_tmem + c0, r0);
+              tmem_ld8(d_tmem + N + c0, r1);
               tmem_wait_ld();
 #pragma unroll
-              for (int j = 0; j < 16; ++j) { ga[j] = __uint_as_float(r0[j]); up[j] = __uint_as_float(r1[j]); }
+              for (int j = 0; j < 8; ++j) { ga[j] = __uint_as_float(r0[j]); up[j] = __uint_as_float(r1[j]); }
             }
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
+            for (int j = 0; j < 8; ++j) {
               const int n = c0 + j;
               if (n < ui.rows) {
                 const float v = silu_f(ga[j] * gsc) * (up[j] * gsc);
@@ -102,31 +102,31 @@
             const int col = (2 * ui.pair + t2) * 128 + row;
             float osc = gsc;
             if (p.post_norm_w != nullptr) osc *= 1.0f + __bfloat162float(p.post_norm_w[col]);
-            for (int c0 = 0; c0 < N; c0 += 16) {
+            for (int c0 = 0; c0 < N; c0 += 8) {
               if (c0 >= ui.rows) break;
-              float acc[16];
+              float acc[8];
               if (p.splits > 1) {
 #pragma unroll
-                for (int j = 0; j < 16; ++j) acc[j] = 0.f;
+                for (int j = 0; j < 8; ++j) acc[j] = 0.f;
                 for (int s = 0; s < p.splits; ++s) {
                   const float* ps = part0 + s * part_stride;
                   const float4* pp =
                       reinterpret_cast<const float4*>(ps + (static_cast<size_t>(t2) * 128 + row) * N + c0);
 #pragma unroll
-                  for (int j = 0; j < 4; ++j) {
+                  for (int j = 0; j < 2; ++j) {
                     const float4 a = __ldcg(pp + j);
                     acc[4 * j] += a.x; acc[4 * j + 1] += a.y; acc[4 * j + 2] += a.z; acc[4 * j + 3] += a.w;
                   }
                 }
               } else {
-                uint32_t r[16];
-                tmem_ld16(d_tmem + t2 * N + c0, r);
+                uint32_t r[8];
+                tmem_ld8(d_tmem + t2 * N + c0, r);
                 tmem_wait_ld();
 #pragma unroll
-                for (int j = 0; j < 16; ++j) acc[j] = __uint_as_float(r[j]);
+                for (int j = 0; j < 8; ++j) acc[j] = __uint_as_float(r[j]);
               }
 #pragma unroll
-              for (int j = 0; j < 16; ++j) {
+              for (int j = 0; j < 8; ++j) {
                 const int n = c0 + j;
                 if (n < ui.rows) outp[static_cast<size_t>(ui.row0 + n) * p.out_ld + col] = acc[j] * osc;
               }

@@ -2,15 +2,16 @@
 // Copies the token rows of the unit (x rows through the permutation for PHASE 0, sorted inter
 // rows for PHASE 1) with 16-byte cp.async into the K-major core-matrix layout of the B operand:
 // element (n, k) at (n/8)*B_SBO + (k/8)*B_LBO + (n%8)*16 + (k%8)*2. Eight lanes write one
-// 128-byte core matrix, so shared-memory writes are conflict free. A stage is published one
-// stage late (after the next one is issued), once its copies have landed and a proxy fence
-// has ordered them before the tensor core's reads.
+// 128-byte core matrix, so shared-memory writes are conflict free. A stage is published a few
+// stages late, once its copies have landed and a proxy fence has ordered them before the
+// tensor core's reads.
     const int gt = tid - 64;                    // 0..63
     const int n_sub = gt & 7, c_sub = gt >> 3;  // token within an 8-group, chunk within an 8-chunk group
-    uint32_t it = 0;
+    // A stage is published GLAG stages after it was issued, so the loop never waits for the
+    // copies it has just started (one stage of lag made every iteration a full memory latency).
+    constexpr int GLAG = NST >= 5 ? 3 : (NST >= 4 ? 2 : 1);
+    uint32_t it = 0, signalled = 0;
     bool ok = true;
-    bool pending = false;  // a committed cp.async group whose barrier has not been signalled
-    uint32_t pending_slot = 0;
     const size_t act_ld = static_cast<size_t>(p.K);
     for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
       const UnitInfo ui = decode_unit(u, tile_start, p, N);
@@ -42,19 +43,19 @@
           }
         }
         cp_async_commit();
-        if (pending) {
-          cp_async_wait<1>();
+        if (it + 1 - signalled > GLAG) {
+          cp_async_wait<GLAG>();
           fence_proxy_async_smem();
           __syncwarp();
-          if (lane == 0) mbar_arrive(&ctl.b_full[pending_slot]);
+          if (lane == 0) mbar_arrive(&ctl.b_full[signalled % NST]);
+          ++signalled;
         }
-        pending = true;
-        pending_slot = slot;
       }
     }
-    if (pending) {
+    if (signalled < it) {
       cp_async_wait<0>();
       fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&ctl.b_full[pending_slot]);
+      for (; signalled < it; ++signalled)
+        if (lane == 0) mbar_arrive(&ctl.b_full[signalled % NST]);
     }
