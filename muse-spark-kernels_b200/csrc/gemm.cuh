@@ -185,6 +185,13 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) moe_gemm_kernel(const GemmPar
     tmem_alloc(&ctl.tmem_base, TMEM_COLS);
     tmem_relinquish();
   }
+  // Programmatic dependent launch: everything above ran while the previous kernel was still
+  // draining. PHASE 0 reads the sort tables next, so it waits here. PHASE 1 is launched behind
+  // PHASE 0, which itself only passed this point after the sort had completed, so the tables
+  // are already final: only the activation gather (inter rows) waits, and the weight stream,
+  // dequant and TMEM ring of the down GEMM fill up during the tail of the gate/up GEMM.
+  if (PHASE == 0) pdl_wait();
+  pdl_launch_dependents();
   if (warp == 2) {  // exclusive prefix of per-expert tile counts
     int carry = 0;
     for (int base = 0; base < p.nloc; base += 32) {

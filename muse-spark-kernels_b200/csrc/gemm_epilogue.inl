@@ -5,6 +5,7 @@
     const int row = (warp & 3) * 32 + lane;
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
     uint32_t unit_i = 0, epi_par = 0;
+    if (PHASE == 1) pdl_wait();  // y rows and the tables must not be touched before the previous grid is done
     bool ok = true;
     // bounded barrier over the 128 epilogue threads (a plain bar.sync could not time out)
     auto epi_sync = [&]() -> bool {

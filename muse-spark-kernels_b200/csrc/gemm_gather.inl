@@ -11,6 +11,7 @@
     // copies it has just started (one stage of lag made every iteration a full memory latency).
     constexpr int GLAG = NST >= 5 ? 3 : (NST >= 4 ? 2 : 1);
     uint32_t it = 0, signalled = 0;
+    if (PHASE == 1) pdl_wait();  // inter is written by the gate/up GEMM
     bool ok = true;
     const size_t act_ld = static_cast<size_t>(p.K);
     for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {

@@ -121,6 +121,7 @@ __global__ void __launch_bounds__(COMBINE_THREADS) combine_kernel(const float* _
                                                                   int post_norm, float eps) {
   __shared__ float wsum[COMBINE_THREADS / 32];
   const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  pdl_wait();  // y and inv come from the kernels before this one
   const int n4 = H / 4;  // float4 per row; thread tid owns indices i*256 + tid
   float4 acc[COMBINE_MAX_PER_THREAD / 4];
 #pragma unroll
@@ -266,9 +267,9 @@ static int pick_split(double units, int n_stages, int grid) {
   double best_cost = 1e30;
   for (int s = 1; s <= std::min(n_stages, 8); ++s) {
     const double waves = std::ceil(units * s / grid);
-    // per wave: the K stages of one unit plus its fixed cost (pipeline fill, epilogue), in stage times;
-    // splitting adds the partial round trip and the ticket
-    const double cost = waves * (std::ceil(static_cast<double>(n_stages) / s) + 2.0) + (s > 1 ? 3.0 : 0.0);
+    // per wave: the K stages of one unit plus a switch cost (the epilogue overlaps the next unit), in
+    // stage times; splitting adds the partial stores per unit and one ticket round trip at the end
+    const double cost = waves * (std::ceil(static_cast<double>(n_stages) / s) + 0.5 + (s > 1 ? 0.3 : 0.0)) + (s > 1 ? 2.0 : 0.0);
     if (cost < best_cost - 1e-9) { best_cost = cost; best = s; }
   }
   return best;
@@ -332,10 +333,10 @@ static Carve carve(const MskMoeCfg* c, int T) {
   k.perm = o; o += round_up(R * 4, 256);
   k.inv = o; o += round_up(R * 4, 256);
   const size_t pairs = std::max(c->inter / 128, c->hidden / 256);
-  k.tickets = o; o += round_up(max_tiles(c, T) * pairs * 4, 256);
+  k.tickets = o; o += 2 * round_up(max_tiles(c, T) * pairs * 4, 256);  // one region per GEMM
   k.inter = o; o += round_up(R * c->inter * 2, 256);
   k.y = o; o += round_up(R * c->hidden * 4, 256);
-  k.partial = o; o += round_up(partial_floats(c, T) * 4, 256);
+  k.partial = o; o += 2 * round_up(partial_floats(c, T) * 4, 256);  // one region per GEMM
   k.total = o;
   return k;
 }
@@ -351,8 +352,17 @@ static int launch_gemm(const GemmParams& p, int grid, cudaStream_t st) {
     if (e != cudaSuccess) return static_cast<int>(e);
     attr_set[dev] = true;
   }
-  moe_gemm_kernel<N, PHASE><<<grid, GEMM_THREADS, GemmCfg<N>::SMEM_BYTES, st>>>(p);
-  return static_cast<int>(cudaGetLastError());
+  cudaLaunchConfig_t lc{};
+  lc.gridDim = dim3(static_cast<unsigned>(grid));
+  lc.blockDim = dim3(GEMM_THREADS);
+  lc.dynamicSmemBytes = GemmCfg<N>::SMEM_BYTES;
+  lc.stream = st;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;  // may start while its predecessor drains
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  lc.attrs = at;
+  lc.numAttrs = 1;
+  return static_cast<int>(cudaLaunchKernelEx(&lc, moe_gemm_kernel<N, PHASE>, p));
 }
 
 template <int PHASE>
@@ -483,9 +493,19 @@ static int launch_sort(const MskMoeCfg* cfg, const int32_t* ids, int n_tokens, i
     if (e != cudaSuccess) return static_cast<int>(e);
     attr_set[dev] = true;
   }
-  sort_kernel<<<1, SORT_THREADS, sizeof(SortSmem), st>>>(ids, n_tokens * cfg->top_k, cfg->local_start,
-                                                         cfg->local_count, cnt, off, perm, inv);
-  return static_cast<int>(cudaGetLastError());
+  cudaLaunchConfig_t lc{};
+  lc.gridDim = dim3(1);
+  lc.blockDim = dim3(SORT_THREADS);
+  lc.dynamicSmemBytes = sizeof(SortSmem);
+  lc.stream = st;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  lc.attrs = at;
+  lc.numAttrs = 1;
+  return static_cast<int>(cudaLaunchKernelEx(&lc, sort_kernel, ids, static_cast<int>(n_tokens * cfg->top_k),
+                                             static_cast<int>(cfg->local_start), static_cast<int>(cfg->local_count),
+                                             cnt, off, perm, inv));
 }
 
 int msk_moe_sort(const MskMoeCfg* cfg, const int32_t* topk_ids, int n_tokens, int32_t* cnt, int32_t* off,
@@ -601,6 +621,8 @@ static int forward_impl(const MskMoeCfg* cfg, const void* packed13, const void* 
   if (ev) cudaEventRecord(ev[2], st);
 
   p.w = static_cast<const uint8_t*>(packed2); p.gs = gs2; p.act = inter; p.outp = y;
+  p.partial = partial + round_up(partial_floats(cfg, cfg->max_tokens) * 4, 256) / 4;
+  p.tickets = tickets + round_up(max_tiles(cfg, cfg->max_tokens) * std::max(cfg->inter / 128, cfg->hidden / 256) * 4, 256) / 4;
   if (trace) p.trace = trace + TRACE_WORDS;
   p.post_norm_w = static_cast<const __nv_bfloat16*>(post_norm_w);
   p.K = cfg->inter; p.out_ld = cfg->hidden; p.n_pairs = cfg->hidden / 256; p.splits = plan.s2;
@@ -608,11 +630,24 @@ static int forward_impl(const MskMoeCfg* cfg, const void* packed13, const void* 
   if (e != 0) return e;
   if (ev) cudaEventRecord(ev[3], st);
 
-  combine_kernel<<<static_cast<unsigned>(n_tokens), COMBINE_THREADS, 0, st>>>(
-      y, inv, topk_weights, static_cast<__nv_bfloat16*>(out), cfg->hidden, cfg->top_k, post_norm_w != nullptr ? 1 : 0,
-      cfg->post_norm_eps);
+  {
+    cudaLaunchConfig_t lc{};
+    lc.gridDim = dim3(static_cast<unsigned>(n_tokens));
+    lc.blockDim = dim3(COMBINE_THREADS);
+    lc.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    lc.attrs = at;
+    lc.numAttrs = 1;
+    e = static_cast<int>(cudaLaunchKernelEx(&lc, combine_kernel, static_cast<const float*>(y),
+                                            static_cast<const int32_t*>(inv), topk_weights,
+                                            static_cast<__nv_bfloat16*>(out), static_cast<int>(cfg->hidden),
+                                            static_cast<int>(cfg->top_k), post_norm_w != nullptr ? 1 : 0,
+                                            cfg->post_norm_eps));
+  }
   if (ev) cudaEventRecord(ev[4], st);
-  return static_cast<int>(cudaGetLastError());
+  return e;
 }
 
 int msk_moe_forward(const MskMoeCfg* cfg, const void* packed13, const void* packed2, const float* gs13,

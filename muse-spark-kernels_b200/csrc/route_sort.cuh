@@ -210,6 +210,8 @@ __global__ void __launch_bounds__(SORT_THREADS) sort_kernel(const int32_t* __res
                                                             int32_t* __restrict__ perm, int32_t* __restrict__ inv) {
   extern __shared__ __align__(16) unsigned char sort_smem_raw[];
   SortSmem& sm = *reinterpret_cast<SortSmem*>(sort_smem_raw);
+  asm volatile("griddepcontrol.wait;" ::: "memory");               // topk_ids may come from the kernel before
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // let the GEMM kernel set itself up meanwhile
   sort_entries_block(sm, ids, n, lo, nloc, cnt, off, perm, inv);
 }
 
