@@ -143,6 +143,19 @@ int msk_moe_forward_timed(const MskMoeCfg* cfg, const void* packed13, const void
                           const float* topk_weights, void* out, void* workspace, size_t workspace_bytes,
                           int n_tokens, void* stream, float* host_ms);
 
+/* msk_moe_forward for callers that cannot allocate device memory on the calling path (all
+ * memory handed to their own pool, allocator locked, a latency-critical thread that must not
+ * enter the driver's allocator): the scratch lives in a 6 MiB file-scope device array inside the library, which every
+ * GPU that loads the library holds until the process exits. No counterpart in the reference,
+ * whose scratch is always allocated by prepare(). Limits: n_tokens * top_k <= 128,
+ * hidden <= 8192, inter <= 4096, else MSK_ERR_TOO_LARGE. The first call on a device resolves
+ * the array's address (make it outside stream capture). Every call shares the array, which
+ * keeps the last call's contents; the status word is cleared at the start of each call; calls
+ * that overlap on the GPU race on it. Calls no cudaMalloc/cudaFree or allocating routine. */
+int msk_moe_forward_static(const MskMoeCfg* cfg, const void* packed13, const void* packed2, const float* gs13,
+                           const float* gs2, const void* post_norm_w, const void* x, const int32_t* topk_ids,
+                           const float* topk_weights, void* out, int n_tokens, void* stream);
+
 /* The launch plan msk_moe_forward uses for n_tokens: host_out[4] = token tile N, K splits of the
  * gate/up GEMM, K splits of the down GEMM, persistent grid size. The reference picks its build by
  * token count the same way (muse_moe_w4a16/py/03_kernel_fn.py:33-40). */

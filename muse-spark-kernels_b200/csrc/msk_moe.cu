@@ -686,6 +686,94 @@ int msk_moe_forward_timed(const MskMoeCfg* cfg, const void* packed13, const void
   return MSK_OK;
 }
 
+// ------------------------------------------------------------------------------------------
+// msk_moe_forward_static: the routed-expert step for callers that cannot allocate.
+// Some hosts of this library run where no device allocation may happen on the calling path:
+// a serving loop that has handed all device memory to its own pool, a plug-in called while the
+// application's allocator is locked, a latency-critical thread that must not enter the driver's
+// allocator.
+// msk_moe_forward needs a caller-allocated workspace; this variant keeps its scratch (sort
+// tables, the SwiGLU intermediate and the per-route expert outputs) in one file-scope device
+// array instead. The array is part of the loaded library image: every GPU that loads the
+// library holds MSK_STATIC_WS_BYTES of it until the process exits.
+//  * Limits: n_tokens * top_k <= 128 routed rows, hidden <= 8192, inter <= 4096; anything
+//    larger is refused with MSK_ERR_TOO_LARGE. The GEMMs run without K splits here.
+//  * The first call on each device looks up the array's device address (cudaGetSymbolAddress,
+//    with that device current). Make that first call outside stream capture.
+//  * All calls on a device share the one array and it keeps what the last call left; the status
+//    word is cleared on the stream at the start of every call, the tables are rewritten by the
+//    sort. Two calls that overlap on the GPU (different streams) race on it: serialise them.
+//  * No cudaMalloc, cudaFree or allocating library call is made.
+constexpr size_t MSK_STATIC_WS_BYTES = 6u << 20;
+constexpr int MSK_STATIC_MAX_ROWS = 128;
+static __device__ __align__(256) unsigned char g_static_ws[MSK_STATIC_WS_BYTES];
+
+int msk_moe_forward_static(const MskMoeCfg* cfg, const void* packed13, const void* packed2, const float* gs13,
+                           const float* gs2, const void* post_norm_w, const void* x, const int32_t* topk_ids,
+                           const float* topk_weights, void* out, int n_tokens, void* stream) {
+  const int rc = check_cfg(cfg);
+  if (rc != MSK_OK) return rc;
+  if (!packed13 || !packed2 || !gs13 || !gs2) return MSK_ERR_NULL;
+  if (n_tokens < 0) return MSK_ERR_SHAPE;
+  if (n_tokens == 0) return MSK_OK;
+  if (!x || !topk_ids || !topk_weights || !out) return MSK_ERR_NULL;
+  if (!aligned16(packed13) || !aligned16(packed2) || !aligned16(x) || !aligned16(out)) return MSK_ERR_ALIGN;
+  const size_t R = static_cast<size_t>(n_tokens) * cfg->top_k;
+  if (R > static_cast<size_t>(MSK_STATIC_MAX_ROWS) || cfg->hidden > 8192 || cfg->inter > 4096) return MSK_ERR_TOO_LARGE;
+  // carve: [status 256][cnt][off][perm][inv][inter bf16 R x I][y fp32 R x H]
+  size_t o = 256;
+  const size_t o_cnt = o; o += round_up(static_cast<size_t>(cfg->local_count) * 4, 256);
+  const size_t o_off = o; o += round_up(static_cast<size_t>(cfg->local_count + 1) * 4, 256);
+  const size_t o_perm = o; o += round_up(R * 4, 256);
+  const size_t o_inv = o; o += round_up(R * 4, 256);
+  const size_t o_inter = o; o += round_up(R * cfg->inter * 2, 256);
+  const size_t o_y = o; o += round_up(R * cfg->hidden * 4, 256);
+  if (o > MSK_STATIC_WS_BYTES) return MSK_ERR_TOO_LARGE;
+
+  // device address of the array, once per device (the symbol's host-side name is not an address)
+  static unsigned char* base_of[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return MSK_ERR_RANGE;
+  if (base_of[dev] == nullptr) {
+    void* ptr = nullptr;
+    const cudaError_t ce = cudaGetSymbolAddress(&ptr, g_static_ws);
+    if (ce != cudaSuccess) return static_cast<int>(ce);
+    base_of[dev] = static_cast<unsigned char*>(ptr);
+  }
+  unsigned char* b = base_of[dev];
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  cudaError_t ce = cudaMemsetAsync(b, 0, 256, st);  // status word starts at zero
+  if (ce != cudaSuccess) return static_cast<int>(ce);
+
+  int32_t* cnt = reinterpret_cast<int32_t*>(b + o_cnt);
+  int32_t* off = reinterpret_cast<int32_t*>(b + o_off);
+  int32_t* perm = reinterpret_cast<int32_t*>(b + o_perm);
+  int32_t* inv = reinterpret_cast<int32_t*>(b + o_inv);
+  __nv_bfloat16* inter = reinterpret_cast<__nv_bfloat16*>(b + o_inter);
+  float* y = reinterpret_cast<float*>(b + o_y);
+
+  int e = launch_sort(cfg, topk_ids, n_tokens, cnt, off, perm, inv, st);
+  if (e != 0) return e;
+  GemmParams p{};
+  p.cnt = cnt; p.off = off; p.perm = perm; p.partial = nullptr; p.tickets = nullptr;
+  p.status = reinterpret_cast<int32_t*>(b); p.trace = nullptr;
+  p.nloc = cfg->local_count; p.top_k = cfg->top_k; p.evict_first = 1; p.splits = 1;
+  const int grid = cfg->num_ctas > 0 ? cfg->num_ctas : sm_count();
+  p.w = static_cast<const uint8_t*>(packed13); p.gs = gs13; p.act = x; p.outp = inter; p.post_norm_w = nullptr;
+  p.K = cfg->hidden; p.out_ld = cfg->inter; p.n_pairs = cfg->inter / 128;
+  e = launch_gemm_n<0>(16, p, grid, st);
+  if (e != 0) return e;
+  p.w = static_cast<const uint8_t*>(packed2); p.gs = gs2; p.act = inter; p.outp = y;
+  p.post_norm_w = static_cast<const __nv_bfloat16*>(post_norm_w);
+  p.K = cfg->inter; p.out_ld = cfg->hidden; p.n_pairs = cfg->hidden / 256;
+  e = launch_gemm_n<1>(16, p, grid, st);
+  if (e != 0) return e;
+  combine_kernel<<<static_cast<unsigned>(n_tokens), COMBINE_THREADS, 0, st>>>(
+      y, inv, topk_weights, static_cast<__nv_bfloat16*>(out), cfg->hidden, cfg->top_k, post_norm_w != nullptr ? 1 : 0,
+      cfg->post_norm_eps);
+  return static_cast<int>(cudaGetLastError());
+}
+
 int msk_moe_plan(const MskMoeCfg* cfg, int n_tokens, int* host_out) {
   const int rc = check_cfg(cfg);
   if (rc != MSK_OK) return rc;

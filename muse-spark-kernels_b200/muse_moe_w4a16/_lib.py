@@ -70,6 +70,7 @@ SIGNATURES = {
     "msk_moe_forward": [_CFG, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, ctypes.c_size_t, ctypes.c_int, _P],
     "msk_moe_forward_timed": [_CFG, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, ctypes.c_size_t, ctypes.c_int, _P,
                               ctypes.POINTER(ctypes.c_float)],
+    "msk_moe_forward_static": [_CFG, _P, _P, _P, _P, _P, _P, _P, _P, _P, ctypes.c_int, _P],
     "msk_moe_plan": [_CFG, ctypes.c_int, _INTP],
     "msk_moe_workspace_view": [_CFG, _P, ctypes.c_int, ctypes.POINTER(_P)],
     "msk_moe_read_status": [_P, _INTP, _P],
