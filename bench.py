@@ -304,7 +304,7 @@ def run_gpu(args, spec):
                    "touched_experts_mean": mean_touched},
         "e2e": {"value": T * args.steps / (sum(e2e_ms) * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "ms_per_step": sum(e2e_ms) / args.steps},
-        "gpu_launches": 5 * args.steps,
+        "gpu_launches": (4 if T <= 32 else 5) * args.steps,
         "roofline": roof,
         "step_roofline": {"hbm_frac": step_bytes / (total_ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
                           "tensor_frac": step_flops / (total_ms * 1e-3) / 1e12 / peaks["bf16_tflops_sustained"],

@@ -61,6 +61,7 @@ typedef struct MskMoeCfg {
   int32_t token_tile;    /* MMA N (tokens per tile): 16/32/64/128; 0 = chosen from n_tokens */
   int32_t max_tokens;    /* token capacity the workspace is sized for (msk_moe_forward rejects more) */
   int32_t trace;         /* non-zero: the GEMM kernels stamp %globaltimer per CTA into the workspace (view 6) */
+  int32_t stop_after;    /* measuring aid: 0 = whole step; 1/2/3 = return after sort / gate-up GEMM / down GEMM */
 } MskMoeCfg;
 
 /* ---- prepare-time repack (lossless; replaces the four layouts built by
@@ -133,6 +134,15 @@ int msk_moe_forward(const MskMoeCfg* cfg, const void* packed13, const void* pack
                     const float* gs2, const void* post_norm_w, const void* x, const int32_t* topk_ids,
                     const float* topk_weights, void* out, void* workspace, size_t workspace_bytes, int n_tokens,
                     void* stream);
+
+/* msk_moe_forward with the routing inside: top-k of `logits` (fp32 [T, E]; `bias` as in
+ * msk_moe_route) is written to topk_ids_out / topk_weights_out and used for the step. Up to 32
+ * tokens routing and sort share one launch. This is the call the layer callers' route-then-experts
+ * sequence maps to (muse_decode_layer/py/06_kernel_fn.py:115-149). */
+int msk_moe_forward_logits(const MskMoeCfg* cfg, const void* packed13, const void* packed2, const float* gs13,
+                           const float* gs2, const void* post_norm_w, const void* x, const float* logits,
+                           const float* bias, int32_t* topk_ids_out, float* topk_weights_out, void* out,
+                           void* workspace, size_t workspace_bytes, int n_tokens, void* stream);
 
 /* msk_moe_forward with a CUDA event before and after each of its four launches. Waits for the
  * last one and returns the elapsed milliseconds host_ms[4] = sort, gate/up GEMM, down GEMM,

@@ -12,7 +12,7 @@
 //                or split-K partials;
 //   warps 8-23   dequant (gemm_dequant.inl): 2 tiles x 4 lane quarters x 2 K halves. A thread
 //                owns one weight row of its tile: shared-memory codes -> BF16 (layout.cuh) ->
-//                tcgen05.st into a ring of TMEM A slots (64 K each) the MMA warp consumes.
+//                tcgen05.st into a ring of TMEM A slots (128 K each) the MMA warp consumes.
 // Measured on B200: tcgen05.mma M=128 N=16 K=16 with A in TMEM retires every ~9 cycles, with
 // A in shared memory every ~39; the decode ALU work (~2 instructions per weight) is what has
 // to be spread over all four schedulers, hence sixteen dequant warps.
@@ -54,14 +54,17 @@ struct GemmCfg {
   static constexpr int STAGE_BYTES = 2 * TILE_BYTES + B_STAGE_BYTES;
   static constexpr int NST = N <= 16 ? 5 : (N <= 32 ? 4 : (N <= 64 ? 3 : 2));
   // TMEM: NDBUF accumulator buffers of 2N columns (tile 0 | tile 1) from column 0; above them
-  // the A ring: two groups (tiles) of NSLOT slots, 32 columns (64 K) each.
+  // the A ring: two groups (tiles) of NSLOT slots, 64 columns (128 K = half a stage) each.
   static constexpr int NDBUF = N <= 64 ? 2 : 1;
   static constexpr int A_BASE = N <= 32 ? 128 : 256;
-  static constexpr int NSLOT = N <= 32 ? 6 : 4;
-  static constexpr int A_GROUP_COLS = NSLOT * 32;
+  static constexpr int NSLOT = N <= 32 ? 3 : 2;
+  static constexpr int SLOT_COLS = 64;
+  static constexpr int A_GROUP_COLS = NSLOT * SLOT_COLS;
   static constexpr int LUT_BYTES = 1024;
   static constexpr int CTRL_BYTES = 1024;  // barriers, TMEM base, abort word, tile table header
-  static constexpr int SMEM_BYTES = NST * STAGE_BYTES + LUT_BYTES + CTRL_BYTES + (MAX_LOCAL_EXPERTS + 1) * 4 + 1024;
+  static constexpr int TABLE_INTS = MAX_LOCAL_EXPERTS + 4;  // per table: tile_start, cnt, off copies
+  static constexpr int TABLE_BYTES = 3 * TABLE_INTS * 4;
+  static constexpr int SMEM_BYTES = NST * STAGE_BYTES + LUT_BYTES + CTRL_BYTES + TABLE_BYTES + 1024;
   static_assert(NDBUF * 2 * N <= A_BASE && A_BASE + 2 * A_GROUP_COLS <= TMEM_COLS, "TMEM budget");
 };
 
@@ -121,6 +124,9 @@ struct UnitInfo {
 // unit index -> (token tile, pair, split); the token tile is located in the per-expert
 // exclusive prefix of tile counts by binary search.
 __device__ __forceinline__ UnitInfo decode_unit(int u, const int* tile_start, const GemmParams& p, int N) {
+  // tile_start is followed in shared memory by copies of cnt[] and off[] (GemmCfg::TABLE_INTS apart)
+  const int* cnt_s = tile_start + (MAX_LOCAL_EXPERTS + 4);
+  const int* off_s = cnt_s + (MAX_LOCAL_EXPERTS + 4);
   UnitInfo ui;
   ui.split = u % p.splits;
   const int v = u / p.splits;
@@ -133,8 +139,8 @@ __device__ __forceinline__ UnitInfo decode_unit(int u, const int* tile_start, co
   }
   ui.expert = lo;
   const int local_tile = ui.tile - tile_start[lo];
-  const int c = p.cnt[lo];
-  ui.row0 = p.off[lo] + local_tile * N;
+  const int c = cnt_s[lo];
+  ui.row0 = off_s[lo] + local_tile * N;
   ui.rows = min(N, c - local_tile * N);
   return ui;
 }
@@ -196,7 +202,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) moe_gemm_kernel(const GemmPar
     int carry = 0;
     for (int base = 0; base < p.nloc; base += 32) {
       const int e = base + lane;
-      const int c = e < p.nloc ? (p.cnt[e] + N - 1) / N : 0;
+      const int cn = e < p.nloc ? p.cnt[e] : 0;
+      if (e < p.nloc) tile_start[C::TABLE_INTS + e] = cn;
+      const int c = (cn + N - 1) / N;
       int incl = c;
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
@@ -210,6 +218,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) moe_gemm_kernel(const GemmPar
       tile_start[p.nloc] = carry;
       ctl.n_tiles = carry;
     }
+  }
+  if (warp == 3) {  // off[] copy, in parallel with the scan above
+    for (int e = lane; e <= p.nloc; e += 32) tile_start[2 * C::TABLE_INTS + e] = p.off[e];
   }
   tc_fence_before();
   __syncthreads();

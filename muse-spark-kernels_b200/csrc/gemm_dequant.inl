@@ -1,8 +1,8 @@
 // Role body of moe_gemm_kernel (included inside the kernel): dequant, warps 8-23.
 // Warp = (K half kh, tile g, lane quarter). Thread `row` of a quarter owns one weight row of
-// tile g. Per K stage the warps of half kh fill A slots kh and kh+2 (64 K each): two 16-byte
-// code chunks and four scale bytes -> 2 x 16 BF16x2 registers -> two tcgen05.st, each issued
-// right after its chunk is decoded. A slot is handed to the MMA warp (`retire`) after the
+// tile g. Per K stage the warps of half kh fill one A slot (128 K): four 16-byte code chunks
+// and eight scale bytes -> 4 x 16 BF16x2 registers -> four tcgen05.st, each issued right after
+// its chunk is decoded. A slot is handed to the MMA warp (`retire`) after the
 // first chunk of the following slot has been decoded, so the store latency hides behind it.
     const int didx = warp - 8;
     const int g = (didx >> 2) & 1;
@@ -13,15 +13,7 @@
     const uint32_t lut_s = smem_u32(lut);
     uint32_t it = 0;
     int tri = 0;
-#ifdef MSK_EXP_DQ_CLOCKS
-    long long dk_raw = 0, dk_retire = 0, dk_aempty = 0, dk0 = 0;
-    const long long dk_start = clock64();
-#define DK_BEGIN() dk0 = clock64()
-#define DK_END(acc) acc += clock64() - dk0
-#else
-#define DK_BEGIN()
-#define DK_END(acc)
-#endif
+    uint32_t as = kh, apar = 0;  // ring slot of this warp's next K half and its phase parity
     bool ok = true;
     bool pending = false;      // stores of the previous slot issued, slot not yet handed over
     uint32_t pending_slot = 0;
@@ -37,9 +29,7 @@
       const int ks0 = ui.split * per_split, ks1 = min(nst_total, ks0 + per_split);
       for (int ks = ks0; ks < ks1 && ok; ++ks, ++it) {
         const uint32_t slot = it % NST, par = (it / NST) & 1u;
-        DK_BEGIN();
         if (!mbar_wait(&ctl.raw_full[slot], par, abortw)) { ok = false; break; }
-        DK_END(dk_raw);
         if (it == 0 && tid == 256) MSK_TR(TR_FIRST_RAW);
         if (tid == 256) MSK_TRD(0, tri, 1);
         const uint32_t tile = smem_u32(ring + slot * C::STAGE_BYTES + g * TILE_BYTES);
@@ -48,19 +38,17 @@
         asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
                      : "=r"(sfa[0]), "=r"(sfa[1]), "=r"(sfa[2]), "=r"(sfa[3])
                      : "r"(tile + TILE_CODE_BYTES + row * 16));
+        {
+          // this warp's slot of the stage: K half kh = chunks 4*kh .. 4*kh+3
 #pragma unroll
-        for (int i = 0; i < 2; ++i) {
-          const int sl = 2 * i + kh;             // 64 K per A slot = two 32-K chunks = four scale blocks
-          const uint32_t sc = it * 4u + sl;
-          const uint32_t as = sc % NSLOT, apar = (sc / NSLOT) & 1u;
-#pragma unroll
-          for (int c = 0; c < 2; ++c) {
-            const int chunk = sl * 2 + c;
+          for (int c = 0; c < 4; ++c) {
+            const int chunk = kh * 4 + c;
             uint32_t q[4];
             asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
                          : "=r"(q[0]), "=r"(q[1]), "=r"(q[2]), "=r"(q[3])
                          : "r"(tile_row + chunk * 2048));
-            const uint32_t sw = (chunk & 1) ? (sfa[chunk >> 1] >> 16) : sfa[chunk >> 1];
+            const uint32_t sfw = kh ? (c < 2 ? sfa[2] : sfa[3]) : (c < 2 ? sfa[0] : sfa[1]);
+            const uint32_t sw = (c & 1) ? (sfw >> 16) : sfw;
             const uint32_t s0 = lds32(lut_s + ((sw << 2) & 0x3FCu)), s1 = lds32(lut_s + ((sw >> 6) & 0x3FCu));
             uint32_t o[16];
 #pragma unroll
@@ -75,22 +63,19 @@
             }
             if (c == 0) {
               // hand over the previous slot (its stores had the decode above to land), claim this one
-              if (tid == 256) MSK_TRD(0, tri, 2);
-              DK_BEGIN();
               if (pending) retire();
-              DK_END(dk_retire);
-              DK_BEGIN();
               if (!mbar_wait(&ctl.a_empty[as], apar ^ 1u, abortw)) { ok = false; break; }
               tc_fence_after();
-              DK_END(dk_aempty);
-              if (tid == 256) MSK_TRD(0, tri, 3);
             }
-            tmem_st16(a_tmem + as * 32 + c * 16, o);
+            tmem_st16(a_tmem + as * C::SLOT_COLS + c * 16, o);
           }
           if (!ok) break;
           pending = true;
           pending_slot = as;
-          if (sc == 0 && tid == 256) MSK_TR(TR_FIRST_AFULL);
+          if (it == 0 && tid == 256) MSK_TR(TR_FIRST_AFULL);
+          // the other K half takes the next ring slot; this warp's next one is two further
+          as += 2;
+          if (as >= NSLOT) { as -= NSLOT; apar ^= 1u; }
         }
         if (!ok) break;
         __syncwarp();
@@ -99,9 +84,3 @@
       if (!ok) break;
       if (pending) retire();  // the accumulators need every slot of the unit
     }
-#ifdef MSK_EXP_DQ_CLOCKS
-    if (tid == 256 && p.trace != nullptr) {
-      p.trace[blockIdx.x * 16 + 10] = dk_raw; p.trace[blockIdx.x * 16 + 11] = dk_retire; p.trace[blockIdx.x * 16 + 12] = dk_aempty;
-      p.trace[blockIdx.x * 16 + 13] = clock64() - dk_start; p.trace[blockIdx.x * 16 + 15] = it;
-    }
-#endif

@@ -111,56 +111,80 @@ __global__ void __launch_bounds__(128) dequant_packed_kernel(const uint8_t* pack
 // (muse_moe_w4a16/cuda/moe.cu:2604-2766; muse_decode_layer/py/04_triton_kernels.py:616-632).
 // The block sum of squares is a fixed shuffle tree followed by a fixed-order sum of the
 // eight warp partials, so the result does not depend on scheduling.
-constexpr int COMBINE_THREADS = 256;
-constexpr int COMBINE_MAX_PER_THREAD = 32;  // H <= 8192
+constexpr int COMBINE_THREADS = 512;
+constexpr int COMBINE_MAX_F4 = 4;   // float4 per thread per row: H <= 8192
+constexpr int COMBINE_GROUP = 4;    // slots whose rows are loaded together
 
 __global__ void __launch_bounds__(COMBINE_THREADS) combine_kernel(const float* __restrict__ y,
                                                                   const int32_t* __restrict__ inv,
                                                                   const float* __restrict__ tw,
                                                                   __nv_bfloat16* __restrict__ out, int H, int k,
                                                                   int post_norm, float eps) {
-  __shared__ float wsum[COMBINE_THREADS / 32];
+  __shared__ float wsum[COMBINE_GROUP][COMBINE_THREADS / 32];
   const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   pdl_wait();  // y and inv come from the kernels before this one
-  const int n4 = H / 4;  // float4 per row; thread tid owns indices i*256 + tid
-  float4 acc[COMBINE_MAX_PER_THREAD / 4];
+  const int n4 = H / 4;  // float4 per row; thread tid owns indices i*512 + tid
+  float4 acc[COMBINE_MAX_F4];
 #pragma unroll
-  for (int i = 0; i < COMBINE_MAX_PER_THREAD / 4; ++i) acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-  for (int s = 0; s < k; ++s) {
-    const int q = inv[static_cast<size_t>(t) * k + s];
-    if (q < 0) continue;  // uniform over the block
-    const float4* row = reinterpret_cast<const float4*>(y + static_cast<size_t>(q) * H);
-    float4 v[COMBINE_MAX_PER_THREAD / 4];
-    float ss = 0.f;
+  for (int i = 0; i < COMBINE_MAX_F4; ++i) acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+  // Slots are taken COMBINE_GROUP at a time so that their row loads are in flight together (one
+  // memory latency per group instead of one per slot); the sums still run in slot order.
+  for (int s0 = 0; s0 < k; s0 += COMBINE_GROUP) {
+    int q[COMBINE_GROUP];
+    float wgt[COMBINE_GROUP];
 #pragma unroll
-    for (int i = 0; i < COMBINE_MAX_PER_THREAD / 4; ++i) {
-      if (i * COMBINE_THREADS + tid < n4) {
-        v[i] = row[i * COMBINE_THREADS + tid];
-        ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
+    for (int g = 0; g < COMBINE_GROUP; ++g) {
+      const bool in = s0 + g < k;
+      q[g] = in ? inv[static_cast<size_t>(t) * k + s0 + g] : -1;
+      wgt[g] = in ? tw[static_cast<size_t>(t) * k + s0 + g] : 0.f;
+    }
+    float4 v[COMBINE_GROUP][COMBINE_MAX_F4];
+    float ss[COMBINE_GROUP];
+#pragma unroll
+    for (int g = 0; g < COMBINE_GROUP; ++g) {
+      ss[g] = 0.f;
+      const float4* row = reinterpret_cast<const float4*>(y + static_cast<size_t>(q[g] < 0 ? 0 : q[g]) * H);
+#pragma unroll
+      for (int i = 0; i < COMBINE_MAX_F4; ++i) {
+        v[g][i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (q[g] >= 0 && i * COMBINE_THREADS + tid < n4) v[g][i] = row[i * COMBINE_THREADS + tid];
       }
     }
-    float scale = tw[static_cast<size_t>(t) * k + s];
     if (post_norm) {
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-      __syncthreads();  // wsum of the previous slot fully read
-      if (lane == 0) wsum[warp] = ss;
-      __syncthreads();
-      float tot = 0.f;
+      for (int g = 0; g < COMBINE_GROUP; ++g) {
 #pragma unroll
-      for (int w = 0; w < COMBINE_THREADS / 32; ++w) tot += wsum[w];
-      scale *= rsqrtf(tot / static_cast<float>(H) + eps);
+        for (int i = 0; i < COMBINE_MAX_F4; ++i)
+          ss[g] += v[g][i].x * v[g][i].x + v[g][i].y * v[g][i].y + v[g][i].z * v[g][i].z + v[g][i].w * v[g][i].w;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss[g] += __shfl_xor_sync(0xffffffffu, ss[g], o);
+      }
+      __syncthreads();  // wsum of the previous group fully read
+      if (lane == 0) {
+#pragma unroll
+        for (int g = 0; g < COMBINE_GROUP; ++g) wsum[g][warp] = ss[g];
+      }
+      __syncthreads();
+#pragma unroll
+      for (int g = 0; g < COMBINE_GROUP; ++g) {
+        float tot = 0.f;
+#pragma unroll
+        for (int w = 0; w < COMBINE_THREADS / 32; ++w) tot += wsum[g][w];  // fixed order
+        wgt[g] *= rsqrtf(tot / static_cast<float>(H) + eps);
+      }
     }
 #pragma unroll
-    for (int i = 0; i < COMBINE_MAX_PER_THREAD / 4; ++i) {
-      if (i * COMBINE_THREADS + tid < n4) {
-        acc[i].x += v[i].x * scale; acc[i].y += v[i].y * scale;
-        acc[i].z += v[i].z * scale; acc[i].w += v[i].w * scale;
+    for (int g = 0; g < COMBINE_GROUP; ++g) {  // slot order within the group
+      if (q[g] < 0) continue;
+#pragma unroll
+      for (int i = 0; i < COMBINE_MAX_F4; ++i) {
+        acc[i].x += v[g][i].x * wgt[g]; acc[i].y += v[g][i].y * wgt[g];
+        acc[i].z += v[g][i].z * wgt[g]; acc[i].w += v[g][i].w * wgt[g];
       }
     }
   }
 #pragma unroll
-  for (int i = 0; i < COMBINE_MAX_PER_THREAD / 4; ++i) {
+  for (int i = 0; i < COMBINE_MAX_F4; ++i) {
     if (i * COMBINE_THREADS + tid < n4) {
       __nv_bfloat162 lo = __floats2bfloat162_rn(acc[i].x, acc[i].y);
       __nv_bfloat162 hi = __floats2bfloat162_rn(acc[i].z, acc[i].w);
@@ -228,7 +252,7 @@ static inline size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; 
 static int check_cfg(const MskMoeCfg* c) {
   if (c == nullptr) return MSK_ERR_NULL;
   if (c->hidden <= 0 || c->inter <= 0 || c->hidden % 256 != 0 || c->inter % 256 != 0) return MSK_ERR_SHAPE;
-  if (c->hidden > COMBINE_THREADS * COMBINE_MAX_PER_THREAD) return MSK_ERR_SHAPE;  // combine keeps a row in registers
+  if (c->hidden > COMBINE_THREADS * COMBINE_MAX_F4 * 4) return MSK_ERR_SHAPE;  // combine keeps a row in registers
   if (c->max_tokens < 0) return MSK_ERR_SHAPE;
   if (c->top_k < 1 || c->top_k > MAX_TOP_K) return MSK_ERR_SHAPE;
   if (c->local_count < 1 || c->local_count > MAX_LOCAL_EXPERTS) return MSK_ERR_SHAPE;
@@ -508,6 +532,36 @@ static int launch_sort(const MskMoeCfg* cfg, const int32_t* ids, int n_tokens, i
                                              cnt, off, perm, inv));
 }
 
+constexpr int FUSED_ROUTE_MAX_TOKENS = 32;  // up to here one CTA routes and sorts in a single launch
+
+static int launch_route_sort(const MskMoeCfg* cfg, const float* logits, const float* bias, int32_t* ids, float* tw,
+                             int n_tokens, int32_t* cnt, int32_t* off, int32_t* perm, int32_t* inv, cudaStream_t st) {
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(route_sort_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(sizeof(SortSmem)));
+    if (e != cudaSuccess) return static_cast<int>(e);
+    attr_set[dev] = true;
+  }
+  cudaLaunchConfig_t lc{};
+  lc.gridDim = dim3(1);
+  lc.blockDim = dim3(SORT_THREADS);
+  lc.dynamicSmemBytes = sizeof(SortSmem);
+  lc.stream = st;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  lc.attrs = at;
+  lc.numAttrs = 1;
+  return static_cast<int>(cudaLaunchKernelEx(&lc, route_sort_kernel, logits, bias, ids, tw, n_tokens,
+                                             static_cast<int>(cfg->n_experts), static_cast<int>(cfg->top_k),
+                                             static_cast<int>(cfg->routing_mode), cfg->route_scale,
+                                             static_cast<int>(cfg->local_start), static_cast<int>(cfg->local_count),
+                                             cnt, off, perm, inv));
+}
+
 int msk_moe_sort(const MskMoeCfg* cfg, const int32_t* topk_ids, int n_tokens, int32_t* cnt, int32_t* off,
                  int32_t* perm, int32_t* inv, void* stream) {
   const int rc = check_cfg(cfg);
@@ -562,7 +616,14 @@ int msk_moe_workspace_view(const MskMoeCfg* cfg, void* workspace, int which, voi
 static int forward_impl(const MskMoeCfg* cfg, const void* packed13, const void* packed2, const float* gs13,
                         const float* gs2, const void* post_norm_w, const void* x, const int32_t* topk_ids,
                         const float* topk_weights, void* out, void* workspace, size_t workspace_bytes, int n_tokens,
-                        void* stream, cudaEvent_t* ev) {
+                        void* stream, cudaEvent_t* ev, const float* logits = nullptr, const float* bias = nullptr,
+                        int32_t* ids_out = nullptr, float* tw_out = nullptr) {
+  // with `logits` the routing runs here too: ids_out / tw_out receive it and feed the rest
+  if (logits != nullptr) {
+    if (!ids_out || !tw_out) return MSK_ERR_NULL;
+    topk_ids = ids_out;
+    topk_weights = tw_out;
+  }
   const int rc = check_cfg(cfg);
   if (rc != MSK_OK) return rc;
   if (!packed13 || !packed2 || !gs13 || !gs2 || !workspace) return MSK_ERR_NULL;
@@ -602,9 +663,21 @@ static int forward_impl(const MskMoeCfg* cfg, const void* packed13, const void* 
   }
 
   if (ev) cudaEventRecord(ev[0], st);
-  int e = launch_sort(cfg, topk_ids, n_tokens, cnt, off, perm, inv, st);
+  int e = 0;
+  if (logits != nullptr && n_tokens <= FUSED_ROUTE_MAX_TOKENS) {
+    e = launch_route_sort(cfg, logits, bias, ids_out, tw_out, n_tokens, cnt, off, perm, inv, st);
+  } else {
+    if (logits != nullptr) {
+      route_topk_kernel<<<static_cast<unsigned>((n_tokens + 7) / 8), 256, 0, st>>>(
+          logits, bias, ids_out, tw_out, n_tokens, cfg->n_experts, cfg->top_k, cfg->routing_mode, cfg->route_scale);
+      e = static_cast<int>(cudaGetLastError());
+      if (e != 0) return e;
+    }
+    e = launch_sort(cfg, topk_ids, n_tokens, cnt, off, perm, inv, st);
+  }
   if (e != 0) return e;
   if (ev) cudaEventRecord(ev[1], st);
+  if (cfg->stop_after == 1) return MSK_OK;
 
   GemmParams p{};
   p.cnt = cnt; p.off = off; p.perm = perm; p.partial = partial; p.tickets = tickets; p.status = status;
@@ -619,6 +692,7 @@ static int forward_impl(const MskMoeCfg* cfg, const void* packed13, const void* 
   e = launch_gemm_n<0>(plan.N, p, plan.grid, st);
   if (e != 0) return e;
   if (ev) cudaEventRecord(ev[2], st);
+  if (cfg->stop_after == 2) return MSK_OK;
 
   p.w = static_cast<const uint8_t*>(packed2); p.gs = gs2; p.act = inter; p.outp = y;
   p.partial = partial + round_up(partial_floats(cfg, cfg->max_tokens) * 4, 256) / 4;
@@ -629,6 +703,7 @@ static int forward_impl(const MskMoeCfg* cfg, const void* packed13, const void* 
   e = launch_gemm_n<1>(plan.N, p, plan.grid, st);
   if (e != 0) return e;
   if (ev) cudaEventRecord(ev[3], st);
+  if (cfg->stop_after == 3) return MSK_OK;
 
   {
     cudaLaunchConfig_t lc{};
@@ -656,6 +731,16 @@ int msk_moe_forward(const MskMoeCfg* cfg, const void* packed13, const void* pack
                     void* stream) {
   return forward_impl(cfg, packed13, packed2, gs13, gs2, post_norm_w, x, topk_ids, topk_weights, out, workspace,
                       workspace_bytes, n_tokens, stream, nullptr);
+}
+
+int msk_moe_forward_logits(const MskMoeCfg* cfg, const void* packed13, const void* packed2, const float* gs13,
+                           const float* gs2, const void* post_norm_w, const void* x, const float* logits,
+                           const float* bias, int32_t* topk_ids_out, float* topk_weights_out, void* out,
+                           void* workspace, size_t workspace_bytes, int n_tokens, void* stream) {
+  if (!logits) return MSK_ERR_NULL;
+  if (cfg != nullptr && cfg->top_k > cfg->n_experts) return MSK_ERR_SHAPE;
+  return forward_impl(cfg, packed13, packed2, gs13, gs2, post_norm_w, x, nullptr, nullptr, out, workspace,
+                      workspace_bytes, n_tokens, stream, nullptr, logits, bias, topk_ids_out, topk_weights_out);
 }
 
 int msk_moe_forward_timed(const MskMoeCfg* cfg, const void* packed13, const void* packed2, const float* gs13,

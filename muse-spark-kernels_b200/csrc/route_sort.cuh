@@ -47,17 +47,12 @@ __device__ __forceinline__ uint32_t orderable_u32(float f) {
 // mode 0: score = logit, weights = softmax over the k selected logits.
 // mode 1: s = sigmoid(logit * scale), score = s + bias, weights = s / (sum s + 1e-15)
 //         (muse_decode_layer/py/04_triton_kernels.py:541-552).
-__global__ void __launch_bounds__(256) route_topk_kernel(const float* __restrict__ logits,
-                                                         const float* __restrict__ bias, int32_t* __restrict__ ids,
-                                                         float* __restrict__ wts, int T, int E, int k, int mode,
-                                                         float scale) {
-  const int t = blockIdx.x * 8 + (threadIdx.x >> 5);
-  const int lane = threadIdx.x & 31;
-  if (t >= T) return;
-  constexpr int PER = MAX_EXPERTS / 32;
+template <int PER>
+__device__ __forceinline__ void route_one_token(const float* __restrict__ row, const float* __restrict__ bias,
+                                                int32_t* __restrict__ ids_row, float* __restrict__ wts_row, int E, int k,
+                                                int mode, float scale, int lane) {
   uint64_t key[PER];
   float raw[PER];  // the value the weight is formed from (logit or sigmoid score)
-  const float* row = logits + static_cast<size_t>(t) * E;
 #pragma unroll
   for (int i = 0; i < PER; ++i) {
     const int e = i * 32 + lane;
@@ -117,9 +112,27 @@ __global__ void __launch_bounds__(256) route_topk_kernel(const float* __restrict
     w = my_val / (sum + 1e-15f);
   }
   if (lane < k) {
-    ids[static_cast<size_t>(t) * k + lane] = my_id;
-    wts[static_cast<size_t>(t) * k + lane] = w;
+    ids_row[lane] = my_id;
+    wts_row[lane] = w;
   }
+}
+
+__device__ __forceinline__ void route_token_dispatch(const float* row, const float* bias, int32_t* ids_row,
+                                                     float* wts_row, int E, int k, int mode, float scale, int lane) {
+  if (E <= 128) route_one_token<4>(row, bias, ids_row, wts_row, E, k, mode, scale, lane);
+  else if (E <= 256) route_one_token<8>(row, bias, ids_row, wts_row, E, k, mode, scale, lane);
+  else route_one_token<MAX_EXPERTS / 32>(row, bias, ids_row, wts_row, E, k, mode, scale, lane);
+}
+
+__global__ void __launch_bounds__(256) route_topk_kernel(const float* __restrict__ logits,
+                                                         const float* __restrict__ bias, int32_t* __restrict__ ids,
+                                                         float* __restrict__ wts, int T, int E, int k, int mode,
+                                                         float scale) {
+  const int t = blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (t >= T) return;
+  route_token_dispatch(logits + static_cast<size_t>(t) * E, bias, ids + static_cast<size_t>(t) * k,
+                       wts + static_cast<size_t>(t) * k, E, k, mode, scale, lane);
 }
 
 // -------------------------------------------------------------------- sort
@@ -140,7 +153,9 @@ __device__ __forceinline__ int local_expert(int id, int lo, int nloc) {
   return (id >= 0 && l >= 0 && l < nloc) ? l : -1;
 }
 
-__device__ void sort_entries_block(SortSmem& sm, const int32_t* __restrict__ ids, int n, int lo, int nloc,
+// `ids` is deliberately not __restrict__: the fused kernel writes the ids in the same launch, so
+// the loads must stay ordinary coherent loads.
+__device__ void sort_entries_block(SortSmem& sm, const int32_t* ids, int n, int lo, int nloc,
                                    int32_t* __restrict__ cnt, int32_t* __restrict__ off, int32_t* __restrict__ perm,
                                    int32_t* __restrict__ inv) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -213,6 +228,27 @@ __global__ void __launch_bounds__(SORT_THREADS) sort_kernel(const int32_t* __res
   asm volatile("griddepcontrol.wait;" ::: "memory");               // topk_ids may come from the kernel before
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // let the GEMM kernel set itself up meanwhile
   sort_entries_block(sm, ids, n, lo, nloc, cnt, off, perm, inv);
+}
+
+// Routing and sort in one launch for small token counts: every warp routes the tokens
+// t = warp, warp + 32, ...; after a block barrier the same CTA sorts the entries it just wrote.
+__global__ void __launch_bounds__(SORT_THREADS) route_sort_kernel(const float* __restrict__ logits,
+                                                                  const float* __restrict__ bias,
+                                                                  int32_t* __restrict__ ids, float* __restrict__ wts,
+                                                                  int T, int E, int k, int mode, float scale, int lo,
+                                                                  int nloc, int32_t* __restrict__ cnt,
+                                                                  int32_t* __restrict__ off, int32_t* __restrict__ perm,
+                                                                  int32_t* __restrict__ inv) {
+  extern __shared__ __align__(16) unsigned char sort_smem_raw[];
+  SortSmem& sm = *reinterpret_cast<SortSmem*>(sort_smem_raw);
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int t = warp; t < T; t += SORT_WARPS)
+    route_token_dispatch(logits + static_cast<size_t>(t) * E, bias, ids + static_cast<size_t>(t) * k,
+                         wts + static_cast<size_t>(t) * k, E, k, mode, scale, lane);
+  __syncthreads();  // the ids written above are read back below by other threads of this CTA
+  sort_entries_block(sm, ids, T * k, lo, nloc, cnt, off, perm, inv);
 }
 
 }  // namespace msk

@@ -36,7 +36,7 @@ def _stream():
 
 def prepare(weights, *, local_start=0, n_experts=None, top_k=8, max_tokens=8192, routing_mode="softmax_topk",
             route_scale=0.1767766952966369, post_norm_eps=1e-8, num_ctas=0, split_k13=0, split_k2=0, token_tile=0,
-            trace=0):
+            trace=0, stop_after=0):
     """Repack the NVFP4 weights into the tile layout the GEMM kernel streams (bit and byte
     permutations only, never requantised) and allocate the workspace. Returns `state`."""
     w13 = _u8(weights["w13"])
@@ -55,7 +55,7 @@ def prepare(weights, *, local_start=0, n_experts=None, top_k=8, max_tokens=8192,
     cfg = MskMoeCfg(hidden=H, inter=I, n_experts=n_experts or n_local, local_start=local_start,
                     local_count=n_local, top_k=top_k, routing_mode=_MODES[routing_mode], route_scale=route_scale,
                     post_norm_eps=post_norm_eps, num_ctas=num_ctas, split_k13=split_k13, split_k2=split_k2,
-                    token_tile=token_tile, max_tokens=max_tokens, trace=trace)
+                    token_tile=token_tile, max_tokens=max_tokens, trace=trace, stop_after=stop_after)
     b13, b2 = ctypes.c_size_t(), ctypes.c_size_t()
     _lib.check(lib.msk_moe_packed_bytes(ctypes.byref(cfg), ctypes.byref(b13), ctypes.byref(b2)), "msk_moe_packed_bytes")
     with torch.cuda.device(dev):
@@ -84,12 +84,12 @@ def prepare(weights, *, local_start=0, n_experts=None, top_k=8, max_tokens=8192,
     return state
 
 
-def _route(data, state, x, T):
+def _logits(data, state, x, T):
+    """Router logits of this call: given, or x @ router^T computed by the library; None when the
+    caller supplies ids and weights."""
     cfg, lib = state["cfg"], state["lib"].lib
-    if "topk_ids" in data and data["topk_ids"] is not None:
-        ids = data["topk_ids"].to(torch.int32).contiguous()
-        tw = data["topk_weights"].to(torch.float32).contiguous()
-        return ids, tw
+    if data.get("topk_ids") is not None:
+        return None
     logits = data.get("router_logits")
     if logits is None:
         if state["router"] is None:
@@ -97,7 +97,15 @@ def _route(data, state, x, T):
         logits = torch.empty((T, cfg.n_experts), dtype=torch.float32, device=x.device)
         _lib.check(lib.msk_moe_router_logits(ctypes.byref(cfg), _lib.ptr(x), _lib.ptr(state["router"]),
                                              _lib.ptr(logits), T, _stream()), "msk_moe_router_logits")
-    logits = logits.to(torch.float32).contiguous()
+    return logits.to(torch.float32).contiguous()
+
+
+def _route(data, state, x, T):
+    """ids and weights as separate launches (used by the measuring entry point)."""
+    cfg, lib = state["cfg"], state["lib"].lib
+    logits = _logits(data, state, x, T)
+    if logits is None:
+        return data["topk_ids"].to(torch.int32).contiguous(), data["topk_weights"].to(torch.float32).contiguous()
     ids = torch.empty((T, cfg.top_k), dtype=torch.int32, device=x.device)
     tw = torch.empty((T, cfg.top_k), dtype=torch.float32, device=x.device)
     _lib.check(lib.msk_moe_route(ctypes.byref(cfg), _lib.ptr(logits), _lib.ptr(state["route_bias"]), _lib.ptr(ids),
@@ -115,13 +123,25 @@ def kernel_fn(data, state, return_routing=False):
     dcfg = data.get("config")
     if dcfg is not None and (dcfg["local_start"] != state["lo"] or dcfg["local_count"] != state["cnt"]):
         raise RuntimeError("muse_moe_w4a16.kernel_fn: config local range differs from the prepared state")
-    ids, tw = _route(data, state, x, T)
     out = torch.empty((T, cfg.hidden), dtype=torch.bfloat16, device=x.device)
-    _lib.check(lib.msk_moe_forward(ctypes.byref(cfg), _lib.ptr(state["packed13"]), _lib.ptr(state["packed2"]),
-                                   _lib.ptr(state["gs13"]), _lib.ptr(state["gs2"]), _lib.ptr(state["post_norm_w"]),
-                                   _lib.ptr(x), _lib.ptr(ids), _lib.ptr(tw), _lib.ptr(out),
-                                   _lib.ptr(state["workspace"]), state["workspace_bytes"], T, _stream()),
-               "msk_moe_forward")
+    logits = _logits(data, state, x, T)
+    if logits is None:
+        ids = data["topk_ids"].to(torch.int32).contiguous()
+        tw = data["topk_weights"].to(torch.float32).contiguous()
+        _lib.check(lib.msk_moe_forward(ctypes.byref(cfg), _lib.ptr(state["packed13"]), _lib.ptr(state["packed2"]),
+                                       _lib.ptr(state["gs13"]), _lib.ptr(state["gs2"]), _lib.ptr(state["post_norm_w"]),
+                                       _lib.ptr(x), _lib.ptr(ids), _lib.ptr(tw), _lib.ptr(out),
+                                       _lib.ptr(state["workspace"]), state["workspace_bytes"], T, _stream()),
+                   "msk_moe_forward")
+    else:
+        ids = torch.empty((T, cfg.top_k), dtype=torch.int32, device=x.device)
+        tw = torch.empty((T, cfg.top_k), dtype=torch.float32, device=x.device)
+        _lib.check(lib.msk_moe_forward_logits(ctypes.byref(cfg), _lib.ptr(state["packed13"]), _lib.ptr(state["packed2"]),
+                                              _lib.ptr(state["gs13"]), _lib.ptr(state["gs2"]),
+                                              _lib.ptr(state["post_norm_w"]), _lib.ptr(x), _lib.ptr(logits),
+                                              _lib.ptr(state["route_bias"]), _lib.ptr(ids), _lib.ptr(tw), _lib.ptr(out),
+                                              _lib.ptr(state["workspace"]), state["workspace_bytes"], T, _stream()),
+                   "msk_moe_forward_logits")
     if return_routing:
         return out, ids, tw
     return out

@@ -42,6 +42,7 @@ class MskMoeCfg(ctypes.Structure):
         ("token_tile", ctypes.c_int32),
         ("max_tokens", ctypes.c_int32),
         ("trace", ctypes.c_int32),
+        ("stop_after", ctypes.c_int32),
     ]
 
     def __deepcopy__(self, memo):
@@ -68,6 +69,7 @@ SIGNATURES = {
     "msk_moe_workspace_bytes": [_CFG, _SZP],
     "msk_moe_workspace_init": [_CFG, _P, ctypes.c_size_t, _P],
     "msk_moe_forward": [_CFG, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, ctypes.c_size_t, ctypes.c_int, _P],
+    "msk_moe_forward_logits": [_CFG, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, ctypes.c_size_t, ctypes.c_int, _P],
     "msk_moe_forward_timed": [_CFG, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, ctypes.c_size_t, ctypes.c_int, _P,
                               ctypes.POINTER(ctypes.c_float)],
     "msk_moe_forward_static": [_CFG, _P, _P, _P, _P, _P, _P, _P, _P, _P, ctypes.c_int, _P],
