@@ -32,6 +32,7 @@
 #pragma once
 #include <cstdint>
 #include <cuda_bf16.h>
+#include <cuda.h>
 #include <cuda_runtime.h>
 
 #include "layout.cuh"
@@ -60,6 +61,10 @@ struct GemmCfg {
   static constexpr int NSLOT = N <= 32 ? 3 : 2;
   static constexpr int SLOT_COLS = 64;
   static constexpr int A_GROUP_COLS = NSLOT * SLOT_COLS;
+  // Token tiles of 64 and more fetch the activation operand with TMA (2-D boxes of 64 K x N rows,
+  // 128-byte swizzle) from rows that are contiguous in sorted order; narrower tiles gather rows
+  // through the permutation with cp.async (gemm_gather.inl).
+  static constexpr bool TMA_B = N >= 64;
   static constexpr int LUT_BYTES = 1024;
   static constexpr int CTRL_BYTES = 1024;  // barriers, TMEM base, abort word, tile table header
   static constexpr int TABLE_INTS = MAX_LOCAL_EXPERTS + 4;  // per table: tile_start, cnt, off copies
@@ -69,6 +74,7 @@ struct GemmCfg {
 };
 
 struct GemmParams {
+  CUtensorMap tmap_act;      // TMA_B only: [rows, K] bf16, box 64 x N, 128-byte swizzle (64-byte aligned: first member)
   const uint8_t* w;          // packed tiles of this GEMM
   const float* gs;           // [local_count] global scales
   const void* act;           // PHASE 0: x bf16 [T, H]; PHASE 1: inter bf16 [R, I]
@@ -148,7 +154,7 @@ __device__ __forceinline__ UnitInfo decode_unit(int u, const int* tile_start, co
 __device__ __forceinline__ float silu_f(float g) { return g / (1.0f + __expf(-g)); }
 
 template <int N, int PHASE>
-__global__ void __launch_bounds__(GEMM_THREADS, 1) moe_gemm_kernel(const GemmParams p) {
+__global__ void __launch_bounds__(GEMM_THREADS, 1) moe_gemm_kernel(const __grid_constant__ GemmParams p) {
   using C = GemmCfg<N>;
   constexpr int NST = C::NST;
   constexpr int NSLOT = C::NSLOT;
@@ -169,7 +175,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) moe_gemm_kernel(const GemmPar
     for (int i = 0; i < NST; ++i) {
       mbar_init(&ctl.raw_full[i], 1);
       mbar_init(&ctl.raw_empty[i], 16);
-      mbar_init(&ctl.b_full[i], 2);
+      mbar_init(&ctl.b_full[i], C::TMA_B ? 1 : 2);
       mbar_init(&ctl.b_empty[i], 1);
     }
     for (int i = 0; i < NSLOT; ++i) {

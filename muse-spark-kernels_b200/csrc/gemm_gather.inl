@@ -5,12 +5,14 @@
 // 128-byte core matrix, so shared-memory writes are conflict free. A stage is published a few
 // stages late, once its copies have landed and a proxy fence has ordered them before the
 // tensor core's reads.
+    if (!C::TMA_B) {
     const int gt = tid - 64;                    // 0..63
     const int n_sub = gt & 7, c_sub = gt >> 3;  // token within an 8-group, chunk within an 8-chunk group
     // A stage is published GLAG stages after it was issued, so the loop never waits for the
     // copies it has just started (one stage of lag made every iteration a full memory latency).
     constexpr int GLAG = NST >= 5 ? 3 : (NST >= 4 ? 2 : 1);
     uint32_t it = 0, signalled = 0;
+    const uint64_t keep = policy_evict_last();  // token rows are re-read by every pair of the expert
     if (PHASE == 1) pdl_wait();  // inter is written by the gate/up GEMM
     bool ok = true;
     const size_t act_ld = static_cast<size_t>(p.K);
@@ -40,7 +42,7 @@
 #pragma unroll
           for (int cg = 0; cg < 4; ++cg) {
             const int chunk = cg * 8 + c_sub;
-            cp_async16(dstB + ng * B_SBO + chunk * B_LBO + n_sub * 16, s + chunk * 8, valid);
+            cp_async16_hint(dstB + ng * B_SBO + chunk * B_LBO + n_sub * 16, s + chunk * 8, valid, keep);
           }
         }
         cp_async_commit();
@@ -59,4 +61,5 @@
       __syncwarp();
       for (; signalled < it; ++signalled)
         if (lane == 0) mbar_arrive(&ctl.b_full[signalled % NST]);
+    }
     }

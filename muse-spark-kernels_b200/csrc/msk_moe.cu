@@ -104,6 +104,24 @@ __global__ void __launch_bounds__(128) dequant_packed_kernel(const uint8_t* pack
   }
 }
 
+// ------------------------------------------------------------- row gather
+// xs[q, :] = x[perm[q] / top_k, :] for the routed rows q < off[nloc]: token rows in sorted
+// (expert-major) order, so that wide token tiles can be fetched as plain 2-D TMA boxes. The
+// reference's prefill path gathers rows into per-expert tiles the same way
+// (muse_prefill_layer/cuda/prefill.cu:1446-1608), there fused with its pre-expert norm.
+__global__ void __launch_bounds__(256) gather_rows_kernel(const __nv_bfloat16* __restrict__ x,
+                                                          const int32_t* __restrict__ perm,
+                                                          const int32_t* __restrict__ off, int nloc, int top_k, int H,
+                                                          __nv_bfloat16* __restrict__ xs) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int q = blockIdx.x;
+  if (q >= off[nloc]) return;
+  const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<size_t>(perm[q] / top_k) * H);
+  uint4* dst = reinterpret_cast<uint4*>(xs + static_cast<size_t>(q) * H);
+  for (int i = threadIdx.x; i < H / 8; i += 256) dst[i] = src[i];
+}
+
 // ---------------------------------------------------------------- combine
 // One block per token: out[t] = bf16( sum over slots in index order of
 // w[t,s] * norm_s * y[inv[t,s]] ), norm_s = rsqrt(mean(y^2) + eps) when the post-expert
@@ -318,7 +336,7 @@ static Plan make_plan(const MskMoeCfg* c, int T) {
 
 // Workspace carving. Everything is sized for max_tokens with the worst plan.
 struct Carve {
-  size_t status, trace, cnt, off, perm, inv, tickets, inter, y, partial, total;
+  size_t status, trace, cnt, off, perm, inv, tickets, inter, y, partial, xs, total;
 };
 constexpr size_t MAX_SPLIT = 8;
 constexpr size_t TRACE_CTAS = 256;
@@ -361,8 +379,34 @@ static Carve carve(const MskMoeCfg* c, int T) {
   k.inter = o; o += round_up(R * c->inter * 2, 256);
   k.y = o; o += round_up(R * c->hidden * 4, 256);
   k.partial = o; o += 2 * round_up(partial_floats(c, T) * 4, 256);  // one region per GEMM
+  k.xs = o; o += round_up(R * c->hidden * 2, 256);  // sorted copy of the token rows (wide token tiles only)
   k.total = o;
   return k;
+}
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point lookup (no link against libcuda).
+typedef CUresult (*TensorMapEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                      const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                      CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static int encode_act_map(CUtensorMap* map, const void* base, size_t rows, int K, int box_rows) {
+  static TensorMapEncodeFn fn = nullptr;
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    const cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    if (qres != cudaDriverEntryPointSuccess || ptr == nullptr) return static_cast<int>(cudaErrorNotSupported);
+    fn = reinterpret_cast<TensorMapEncodeFn>(ptr);
+  }
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(K) * 2};
+  const cuuint32_t box[2] = {64u, static_cast<cuuint32_t>(box_rows)};
+  const cuuint32_t estr[2] = {1u, 1u};
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : static_cast<int>(cudaErrorInvalidValue);
 }
 
 template <int N, int PHASE>
@@ -647,6 +691,7 @@ static int forward_impl(const MskMoeCfg* cfg, const void* packed13, const void* 
   __nv_bfloat16* inter = reinterpret_cast<__nv_bfloat16*>(b + k.inter);
   float* y = reinterpret_cast<float*>(b + k.y);
   float* partial = reinterpret_cast<float*>(b + k.partial);
+  __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(b + k.xs);
 
   Plan plan = make_plan(cfg, n_tokens);
   if (plan.N != 16 && plan.N != 32 && plan.N != 64 && plan.N != 128) return MSK_ERR_SHAPE;
@@ -685,10 +730,34 @@ static int forward_impl(const MskMoeCfg* cfg, const void* packed13, const void* 
   unsigned long long* trace = (cfg->trace != 0 && plan.grid <= static_cast<int>(TRACE_CTAS))
                                   ? reinterpret_cast<unsigned long long*>(b + k.trace) : nullptr;
   p.trace = trace;
-  p.evict_first = plan.N <= 64 ? 1 : 0;
+  // weights stream through L2 once per token tile; the activation rows are what many CTAs re-read,
+  // so the weights must not be the ones L2 keeps
+  p.evict_first = 1;
 
+  const bool tma_b = plan.N >= 64;  // GemmCfg<N>::TMA_B
+  const size_t r_max = static_cast<size_t>(cfg->max_tokens) * cfg->top_k;
   p.w = static_cast<const uint8_t*>(packed13); p.gs = gs13; p.act = x; p.outp = inter; p.post_norm_w = nullptr;
   p.K = cfg->hidden; p.out_ld = cfg->inter; p.n_pairs = cfg->inter / 128; p.splits = plan.s13;
+  if (tma_b) {
+    // sorted copy of the token rows, then the activation operand is a plain 2-D tensor for TMA
+    cudaLaunchConfig_t lc{};
+    lc.gridDim = dim3(static_cast<unsigned>(n_tokens * cfg->top_k));
+    lc.blockDim = dim3(256);
+    lc.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    lc.attrs = at;
+    lc.numAttrs = 1;
+    e = static_cast<int>(cudaLaunchKernelEx(&lc, gather_rows_kernel, static_cast<const __nv_bfloat16*>(x),
+                                            static_cast<const int32_t*>(perm), static_cast<const int32_t*>(off),
+                                            static_cast<int>(cfg->local_count), static_cast<int>(cfg->top_k),
+                                            static_cast<int>(cfg->hidden), xs));
+    if (e != 0) return e;
+    p.act = xs;
+    e = encode_act_map(&p.tmap_act, xs, r_max, cfg->hidden, plan.N);
+    if (e != 0) return e;
+  }
   e = launch_gemm_n<0>(plan.N, p, plan.grid, st);
   if (e != 0) return e;
   if (ev) cudaEventRecord(ev[2], st);
@@ -700,6 +769,10 @@ static int forward_impl(const MskMoeCfg* cfg, const void* packed13, const void* 
   if (trace) p.trace = trace + TRACE_WORDS;
   p.post_norm_w = static_cast<const __nv_bfloat16*>(post_norm_w);
   p.K = cfg->inter; p.out_ld = cfg->hidden; p.n_pairs = cfg->hidden / 256; p.splits = plan.s2;
+  if (tma_b) {
+    e = encode_act_map(&p.tmap_act, inter, r_max, cfg->inter, plan.N);
+    if (e != 0) return e;
+  }
   e = launch_gemm_n<1>(plan.N, p, plan.grid, st);
   if (e != 0) return e;
   if (ev) cudaEventRecord(ev[3], st);

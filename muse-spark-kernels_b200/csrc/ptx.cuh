@@ -132,6 +132,17 @@ __device__ __forceinline__ void bulk_g2s_nohint(void* smem_dst, const void* gmem
                "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar))
                : "memory");
 }
+// 2-D tiled TMA load (no multicast): box of the tensor map at element coordinates (c0 inner,
+// c1 outer) -> this CTA's shared memory, completing on `bar`. c0 * element size must be a
+// multiple of 16 bytes.
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const void* tmap, int c0, int c1, uint64_t* bar,
+                                            uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint "
+      "[%0], [%1, {%2, %3}], [%4], %5;" ::"r"(smem_u32(smem_dst)),
+      "l"(tmap), "r"(c0), "r"(c1), "r"(smem_u32(bar)), "l"(policy)
+      : "memory");
+}
 __device__ __forceinline__ void prefetch_l2(const void* gmem, uint32_t bytes) {
   asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(gmem), "r"(bytes) : "memory");
 }
@@ -141,6 +152,12 @@ __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src,
   // src-size 0 zero-fills the 16 destination bytes (used for padding rows).
   const uint32_t sz = valid ? 16u : 0u;
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(smem_dst)), "l"(gmem_src), "r"(sz)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async16_hint(void* smem_dst, const void* gmem_src, bool valid, uint64_t policy) {
+  const uint32_t sz = valid ? 16u : 0u;
+  asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2, %3;" ::"r"(smem_u32(smem_dst)),
+               "l"(gmem_src), "r"(sz), "l"(policy)
                : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
@@ -184,6 +201,19 @@ __device__ __forceinline__ uint64_t smem_desc_kmajor_noswz(uint32_t saddr, uint3
   d |= static_cast<uint64_t>((sbo >> 4) & 0x3FFFu) << 32;
   d |= 1ull << 46;  // descriptor version for sm_100
   return d;         // layout type 0 = no swizzle, base offset 0
+}
+
+// Shared-memory matrix descriptor, K-major, 128-byte swizzle: rows of 128 bytes (64 BF16),
+// 8-row groups 1024 bytes apart, as written by a TMA load with CU_TENSOR_MAP_SWIZZLE_128B.
+// The tile base must be 1024-byte aligned; a K step of 16 elements advances saddr by 32 bytes.
+__device__ __forceinline__ uint64_t smem_desc_kmajor_sw128(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>(1) << 16;          // leading byte offset: unused with swizzled K-major
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;  // stride byte offset between 8-row groups
+  d |= 1ull << 46;                              // descriptor version for sm_100
+  d |= 2ull << 61;                              // layout type: 128-byte swizzle
+  return d;
 }
 
 // Instruction descriptor for kind::f16: D = FP32, A/B = F16 (0) or BF16 (1), both K-major.
