@@ -9,7 +9,8 @@
 //   warps 2-3    activation gather: cp.async of the token rows of the tile (through the
 //                permutation for the gate/up GEMM) into the K-major core-matrix layout;
 //   warps 4-7    epilogue (gemm_epilogue.inl): TMEM accumulators -> SwiGLU / scale -> global,
-//                or split-K partials;
+//                or split-K partials (token tiles up to 64; for 128 the accumulators are single-
+//                buffered and the sixteen dequant warps, idle by then, share the epilogue);
 //   warps 8-23   dequant (gemm_dequant.inl): 2 tiles x 4 lane quarters x 2 K halves. A thread
 //                owns one weight row of its tile: shared-memory codes -> BF16 (layout.cuh) ->
 //                tcgen05.st into a ring of TMEM A slots (128 K each) the MMA warp consumes.
@@ -153,6 +154,47 @@ __device__ __forceinline__ UnitInfo decode_unit(int u, const int* tile_start, co
 
 __device__ __forceinline__ float silu_f(float g) { return g / (1.0f + __expf(-g)); }
 
+// Epilogue of a unit without K splits for the thread that owns TMEM lane `row`: columns
+// [c_beg, c_end) of the accumulators at d_tmem (lane base included). PHASE 0 reads gate (tile 0)
+// and up (tile 1) and writes bf16(silu(g) * u) into inter; PHASE 1 writes the rows of `tile`
+// scaled by gs (and 1 + post_norm_w) into y.
+template <int N, int PHASE>
+__device__ __forceinline__ void epilogue_columns(const GemmParams& p, const UnitInfo& ui, uint32_t d_tmem, int row,
+                                                 int c_beg, int c_end, int tile) {
+  const float gsc = p.gs[ui.expert] * TWO_POW_62;
+  if (PHASE == 0) {
+    __nv_bfloat16* outp = static_cast<__nv_bfloat16*>(p.outp) + static_cast<size_t>(ui.row0) * p.out_ld + ui.pair * 128 + row;
+    for (int c0 = c_beg; c0 < c_end; c0 += 16) {
+      if (c0 >= ui.rows) break;
+      uint32_t r0[16], r1[16];
+      tmem_ld16(d_tmem + c0, r0);
+      tmem_ld16(d_tmem + N + c0, r1);
+      tmem_wait_ld();
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        if (c0 + j < ui.rows) {
+          const float v = silu_f(__uint_as_float(r0[j]) * gsc) * (__uint_as_float(r1[j]) * gsc);
+          outp[static_cast<size_t>(c0 + j) * p.out_ld] = __float2bfloat16_rn(v);
+        }
+      }
+    }
+  } else {
+    const int col = (2 * ui.pair + tile) * 128 + row;
+    float osc = gsc;
+    if (p.post_norm_w != nullptr) osc *= 1.0f + __bfloat162float(p.post_norm_w[col]);
+    float* outp = static_cast<float*>(p.outp) + static_cast<size_t>(ui.row0) * p.out_ld + col;
+    for (int c0 = c_beg; c0 < c_end; c0 += 32) {
+      if (c0 >= ui.rows) break;
+      uint32_t r[32];
+      tmem_ld32(d_tmem + tile * N + c0, r);
+      tmem_wait_ld();
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (c0 + j < ui.rows) outp[static_cast<size_t>(c0 + j) * p.out_ld] = __uint_as_float(r[j]) * osc;
+    }
+  }
+}
+
 template <int N, int PHASE>
 __global__ void __launch_bounds__(GEMM_THREADS, 1) moe_gemm_kernel(const __grid_constant__ GemmParams p) {
   using C = GemmCfg<N>;
@@ -185,7 +227,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) moe_gemm_kernel(const __grid_
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&ctl.d_full[i], 1);
-      mbar_init(&ctl.d_empty[i], 4);
+      mbar_init(&ctl.d_empty[i], C::NDBUF == 1 ? 16 : 4);  // single buffer: the dequant warps run the epilogue
     }
     mbar_init(&ctl.epi_bar, 128);
     ctl.abort_word = 0;

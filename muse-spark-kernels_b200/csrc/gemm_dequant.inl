@@ -24,7 +24,8 @@
       if (lane == 0) mbar_arrive(&ctl.a_full[g][pending_slot]);
       pending = false;
     };
-    for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
+    uint32_t unit_i = 0;
+    for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x, ++unit_i) {
       const UnitInfo ui = decode_unit(u, tile_start, p, N);
       const int ks0 = ui.split * per_split, ks1 = min(nst_total, ks0 + per_split);
       for (int ks = ks0; ks < ks1 && ok; ++ks, ++it) {
@@ -83,4 +84,21 @@
       }
       if (!ok) break;
       if (pending) retire();  // the accumulators need every slot of the unit
+      if (NDBUF == 1) {
+        // single accumulator buffer: the main loop cannot go on until it is drained, so all sixteen
+        // dequant warps drain it together. The four warps of a lane quarter split the columns.
+        if (!mbar_wait(&ctl.d_full[0], unit_i & 1u, abortw)) { ok = false; break; }
+        tc_fence_after();
+        if (tid == 256) { if (unit_i == 0) MSK_TR(TR_FIRST_DFULL); MSK_TR(TR_LAST_DFULL); }
+        if (PHASE == 0) {
+          const int part = kh * 2 + g;  // 0..3: a quarter of the token columns, gate and up of this lane
+          epilogue_columns<N, PHASE>(p, ui, tmem + lane_base, row, part * (N / 4), (part + 1) * (N / 4), 0);
+        } else {
+          epilogue_columns<N, PHASE>(p, ui, tmem + lane_base, row, kh * (N / 2), (kh + 1) * (N / 2), g);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&ctl.d_empty[0]);
+        if (tid == 256 && unit_i == 0) MSK_TR(TR_FIRST_EPI_DONE);
+      }
     }

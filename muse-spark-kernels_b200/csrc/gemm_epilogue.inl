@@ -2,6 +2,7 @@
 // Thread `row` reads TMEM lane `row` of both accumulator tiles of the unit. With K splits
 // the raw accumulators go to partial[base unit][split][tile][row][N]; the thread block that
 // draws the last ticket of a base unit sums the splits in index order and finishes.
+    if (NDBUF > 1) {
     const int row = (warp & 3) * 32 + lane;
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
     uint32_t unit_i = 0, epi_par = 0;
@@ -141,4 +142,5 @@
         if (lane == 0) mbar_arrive(&ctl.d_empty[db]);
       }
       if (tid == 128 && unit_i == 0) MSK_TR(TR_FIRST_EPI_DONE);
+    }
     }

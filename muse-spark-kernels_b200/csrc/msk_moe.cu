@@ -331,6 +331,7 @@ static Plan make_plan(const MskMoeCfg* c, int T) {
   p.s2 = c->split_k2 > 0 ? c->split_k2 : pick_split(tiles * (c->hidden / 256), c->inter / KS, p.grid);
   p.s13 = std::min(p.s13, c->hidden / KS);
   p.s2 = std::min(p.s2, c->inter / KS);
+  if (p.N >= 128) p.s13 = p.s2 = 1;  // the single-buffered wide tile has no split-K epilogue (and no use for one)
   return p;
 }
 
