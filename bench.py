@@ -174,11 +174,26 @@ def run_gpu(args, spec):
         from muse_moe_w4a16 import ep
         return ep.bench_ep(args, spec, dev, rank, world, METRIC, UNIT, ClockSampler, load_peaks)
 
+    if args.experts:
+        # a smaller instance of the same kernels: fewer experts resident, same per-expert shapes
+        s = dict(s, E=args.experts)
+        inputs.SHAPES[spec["shape"]] = s
+        E = args.experts
+        spec = dict(spec, name=spec["name"] + f"_E{E}resident")
     peaks = load_peaks()
     weights = inputs.make_weights(H, I, E, 0, dev)
     state = moe.prepare(weights, n_experts=E, top_k=k, max_tokens=T)
     del weights
     torch.cuda.empty_cache()
+    if args.profile_only:
+        flush = torch.empty(64 * 1024 * 1024, dtype=torch.int32, device=dev)
+        for i in range(max(args.warmup, 1) + args.steps):
+            data, _ = inputs.make_inputs(spec["shape"], T, i % POOL, dev)
+            flush.zero_()
+            moe.kernel_fn(data, state)
+        torch.cuda.synchronize()
+        print(json.dumps({"profile_only": spec["name"], "plan": moe.plan(state, T), "status": moe.read_status(state)}))
+        return
     pool, host_pool = [], []
     for i in range(POOL):
         data, _ = inputs.make_inputs(spec["shape"], T, i, dev)
@@ -323,6 +338,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--workload", default="auto")
+    ap.add_argument("--experts", type=int, default=0, help="resident experts (smaller case for profiler captures)")
+    ap.add_argument("--profile-only", action="store_true", help="run warmup+steps eager steps and exit (for ncu)")
     args = ap.parse_args()
     spec = workload_spec(args.workload, args.gpus)
     if args.impl == "reference":
