@@ -155,7 +155,7 @@ int msk_moe_forward_timed(const MskMoeCfg* cfg, const void* packed13, const void
 
 /* msk_moe_forward for callers that cannot allocate device memory on the calling path (all
  * memory handed to their own pool, allocator locked, a latency-critical thread that must not
- * enter the driver's allocator): the scratch lives in a 6 MiB file-scope device array inside the library, which every
+ * enter the driver's allocator): the scratch lives in an 8 MiB file-scope device array inside the library, which every
  * GPU that loads the library holds until the process exits. No counterpart in the reference,
  * whose scratch is always allocated by prepare(). Limits: n_tokens * top_k <= 128,
  * hidden <= 8192, inter <= 4096, else MSK_ERR_TOO_LARGE. The first call on a device resolves

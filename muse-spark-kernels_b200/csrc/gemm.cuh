@@ -26,10 +26,10 @@
 // buffer and takes a ticket; the unit that draws the last ticket sums the partials in
 // split order 0..S-1 (the order never depends on arrival) and runs the epilogue.
 //
-// Numerics: operands are e2m1*e4m3*2^-62 (exact in BF16) and BF16 activations, FP32
-// accumulation, accumulator * (gs * 2^62) in the epilogue; PHASE 0 writes
-// bf16(silu(g) * u), PHASE 1 writes FP32 rows times (1 + post_norm_w) when given
-// (muse_moe_w4a16/cuda/moe.cu:440-478).
+// Numerics: operands are e2m1*e4m3 (exact in F16) and the BF16 activations held as F16 (exact
+// in the F16 range), FP32 accumulation, accumulator * gs in the epilogue; PHASE 0 writes
+// bf16(silu(g) * u) (stored as F16), PHASE 1 writes FP32 rows times (1 + post_norm_w) when
+// given (muse_moe_w4a16/cuda/moe.cu:440-478).
 #pragma once
 #include <cstdint>
 #include <cuda_bf16.h>
@@ -66,7 +66,7 @@ struct GemmCfg {
   // 128-byte swizzle) from rows that are contiguous in sorted order; narrower tiles gather rows
   // through the permutation with cp.async (gemm_gather.inl).
   static constexpr bool TMA_B = N >= 64;
-  static constexpr int LUT_BYTES = 1024;
+  static constexpr int LUT_BYTES = 0;
   static constexpr int CTRL_BYTES = 1024;  // barriers, TMEM base, abort word, tile table header
   static constexpr int TABLE_INTS = MAX_LOCAL_EXPERTS + 4;  // per table: tile_start, cnt, off copies
   static constexpr int TABLE_BYTES = 3 * TABLE_INTS * 4;
@@ -78,8 +78,8 @@ struct GemmParams {
   CUtensorMap tmap_act;      // TMA_B only: [rows, K] bf16, box 64 x N, 128-byte swizzle (64-byte aligned: first member)
   const uint8_t* w;          // packed tiles of this GEMM
   const float* gs;           // [local_count] global scales
-  const void* act;           // PHASE 0: x bf16 [T, H]; PHASE 1: inter bf16 [R, I]
-  void* outp;                // PHASE 0: inter bf16 [R, I]; PHASE 1: y fp32 [R, H]
+  const void* act;           // PHASE 0: x as f16 [T, H] (or sorted rows [R, H] with TMA_B); PHASE 1: inter f16 [R, I]
+  void* outp;                // PHASE 0: inter f16 [R, I]; PHASE 1: y fp32 [R, H]
   const __nv_bfloat16* post_norm_w;  // PHASE 1 only, nullable
   const int32_t* cnt;        // [local_count]
   const int32_t* off;        // [local_count + 1]
@@ -154,6 +154,13 @@ __device__ __forceinline__ UnitInfo decode_unit(int u, const int* tile_start, co
 
 __device__ __forceinline__ float silu_f(float g) { return g / (1.0f + __expf(-g)); }
 
+// The SwiGLU value as the down GEMM reads it: rounded to BF16 (the reference's one rounding of
+// `inter`, muse_prefill_layer/py/07_selftest.py:70), then held as F16 (exact inside the F16 range).
+__device__ __forceinline__ __half inter_value(float v) {
+  const float r = __bfloat162float(__float2bfloat16_rn(v));
+  return __float2half_rn(fminf(fmaxf(r, -65504.f), 65504.f));
+}
+
 // Epilogue of a unit without K splits for the thread that owns TMEM lane `row`: columns
 // [c_beg, c_end) of the accumulators at d_tmem (lane base included). PHASE 0 reads gate (tile 0)
 // and up (tile 1) and writes bf16(silu(g) * u) into inter; PHASE 1 writes the rows of `tile`
@@ -161,9 +168,9 @@ __device__ __forceinline__ float silu_f(float g) { return g / (1.0f + __expf(-g)
 template <int N, int PHASE>
 __device__ __forceinline__ void epilogue_columns(const GemmParams& p, const UnitInfo& ui, uint32_t d_tmem, int row,
                                                  int c_beg, int c_end, int tile) {
-  const float gsc = p.gs[ui.expert] * TWO_POW_62;
+  const float gsc = p.gs[ui.expert];
   if (PHASE == 0) {
-    __nv_bfloat16* outp = static_cast<__nv_bfloat16*>(p.outp) + static_cast<size_t>(ui.row0) * p.out_ld + ui.pair * 128 + row;
+    __half* outp = static_cast<__half*>(p.outp) + static_cast<size_t>(ui.row0) * p.out_ld + ui.pair * 128 + row;
     for (int c0 = c_beg; c0 < c_end; c0 += 16) {
       if (c0 >= ui.rows) break;
       uint32_t r0[16], r1[16];
@@ -174,7 +181,7 @@ __device__ __forceinline__ void epilogue_columns(const GemmParams& p, const Unit
       for (int j = 0; j < 16; ++j) {
         if (c0 + j < ui.rows) {
           const float v = silu_f(__uint_as_float(r0[j]) * gsc) * (__uint_as_float(r1[j]) * gsc);
-          outp[static_cast<size_t>(c0 + j) * p.out_ld] = __float2bfloat16_rn(v);
+          outp[static_cast<size_t>(c0 + j) * p.out_ld] = inter_value(v);
         }
       }
     }
@@ -203,7 +210,6 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) moe_gemm_kernel(const __grid_
   constexpr int NDBUF = C::NDBUF;
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* ring = smem;                                        // NST x [tile g0 | tile g1 | B]
-  uint32_t* lut = reinterpret_cast<uint32_t*>(smem + NST * C::STAGE_BYTES);
   GemmCtrl& ctl = *reinterpret_cast<GemmCtrl*>(smem + NST * C::STAGE_BYTES + C::LUT_BYTES);
   int* tile_start = reinterpret_cast<int*>(smem + NST * C::STAGE_BYTES + C::LUT_BYTES + C::CTRL_BYTES);
 
@@ -234,7 +240,6 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) moe_gemm_kernel(const __grid_
     ctl.last_flag = 0;
     fence_mbar_init();
   }
-  if (tid >= 256 && tid < 512) lut[tid - 256] = e4m3_scale_bf16x2(static_cast<uint32_t>(tid - 256));
   if (warp == 1) {
     tmem_alloc(&ctl.tmem_base, TMEM_COLS);
     tmem_relinquish();

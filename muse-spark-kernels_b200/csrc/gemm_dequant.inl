@@ -10,7 +10,6 @@
     const int row = (warp & 3) * 32 + lane;
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t a_tmem = tmem + lane_base + C::A_BASE + g * C::A_GROUP_COLS;
-    const uint32_t lut_s = smem_u32(lut);
     uint32_t it = 0;
     int tri = 0;
     uint32_t as = kh, apar = 0;  // ring slot of this warp's next K half and its phase parity
@@ -49,19 +48,8 @@
                          : "=r"(q[0]), "=r"(q[1]), "=r"(q[2]), "=r"(q[3])
                          : "r"(tile_row + chunk * 2048));
             const uint32_t sfw = kh ? (c < 2 ? sfa[2] : sfa[3]) : (c < 2 ? sfa[0] : sfa[1]);
-            const uint32_t sw = (c & 1) ? (sfw >> 16) : sfw;
-            const uint32_t s0 = lds32(lut_s + ((sw << 2) & 0x3FCu)), s1 = lds32(lut_s + ((sw >> 6) & 0x3FCu));
             uint32_t o[16];
-#pragma unroll
-            for (int w = 0; w < 4; ++w) {
-              uint32_t r0, r1, r2, r3;
-              decode_codes(q[w], r0, r1, r2, r3);
-              const uint32_t s = w < 2 ? s0 : s1;
-              o[4 * w + 0] = hmul2_bf16(r0, s);
-              o[4 * w + 1] = hmul2_bf16(r1, s);
-              o[4 * w + 2] = hmul2_bf16(r2, s);
-              o[4 * w + 3] = hmul2_bf16(r3, s);
-            }
+            decode_chunk(q, (c & 1) ? (sfw >> 16) : sfw, o);
             if (c == 0) {
               // hand over the previous slot (its stores had the decode above to land), claim this one
               if (pending) retire();

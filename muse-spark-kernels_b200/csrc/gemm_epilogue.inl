@@ -22,7 +22,7 @@
       tc_fence_after();
       if (tid == 128) { if (unit_i == 0) MSK_TR(TR_FIRST_DFULL); MSK_TR(TR_LAST_DFULL); }
       const uint32_t d_tmem = tmem + lane_base + db * (2 * N);
-      const float gsc = p.gs[ui.expert] * TWO_POW_62;
+      const float gsc = p.gs[ui.expert];
       const int base_unit = ui.tile * p.n_pairs + ui.pair;
       const size_t part_stride = static_cast<size_t>(2) * 128 * N;  // floats per (base unit, split)
       bool finish = true;
@@ -61,7 +61,7 @@
       if (finish) {
         const float* part0 = p.partial + static_cast<size_t>(base_unit) * p.splits * part_stride;
         if (PHASE == 0) {
-          __nv_bfloat16* outp = static_cast<__nv_bfloat16*>(p.outp);
+          __half* outp = static_cast<__half*>(p.outp);
           const int col = ui.pair * 128 + row;
           for (int c0 = 0; c0 < N; c0 += 8) {
             if (c0 >= ui.rows) break;
@@ -93,7 +93,7 @@
               const int n = c0 + j;
               if (n < ui.rows) {
                 const float v = silu_f(ga[j] * gsc) * (up[j] * gsc);
-                outp[static_cast<size_t>(ui.row0 + n) * p.out_ld + col] = __float2bfloat16_rn(v);
+                outp[static_cast<size_t>(ui.row0 + n) * p.out_ld + col] = inter_value(v);
               }
             }
           }

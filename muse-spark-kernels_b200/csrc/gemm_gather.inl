@@ -20,7 +20,7 @@
       const UnitInfo ui = decode_unit(u, tile_start, p, N);
       const int ks0 = ui.split * per_split, ks1 = min(nst_total, ks0 + per_split);
       // source row of token n = ng*8 + n_sub, for every 8-group ng
-      const __nv_bfloat16* src[N / 8];
+      const __half* src[N / 8];
 #pragma unroll
       for (int ng = 0; ng < N / 8; ++ng) {
         const int n = ng * 8 + n_sub;
@@ -28,7 +28,7 @@
         if (n < ui.rows) {
           const int r = ui.row0 + n;
           const size_t row = PHASE == 0 ? static_cast<size_t>(p.perm[r] / p.top_k) : static_cast<size_t>(r);
-          src[ng] = static_cast<const __nv_bfloat16*>(p.act) + row * act_ld;
+          src[ng] = static_cast<const __half*>(p.act) + row * act_ld;
         }
       }
       for (int ks = ks0; ks < ks1; ++ks, ++it) {
@@ -38,7 +38,7 @@
 #pragma unroll
         for (int ng = 0; ng < N / 8; ++ng) {
           const bool valid = src[ng] != nullptr;
-          const __nv_bfloat16* s = valid ? src[ng] + static_cast<size_t>(ks) * KS : static_cast<const __nv_bfloat16*>(p.act);
+          const __half* s = valid ? src[ng] + static_cast<size_t>(ks) * KS : static_cast<const __half*>(p.act);
 #pragma unroll
           for (int cg = 0; cg < 4; ++cg) {
             const int chunk = cg * 8 + c_sub;

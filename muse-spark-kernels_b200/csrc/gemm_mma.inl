@@ -2,7 +2,7 @@
 // One A slot (128 K, 64 TMEM columns per tile) is consumed by eight K=16 MMAs per tile and
 // handed back with a tcgen05.commit, so several dequant -> MMA -> release hand-offs are in
 // flight at once. The accumulators of consecutive units alternate between NDBUF buffers.
-    constexpr uint32_t idesc = idesc_f16(FMT_BF16, FMT_BF16, 128, N);
+    constexpr uint32_t idesc = idesc_f16(FMT_F16, FMT_F16, 128, N);
     uint32_t it = 0, unit_i = 0, sc = 0;
     uint32_t as = 0, apar = 0;  // A ring position and its phase parity
 #ifdef MSK_EXP_MMA_CLOCKS

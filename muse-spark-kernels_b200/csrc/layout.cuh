@@ -2,28 +2,30 @@
 //
 // One tile = 128 weight rows x 256 K (one K stage):
 //   bytes [0, 16384)      codes: 16-byte chunk c (0..7) of row r at (c*128 + r)*16; a chunk
-//                         holds K [32c, 32c+32) of the stage as four 32-bit words, word i =
-//                         eight codes k = 32c + 8i + (0..7), bit-permuted (below);
+//                         holds K [32c, 32c+32) of the stage, two E2M1 codes per byte in the
+//                         source order (low nibble = even k);
 //   bytes [16384, 18432)  scales: row r's sixteen E4M3 bytes at 16384 + r*16, byte j = block j.
 // Thread r of a 128-thread group owns row r, so every 16-byte shared-memory read of a
-// quarter-warp is 128 contiguous bytes.
+// quarter-warp is 128 contiguous bytes. The repack is a pure byte permutation.
 //
-// Bit permutation of one word (eight 4-bit codes c0..c7, code bits b0=m, b1=e0, b2=e1, b3=s):
-// output register j (codes 2j, 2j+1) must end as BF16x2 bit patterns
-//     lo half: s->15, e1->8, e0->7, m->6      hi half: the same +16,
-// i.e. e2m1 * 2^-126 (BF16 subnormal trick; the meaning of the code bits is the one of
-// muse_moe_w4a16/cuda/moe.cu:293-310). The stored word places those eight bits so that
-//     r0 =  q            & 0x81C081C0
-//     r1 =  rotl(q, 6)   & 0x81C081C0
-//     r2 =  rotl(q, 12)  & 0x81C081C0
-//     r3 = (rotl(q, 2)   & 0x00400040) | (rotl(q, 10) & 0x81808180)
-// (rotation set found by exhaustive search over rotation pairs; 8 integer ops per 8 codes).
-// Each register is then multiplied (mul.bf16x2, exact) by the block scale as BF16
-// e4m3 * 2^64, giving e2m1*e4m3 * 2^-62; the epilogue multiplies the FP32 accumulator by
-// gs * 2^62 (global scale on the accumulator, as muse_moe_w4a16/cuda/moe.cu:771-773).
+// Decode (per 16-byte chunk: 32 codes, two scale blocks): the hardware converts
+//   cvt.rn.f16x2.e2m1x2  one byte  -> two F16 code values {0, .5, 1, 1.5, 2, 3, 4, 6} (signed)
+//   cvt.rn.f16x2.e4m3x2  two bytes -> two F16 scales (zero, subnormal and NaN bytes included)
+// and one mul.f16x2 per code pair gives e2m1 * e4m3, exact in F16 (at most 6 significant bits,
+// magnitudes 2^-10 .. 2688). Measured on B200, each of these retires one warp instruction per
+// two cycles per scheduler, and a chunk costs 16 converts + 16 multiplies + 3 for the scales;
+// the bit-trick decode to BF16 (subnormal placement + mul.bf16x2) needed about twice the ALU
+// work and made the whole kernel ALU-pipe bound. The MMA therefore runs F16 x F16 -> FP32: the
+// activation operand is converted BF16 -> F16 on the way in (exact for 2^-17 <= |x| <= 65504,
+// the range the reference's decode layer also assumes when it feeds its expert kernel "exact
+// fp16" activations, muse_decode_layer/py/04_triton_kernels.py:557), the global scale is
+// applied to the FP32 accumulator (muse_moe_w4a16/cuda/moe.cu:771-773).
 #pragma once
 #include <cstdint>
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "ptx.cuh"
 
 namespace msk {
 
@@ -32,63 +34,32 @@ constexpr int TILE_ROWS = 128;                            // weight rows per til
 constexpr int TILE_CODE_BYTES = TILE_ROWS * KS / 2;       // 16384
 constexpr int TILE_SF_BYTES = TILE_ROWS * KS / 16;        // 2048
 constexpr int TILE_BYTES = TILE_CODE_BYTES + TILE_SF_BYTES;  // 18432
-constexpr float TWO_POW_62 = 4611686018427387904.0f;
-
-// Source bit of the stored word for (output register j, half h, code bit b).
-__host__ __device__ constexpr int stored_bit(int j, int h, int b) {
-  const int o = (b == 0 ? 6 : b == 1 ? 7 : b == 2 ? 8 : 15) + 16 * h;
-  const int rot = j == 0 ? 0 : j == 1 ? 6 : j == 2 ? 12 : (b == 0 ? 2 : 10);
-  return (o - rot + 32) & 31;
-}
-
-// Eight natural-order codes (code c in bits [4c, 4c+4)) -> stored word.
-__host__ __device__ inline uint32_t pack_word(uint32_t nat) {
-  uint32_t q = 0;
-  for (int c = 0; c < 8; ++c) {
-    const uint32_t code = (nat >> (4 * c)) & 0xFu;
-    for (int b = 0; b < 4; ++b) q |= ((code >> b) & 1u) << stored_bit(c >> 1, c & 1, b);
-  }
-  return q;
-}
-__host__ __device__ inline uint32_t unpack_word(uint32_t q) {
-  uint32_t nat = 0;
-  for (int c = 0; c < 8; ++c)
-    for (int b = 0; b < 4; ++b) nat |= ((q >> stored_bit(c >> 1, c & 1, b)) & 1u) << (4 * c + b);
-  return nat;
-}
 
 #ifdef __CUDACC__
-__device__ __forceinline__ uint32_t hmul2_bf16(uint32_t a, uint32_t b) {
-  uint32_t d;
-  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
-  return d;
-}
-
-// Stored word -> four BF16x2 registers holding e2m1 * 2^-126 (codes 2j, 2j+1 in register j).
-__device__ __forceinline__ void decode_codes(uint32_t q, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
-  constexpr uint32_t M = 0x81C081C0u;
-  r0 = q & M;
-  r1 = __funnelshift_l(q, q, 6) & M;
-  r2 = __funnelshift_l(q, q, 12) & M;
-  r3 = (__funnelshift_l(q, q, 2) & 0x00400040u) | (__funnelshift_l(q, q, 10) & 0x81808180u);
-}
-
-// E4M3 byte -> BF16 bit pattern of value * 2^64, replicated in both halves (0x7F/0xFF -> NaN).
-// Formula of the reference's table (muse_moe_w4a16/cuda/moe.cu:2450-2461): exponent field 0 is
-// mt * 2^-9, otherwise (1 + mt/8) * 2^(ex-7).
-__device__ __forceinline__ uint32_t e4m3_scale_bf16x2(uint32_t byte) {
-  const uint32_t ex = (byte >> 3) & 15u, mt = byte & 7u;
-  uint32_t bits;
-  if ((byte & 0x7Fu) == 0x7Fu) {
-    bits = 0x7FFFu;
-  } else if (ex != 0u) {
-    bits = ((byte & 0x7Fu) << 4) + 0x5C00u;  // (ex + 184) << 7 | mt << 4
-  } else {
-    const float v = static_cast<float>(mt) * 36028797018963968.0f;  // mt * 2^-9 * 2^64 = mt * 2^55
-    bits = static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(v)));
+// One chunk: four words (32 codes) and the low 16 bits of `sf2` (the scale bytes of its two
+// blocks) -> sixteen F16x2 registers, register 4w+j = codes (8w+2j, 8w+2j+1) of the chunk.
+__device__ __forceinline__ void decode_chunk(const uint32_t (&q)[4], uint32_t sf2, uint32_t (&o)[16]) {
+  const uint32_t s01 = cvt_e4m3x2_f16(static_cast<uint16_t>(sf2 & 0xFFFFu));
+  const uint32_t s0 = prmt(s01, s01, 0x1010u), s1 = prmt(s01, s01, 0x3232u);
+#pragma unroll
+  for (int w = 0; w < 4; ++w) {
+    uint32_t h0, h1, h2, h3;
+    cvt_e2m1x8_f16(q[w], h0, h1, h2, h3);
+    const uint32_t s = w < 2 ? s0 : s1;
+    o[4 * w + 0] = hmul2_f16(h0, s);
+    o[4 * w + 1] = hmul2_f16(h1, s);
+    o[4 * w + 2] = hmul2_f16(h2, s);
+    o[4 * w + 3] = hmul2_f16(h3, s);
   }
-  bits |= (byte & 0x80u) << 8;
-  return bits | (bits << 16);
+}
+
+// BF16 -> F16 of a register pair, saturating at the F16 range (values beyond it cannot be
+// represented; they do not occur for normalised activations).
+__device__ __forceinline__ uint32_t bf16x2_to_f16x2(uint32_t v) {
+  const float lo = fminf(fmaxf(__uint_as_float(v << 16), -65504.f), 65504.f);
+  const float hi = fminf(fmaxf(__uint_as_float(v & 0xFFFF0000u), -65504.f), 65504.f);
+  const __half2 h = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&h);
 }
 #endif
 

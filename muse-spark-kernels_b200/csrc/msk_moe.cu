@@ -54,13 +54,7 @@ __global__ void __launch_bounds__(256) repack_kernel(uint8_t* codes, uint8_t* sf
   if (part < 8) {
     uint4* src = reinterpret_cast<uint4*>(codes + srow * (g.K / 2) + ks * (KS / 2) + part * 16);
     uint4* dst = reinterpret_cast<uint4*>(ptile + (part * 128 + r) * 16);
-    if (!INVERSE) {
-      const uint4 v = *src;
-      *dst = make_uint4(pack_word(v.x), pack_word(v.y), pack_word(v.z), pack_word(v.w));
-    } else {
-      const uint4 v = *dst;
-      *src = make_uint4(unpack_word(v.x), unpack_word(v.y), unpack_word(v.z), unpack_word(v.w));
-    }
+    if (!INVERSE) *dst = *src; else *src = *dst;
   } else {
     uint4* src = reinterpret_cast<uint4*>(sf + srow * (g.K / 16) + ks * (KS / 16));
     uint4* dst = reinterpret_cast<uint4*>(ptile + TILE_CODE_BYTES + r * 16);
@@ -68,13 +62,10 @@ __global__ void __launch_bounds__(256) repack_kernel(uint8_t* codes, uint8_t* sf
   }
 }
 
-// Packed tiles -> BF16 e2m1*e4m3 matrices, through the decode routine of the GEMM kernel
-// (values carry the 2^-62 factor in registers; multiplied back by 2^62 here, exact).
+// Packed tiles -> BF16 e2m1*e4m3 matrices, through the decode routine of the GEMM kernel (the
+// F16 products are exact and convert to BF16 without rounding).
 __global__ void __launch_bounds__(128) dequant_packed_kernel(const uint8_t* packed, __nv_bfloat16* out, RepackGeom g,
                                                              long long n_tiles) {
-  __shared__ uint32_t lut[256];
-  for (int i = threadIdx.x; i < 256; i += 128) lut[i] = e4m3_scale_bf16x2(static_cast<uint32_t>(i));
-  __syncthreads();
   const long long tile = blockIdx.x;
   if (tile >= n_tiles) return;
   const int r = threadIdx.x;
@@ -87,19 +78,16 @@ __global__ void __launch_bounds__(128) dequant_packed_kernel(const uint8_t* pack
   const uint4 sfw = *reinterpret_cast<const uint4*>(ptile + TILE_CODE_BYTES + r * 16);
   const uint32_t sfa[4] = {sfw.x, sfw.y, sfw.z, sfw.w};
   __nv_bfloat16* orow = out + srow * g.K + ks * KS;
-  const uint32_t two62 = 0x5E805E80u;  // bf16x2 of 2^62
   for (int chunk = 0; chunk < 8; ++chunk) {
-    const uint4 q = *reinterpret_cast<const uint4*>(ptile + (chunk * 128 + r) * 16);
-    const uint32_t qa[4] = {q.x, q.y, q.z, q.w};
+    const uint4 qv = *reinterpret_cast<const uint4*>(ptile + (chunk * 128 + r) * 16);
+    const uint32_t q[4] = {qv.x, qv.y, qv.z, qv.w};
     const uint32_t sw = sfa[chunk >> 1] >> ((chunk & 1) * 16);
-    for (int i = 0; i < 4; ++i) {
-      const uint32_t s = lut[(i < 2 ? sw : (sw >> 8)) & 0xFFu];
-      uint32_t rr[4];
-      decode_codes(qa[i], rr[0], rr[1], rr[2], rr[3]);
-      for (int j = 0; j < 4; ++j) {
-        const uint32_t v = hmul2_bf16(hmul2_bf16(rr[j], s), two62);
-        *reinterpret_cast<uint32_t*>(orow + chunk * 32 + i * 8 + j * 2) = v;
-      }
+    uint32_t o[16];
+    decode_chunk(q, sw, o);
+    for (int j = 0; j < 16; ++j) {
+      const __half2 h = *reinterpret_cast<const __half2*>(&o[j]);
+      orow[chunk * 32 + 2 * j] = __float2bfloat16_rn(__low2float(h));
+      orow[chunk * 32 + 2 * j + 1] = __float2bfloat16_rn(__high2float(h));
     }
   }
 }
@@ -109,17 +97,25 @@ __global__ void __launch_bounds__(128) dequant_packed_kernel(const uint8_t* pack
 // (expert-major) order, so that wide token tiles can be fetched as plain 2-D TMA boxes. The
 // reference's prefill path gathers rows into per-expert tiles the same way
 // (muse_prefill_layer/cuda/prefill.cu:1446-1608), there fused with its pre-expert norm.
+// The copy also converts BF16 -> F16, the operand type of the MMA (layout.cuh).
+// gather != 0: xs[q] = f16(x[perm[q] / top_k]) for q < off[nloc] (grid = T * top_k blocks);
+// gather == 0: xs[t] = f16(x[t]) (grid = T blocks), for the narrow token tiles that gather rows
+// through the permutation themselves.
 __global__ void __launch_bounds__(256) gather_rows_kernel(const __nv_bfloat16* __restrict__ x,
                                                           const int32_t* __restrict__ perm,
                                                           const int32_t* __restrict__ off, int nloc, int top_k, int H,
-                                                          __nv_bfloat16* __restrict__ xs) {
+                                                          int gather, __half* __restrict__ xs) {
   pdl_wait();
   pdl_launch_dependents();
   const int q = blockIdx.x;
-  if (q >= off[nloc]) return;
-  const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<size_t>(perm[q] / top_k) * H);
+  if (gather && q >= off[nloc]) return;
+  const size_t row = gather ? static_cast<size_t>(perm[q] / top_k) : static_cast<size_t>(q);
+  const uint4* src = reinterpret_cast<const uint4*>(x + row * H);
   uint4* dst = reinterpret_cast<uint4*>(xs + static_cast<size_t>(q) * H);
-  for (int i = threadIdx.x; i < H / 8; i += 256) dst[i] = src[i];
+  for (int i = threadIdx.x; i < H / 8; i += 256) {
+    const uint4 v = src[i];
+    dst[i] = make_uint4(bf16x2_to_f16x2(v.x), bf16x2_to_f16x2(v.y), bf16x2_to_f16x2(v.z), bf16x2_to_f16x2(v.w));
+  }
 }
 
 // ---------------------------------------------------------------- combine
@@ -404,7 +400,7 @@ static int encode_act_map(CUtensorMap* map, const void* base, size_t rows, int K
   const cuuint64_t strides[1] = {static_cast<cuuint64_t>(K) * 2};
   const cuuint32_t box[2] = {64u, static_cast<cuuint32_t>(box_rows)};
   const cuuint32_t estr[2] = {1u, 1u};
-  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : static_cast<int>(cudaErrorInvalidValue);
@@ -689,10 +685,10 @@ static int forward_impl(const MskMoeCfg* cfg, const void* packed13, const void* 
   int32_t* perm = reinterpret_cast<int32_t*>(b + k.perm);
   int32_t* inv = reinterpret_cast<int32_t*>(b + k.inv);
   int32_t* tickets = reinterpret_cast<int32_t*>(b + k.tickets);
-  __nv_bfloat16* inter = reinterpret_cast<__nv_bfloat16*>(b + k.inter);
+  __half* inter = reinterpret_cast<__half*>(b + k.inter);
   float* y = reinterpret_cast<float*>(b + k.y);
   float* partial = reinterpret_cast<float*>(b + k.partial);
-  __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(b + k.xs);
+  __half* xs = reinterpret_cast<__half*>(b + k.xs);
 
   Plan plan = make_plan(cfg, n_tokens);
   if (plan.N != 16 && plan.N != 32 && plan.N != 64 && plan.N != 128) return MSK_ERR_SHAPE;
@@ -739,10 +735,10 @@ static int forward_impl(const MskMoeCfg* cfg, const void* packed13, const void* 
   const size_t r_max = static_cast<size_t>(cfg->max_tokens) * cfg->top_k;
   p.w = static_cast<const uint8_t*>(packed13); p.gs = gs13; p.act = x; p.outp = inter; p.post_norm_w = nullptr;
   p.K = cfg->hidden; p.out_ld = cfg->inter; p.n_pairs = cfg->inter / 128; p.splits = plan.s13;
-  if (tma_b) {
-    // sorted copy of the token rows, then the activation operand is a plain 2-D tensor for TMA
+  {
+    // F16 copy of the token rows: sorted (expert-major) for the TMA tiles, plain [T, H] otherwise
     cudaLaunchConfig_t lc{};
-    lc.gridDim = dim3(static_cast<unsigned>(n_tokens * cfg->top_k));
+    lc.gridDim = dim3(static_cast<unsigned>(tma_b ? n_tokens * cfg->top_k : n_tokens));
     lc.blockDim = dim3(256);
     lc.stream = st;
     cudaLaunchAttribute at[1];
@@ -753,11 +749,13 @@ static int forward_impl(const MskMoeCfg* cfg, const void* packed13, const void* 
     e = static_cast<int>(cudaLaunchKernelEx(&lc, gather_rows_kernel, static_cast<const __nv_bfloat16*>(x),
                                             static_cast<const int32_t*>(perm), static_cast<const int32_t*>(off),
                                             static_cast<int>(cfg->local_count), static_cast<int>(cfg->top_k),
-                                            static_cast<int>(cfg->hidden), xs));
+                                            static_cast<int>(cfg->hidden), tma_b ? 1 : 0, xs));
     if (e != 0) return e;
     p.act = xs;
-    e = encode_act_map(&p.tmap_act, xs, r_max, cfg->hidden, plan.N);
-    if (e != 0) return e;
+    if (tma_b) {
+      e = encode_act_map(&p.tmap_act, xs, r_max, cfg->hidden, plan.N);
+      if (e != 0) return e;
+    }
   }
   e = launch_gemm_n<0>(plan.N, p, plan.grid, st);
   if (e != 0) return e;
@@ -852,7 +850,7 @@ int msk_moe_forward_timed(const MskMoeCfg* cfg, const void* packed13, const void
 // application's allocator is locked, a latency-critical thread that must not enter the driver's
 // allocator.
 // msk_moe_forward needs a caller-allocated workspace; this variant keeps its scratch (sort
-// tables, the SwiGLU intermediate and the per-route expert outputs) in one file-scope device
+// tables, the F16 copy of the token rows, the SwiGLU intermediate and the per-route expert outputs) in one file-scope device
 // array instead. The array is part of the loaded library image: every GPU that loads the
 // library holds MSK_STATIC_WS_BYTES of it until the process exits.
 //  * Limits: n_tokens * top_k <= 128 routed rows, hidden <= 8192, inter <= 4096; anything
@@ -863,7 +861,7 @@ int msk_moe_forward_timed(const MskMoeCfg* cfg, const void* packed13, const void
 //    word is cleared on the stream at the start of every call, the tables are rewritten by the
 //    sort. Two calls that overlap on the GPU (different streams) race on it: serialise them.
 //  * No cudaMalloc, cudaFree or allocating library call is made.
-constexpr size_t MSK_STATIC_WS_BYTES = 6u << 20;
+constexpr size_t MSK_STATIC_WS_BYTES = 8u << 20;
 constexpr int MSK_STATIC_MAX_ROWS = 128;
 static __device__ __align__(256) unsigned char g_static_ws[MSK_STATIC_WS_BYTES];
 
@@ -887,6 +885,7 @@ int msk_moe_forward_static(const MskMoeCfg* cfg, const void* packed13, const voi
   const size_t o_inv = o; o += round_up(R * 4, 256);
   const size_t o_inter = o; o += round_up(R * cfg->inter * 2, 256);
   const size_t o_y = o; o += round_up(R * cfg->hidden * 4, 256);
+  const size_t o_xh = o; o += round_up(static_cast<size_t>(n_tokens) * cfg->hidden * 2, 256);
   if (o > MSK_STATIC_WS_BYTES) return MSK_ERR_TOO_LARGE;
 
   // device address of the array, once per device (the symbol's host-side name is not an address)
@@ -908,17 +907,22 @@ int msk_moe_forward_static(const MskMoeCfg* cfg, const void* packed13, const voi
   int32_t* off = reinterpret_cast<int32_t*>(b + o_off);
   int32_t* perm = reinterpret_cast<int32_t*>(b + o_perm);
   int32_t* inv = reinterpret_cast<int32_t*>(b + o_inv);
-  __nv_bfloat16* inter = reinterpret_cast<__nv_bfloat16*>(b + o_inter);
+  __half* inter = reinterpret_cast<__half*>(b + o_inter);
   float* y = reinterpret_cast<float*>(b + o_y);
+  __half* xh = reinterpret_cast<__half*>(b + o_xh);
 
   int e = launch_sort(cfg, topk_ids, n_tokens, cnt, off, perm, inv, st);
+  if (e != 0) return e;
+  gather_rows_kernel<<<static_cast<unsigned>(n_tokens), 256, 0, st>>>(
+      static_cast<const __nv_bfloat16*>(x), perm, off, cfg->local_count, cfg->top_k, cfg->hidden, 0, xh);
+  e = static_cast<int>(cudaGetLastError());
   if (e != 0) return e;
   GemmParams p{};
   p.cnt = cnt; p.off = off; p.perm = perm; p.partial = nullptr; p.tickets = nullptr;
   p.status = reinterpret_cast<int32_t*>(b); p.trace = nullptr;
   p.nloc = cfg->local_count; p.top_k = cfg->top_k; p.evict_first = 1; p.splits = 1;
   const int grid = cfg->num_ctas > 0 ? cfg->num_ctas : sm_count();
-  p.w = static_cast<const uint8_t*>(packed13); p.gs = gs13; p.act = x; p.outp = inter; p.post_norm_w = nullptr;
+  p.w = static_cast<const uint8_t*>(packed13); p.gs = gs13; p.act = xh; p.outp = inter; p.post_norm_w = nullptr;
   p.K = cfg->hidden; p.out_ld = cfg->inter; p.n_pairs = cfg->inter / 128;
   e = launch_gemm_n<0>(16, p, grid, st);
   if (e != 0) return e;

@@ -224,7 +224,7 @@ def workspace_views(state, T):
     R = int(off[-1].item())
     perm = view(2, T * k * 4, torch.int32)
     inv = view(3, T * k * 4, torch.int32)
-    inter = view(4, R * cfg.inter * 2, torch.bfloat16).view(R, cfg.inter)
+    inter = view(4, R * cfg.inter * 2, torch.float16).view(R, cfg.inter)
     y = view(5, R * cfg.hidden * 4, torch.float32).view(R, cfg.hidden)
     return {"cnt": cnt, "off": off, "perm": perm, "inv": inv, "inter": inter, "y": y}
 
