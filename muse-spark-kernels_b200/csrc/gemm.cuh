@@ -4,9 +4,9 @@
 // Per CTA (768 threads, one CTA per SM):
 //   warp 0       weight producer: 1-D bulk async copies (TMA engine) of packed NVFP4 tiles,
 //                two tiles (a "pair") per K stage, into a shared-memory ring;
-//   warp 1       MMA issuer: tcgen05.mma kind::f16, A from TMEM, B from shared memory,
-//                FP32 accumulators in TMEM; owns the TMEM allocation;
-//   warps 2-3    activation gather: cp.async of the token rows of the tile (through the
+//   warps 1, 3   MMA issuers (one per tile of the pair): tcgen05.mma kind::f16, A from TMEM,
+//                B from shared memory, FP32 accumulators in TMEM; warp 1 owns the TMEM allocation;
+//   warp 2       activation gather: cp.async of the token rows of the tile (through the
 //                permutation for the gate/up GEMM) into the K-major core-matrix layout;
 //   warps 4-7    epilogue (gemm_epilogue.inl): TMEM accumulators -> SwiGLU / scale -> global,
 //                or split-K partials (token tiles up to 64; for 128 the accumulators are single-
@@ -114,7 +114,7 @@ enum : int { TR_START = 0, TR_SETUP, TR_FIRST_BULK, TR_FIRST_RAW, TR_FIRST_AFULL
 
 struct GemmCtrl {
   uint64_t raw_full[6], raw_empty[6], b_full[6], b_empty[6];
-  uint64_t a_full[2][6], a_empty[6];
+  uint64_t a_full[2][6], a_empty[2][6];
   uint64_t d_full[2], d_empty[2];
   uint64_t epi_bar;  // the 128 epilogue threads, for the split-K ticket
   uint32_t tmem_base;
@@ -223,16 +223,17 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) moe_gemm_kernel(const __grid_
     for (int i = 0; i < NST; ++i) {
       mbar_init(&ctl.raw_full[i], 1);
       mbar_init(&ctl.raw_empty[i], 16);
-      mbar_init(&ctl.b_full[i], C::TMA_B ? 1 : 2);
-      mbar_init(&ctl.b_empty[i], 1);
+      mbar_init(&ctl.b_full[i], 1);
+      mbar_init(&ctl.b_empty[i], 2);  // one commit per MMA issuer
     }
     for (int i = 0; i < NSLOT; ++i) {
       mbar_init(&ctl.a_full[0][i], 4);
       mbar_init(&ctl.a_full[1][i], 4);
-      mbar_init(&ctl.a_empty[i], 1);
+      mbar_init(&ctl.a_empty[0][i], 1);
+      mbar_init(&ctl.a_empty[1][i], 1);
     }
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&ctl.d_full[i], 1);
+      mbar_init(&ctl.d_full[i], 2);  // one commit per MMA issuer
       mbar_init(&ctl.d_empty[i], C::NDBUF == 1 ? 16 : 4);  // single buffer: the dequant warps run the epilogue
     }
     mbar_init(&ctl.epi_bar, 128);
@@ -286,9 +287,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) moe_gemm_kernel(const __grid_
 
   if (warp == 0) {
 #include "gemm_producer.inl"
-  } else if (warp == 1) {
+  } else if (warp == 1 || warp == 3) {
 #include "gemm_mma.inl"
-  } else if (warp < 4) {
+  } else if (warp == 2) {
 #include "gemm_gather.inl"
   } else if (warp >= 8) {
 #include "gemm_dequant.inl"

@@ -53,7 +53,7 @@
             if (c == 0) {
               // hand over the previous slot (its stores had the decode above to land), claim this one
               if (pending) retire();
-              if (!mbar_wait(&ctl.a_empty[as], apar ^ 1u, abortw)) { ok = false; break; }
+              if (!mbar_wait(&ctl.a_empty[g][as], apar ^ 1u, abortw)) { ok = false; break; }
               tc_fence_after();
             }
             tmem_st16(a_tmem + as * C::SLOT_COLS + c * 16, o);

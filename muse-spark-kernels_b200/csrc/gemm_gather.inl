@@ -1,4 +1,4 @@
-// Role body of moe_gemm_kernel (included inside the kernel): activation gather, warps 2-3.
+// Role body of moe_gemm_kernel (included inside the kernel): activation gather, warp 2.
 // Copies the token rows of the unit (x rows through the permutation for PHASE 0, sorted inter
 // rows for PHASE 1) with 16-byte cp.async into the K-major core-matrix layout of the B operand:
 // element (n, k) at (n/8)*B_SBO + (k/8)*B_LBO + (n%8)*16 + (k%8)*2. Eight lanes write one
@@ -6,8 +6,7 @@
 // stages late, once its copies have landed and a proxy fence has ordered them before the
 // tensor core's reads.
     if (!C::TMA_B) {
-    const int gt = tid - 64;                    // 0..63
-    const int n_sub = gt & 7, c_sub = gt >> 3;  // token within an 8-group, chunk within an 8-chunk group
+    const int n_sub = lane & 7, c_sub = lane >> 3;  // token within an 8-group, chunk within a 4-chunk group
     // A stage is published GLAG stages after it was issued, so the loop never waits for the
     // copies it has just started (one stage of lag made every iteration a full memory latency).
     constexpr int GLAG = NST >= 5 ? 3 : (NST >= 4 ? 2 : 1);
@@ -40,8 +39,8 @@
           const bool valid = src[ng] != nullptr;
           const __half* s = valid ? src[ng] + static_cast<size_t>(ks) * KS : static_cast<const __half*>(p.act);
 #pragma unroll
-          for (int cg = 0; cg < 4; ++cg) {
-            const int chunk = cg * 8 + c_sub;
+          for (int cg = 0; cg < 8; ++cg) {
+            const int chunk = cg * 4 + c_sub;
             cp_async16_hint(dstB + ng * B_SBO + chunk * B_LBO + n_sub * 16, s + chunk * 8, valid, keep);
           }
         }
