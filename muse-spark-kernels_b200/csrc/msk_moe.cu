@@ -548,7 +548,8 @@ int msk_moe_route(const MskMoeCfg* cfg, const float* logits, const float* bias, 
 }
 
 static int launch_sort(const MskMoeCfg* cfg, const int32_t* ids, int n_tokens, int32_t* cnt, int32_t* off,
-                       int32_t* perm, int32_t* inv, cudaStream_t st) {
+                       int32_t* perm, int32_t* inv, cudaStream_t st, const __nv_bfloat16* x = nullptr,
+                       __half* xh = nullptr) {
   static bool attr_set[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -570,13 +571,14 @@ static int launch_sort(const MskMoeCfg* cfg, const int32_t* ids, int n_tokens, i
   lc.numAttrs = 1;
   return static_cast<int>(cudaLaunchKernelEx(&lc, sort_kernel, ids, static_cast<int>(n_tokens * cfg->top_k),
                                              static_cast<int>(cfg->local_start), static_cast<int>(cfg->local_count),
-                                             cnt, off, perm, inv));
+                                             cnt, off, perm, inv, x, xh, n_tokens, static_cast<int>(cfg->hidden)));
 }
 
 constexpr int FUSED_ROUTE_MAX_TOKENS = 32;  // up to here one CTA routes and sorts in a single launch
 
 static int launch_route_sort(const MskMoeCfg* cfg, const float* logits, const float* bias, int32_t* ids, float* tw,
-                             int n_tokens, int32_t* cnt, int32_t* off, int32_t* perm, int32_t* inv, cudaStream_t st) {
+                             int n_tokens, int32_t* cnt, int32_t* off, int32_t* perm, int32_t* inv, cudaStream_t st,
+                             const __nv_bfloat16* x, __half* xh) {
   static bool attr_set[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -600,7 +602,7 @@ static int launch_route_sort(const MskMoeCfg* cfg, const float* logits, const fl
                                              static_cast<int>(cfg->n_experts), static_cast<int>(cfg->top_k),
                                              static_cast<int>(cfg->routing_mode), cfg->route_scale,
                                              static_cast<int>(cfg->local_start), static_cast<int>(cfg->local_count),
-                                             cnt, off, perm, inv));
+                                             cnt, off, perm, inv, x, xh, static_cast<int>(cfg->hidden)));
 }
 
 int msk_moe_sort(const MskMoeCfg* cfg, const int32_t* topk_ids, int n_tokens, int32_t* cnt, int32_t* off,
@@ -706,8 +708,13 @@ static int forward_impl(const MskMoeCfg* cfg, const void* packed13, const void* 
 
   if (ev) cudaEventRecord(ev[0], st);
   int e = 0;
+  // narrow token tiles read an F16 copy of x; for few tokens the sorting CTA makes it
+  const bool tma_b = plan.N >= 64;  // GemmCfg<N>::TMA_B
+  const bool convert_in_sort = !tma_b && n_tokens <= FUSED_ROUTE_MAX_TOKENS;
+  const __nv_bfloat16* xin = convert_in_sort ? static_cast<const __nv_bfloat16*>(x) : nullptr;
+  __half* xh_in_sort = convert_in_sort ? xs : nullptr;
   if (logits != nullptr && n_tokens <= FUSED_ROUTE_MAX_TOKENS) {
-    e = launch_route_sort(cfg, logits, bias, ids_out, tw_out, n_tokens, cnt, off, perm, inv, st);
+    e = launch_route_sort(cfg, logits, bias, ids_out, tw_out, n_tokens, cnt, off, perm, inv, st, xin, xh_in_sort);
   } else {
     if (logits != nullptr) {
       route_topk_kernel<<<static_cast<unsigned>((n_tokens + 7) / 8), 256, 0, st>>>(
@@ -715,7 +722,7 @@ static int forward_impl(const MskMoeCfg* cfg, const void* packed13, const void* 
       e = static_cast<int>(cudaGetLastError());
       if (e != 0) return e;
     }
-    e = launch_sort(cfg, topk_ids, n_tokens, cnt, off, perm, inv, st);
+    e = launch_sort(cfg, topk_ids, n_tokens, cnt, off, perm, inv, st, xin, xh_in_sort);
   }
   if (e != 0) return e;
   if (ev) cudaEventRecord(ev[1], st);
@@ -731,11 +738,11 @@ static int forward_impl(const MskMoeCfg* cfg, const void* packed13, const void* 
   // so the weights must not be the ones L2 keeps
   p.evict_first = 1;
 
-  const bool tma_b = plan.N >= 64;  // GemmCfg<N>::TMA_B
   const size_t r_max = static_cast<size_t>(cfg->max_tokens) * cfg->top_k;
   p.w = static_cast<const uint8_t*>(packed13); p.gs = gs13; p.act = x; p.outp = inter; p.post_norm_w = nullptr;
   p.K = cfg->hidden; p.out_ld = cfg->inter; p.n_pairs = cfg->inter / 128; p.splits = plan.s13;
-  {
+  p.act = xs;
+  if (!convert_in_sort) {
     // F16 copy of the token rows: sorted (expert-major) for the TMA tiles, plain [T, H] otherwise
     cudaLaunchConfig_t lc{};
     lc.gridDim = dim3(static_cast<unsigned>(tma_b ? n_tokens * cfg->top_k : n_tokens));

@@ -3,7 +3,10 @@
 #pragma once
 #include <cstdint>
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
+
+#include "layout.cuh"
 
 namespace msk {
 
@@ -220,13 +223,30 @@ __device__ void sort_entries_block(SortSmem& sm, const int32_t* ids, int n, int 
   }
 }
 
+// F16 copy of the token rows by the sorting CTA (small token counts only: saves a launch in the
+// decode chain). xh may be null.
+__device__ __forceinline__ void convert_rows_block(const __nv_bfloat16* __restrict__ x, __half* __restrict__ xh,
+                                                   int T, int H) {
+  if (xh == nullptr) return;
+  const uint4* src = reinterpret_cast<const uint4*>(x);
+  uint4* dst = reinterpret_cast<uint4*>(xh);
+  const int n = T * (H / 8);
+  for (int i = threadIdx.x; i < n; i += SORT_THREADS) {
+    const uint4 v = src[i];
+    dst[i] = make_uint4(bf16x2_to_f16x2(v.x), bf16x2_to_f16x2(v.y), bf16x2_to_f16x2(v.z), bf16x2_to_f16x2(v.w));
+  }
+}
+
 __global__ void __launch_bounds__(SORT_THREADS) sort_kernel(const int32_t* __restrict__ ids, int n, int lo, int nloc,
                                                             int32_t* __restrict__ cnt, int32_t* __restrict__ off,
-                                                            int32_t* __restrict__ perm, int32_t* __restrict__ inv) {
+                                                            int32_t* __restrict__ perm, int32_t* __restrict__ inv,
+                                                            const __nv_bfloat16* __restrict__ x,
+                                                            __half* __restrict__ xh, int T, int H) {
   extern __shared__ __align__(16) unsigned char sort_smem_raw[];
   SortSmem& sm = *reinterpret_cast<SortSmem*>(sort_smem_raw);
   asm volatile("griddepcontrol.wait;" ::: "memory");               // topk_ids may come from the kernel before
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // let the GEMM kernel set itself up meanwhile
+  convert_rows_block(x, xh, T, H);
   sort_entries_block(sm, ids, n, lo, nloc, cnt, off, perm, inv);
 }
 
@@ -238,11 +258,14 @@ __global__ void __launch_bounds__(SORT_THREADS) route_sort_kernel(const float* _
                                                                   int T, int E, int k, int mode, float scale, int lo,
                                                                   int nloc, int32_t* __restrict__ cnt,
                                                                   int32_t* __restrict__ off, int32_t* __restrict__ perm,
-                                                                  int32_t* __restrict__ inv) {
+                                                                  int32_t* __restrict__ inv,
+                                                                  const __nv_bfloat16* __restrict__ x,
+                                                                  __half* __restrict__ xh, int H) {
   extern __shared__ __align__(16) unsigned char sort_smem_raw[];
   SortSmem& sm = *reinterpret_cast<SortSmem*>(sort_smem_raw);
   asm volatile("griddepcontrol.wait;" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  convert_rows_block(x, xh, T, H);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   for (int t = warp; t < T; t += SORT_WARPS)
     route_token_dispatch(logits + static_cast<size_t>(t) * E, bias, ids + static_cast<size_t>(t) * k,
