@@ -185,6 +185,14 @@ int msk_moe_read_status(const void* workspace, int* host_status, void* stream);
  * 2 gate/up GEMM, 3 down GEMM, 4 combine. host_out: int[4] = regs, static smem, max dyn smem, local. */
 int msk_moe_attrs(int which, int token_tile, int* host_out);
 
+/* Expert-parallel combine at a token's home rank: out[t] = bf16(sum over ranks d in rank order of
+ * back[d, pos[d, t]] where mask[d, t] != 0), FP32 accumulation. back: bf16 [n_ranks, capacity, hidden]
+ * (the partial rows every rank sent back); mask: uint8 [n_ranks, n_tokens]; pos: int64 [n_ranks,
+ * n_tokens]. No counterpart in the reference, which stops at per-rank partial sums and leaves the
+ * exchange to its caller (muse_moe_w4a16/cuda/moe.cu:347-350, 2604). */
+int msk_ep_combine(const void* back, const uint8_t* mask, const int64_t* pos, void* out, int n_ranks, int n_tokens,
+                   int capacity, int hidden, void* stream);
+
 /* HBM streaming probe: every CTA pulls its share of `bytes` from `src` through a ring of
  * bulk async copies, as the GEMM kernel's weight producer does, and adds a checksum to
  * sink[0] (twin of muse_moe_w4a16/cuda/moe_bw.cu). */

@@ -210,6 +210,40 @@ __global__ void __launch_bounds__(COMBINE_THREADS) combine_kernel(const float* _
   }
 }
 
+// ------------------------------------------------------------- EP combine
+// Expert-parallel combine at the token's home rank: out[t] = bf16( sum over ranks d, in rank
+// order, of back[d, pos[d, t]] where mask[d, t] ), FP32 accumulation. back holds the partial rows
+// returned by every rank (equal-split buffers [n, C, H]); pos/mask are the dispatch plan.
+__global__ void __launch_bounds__(256) ep_combine_kernel(const __nv_bfloat16* __restrict__ back,
+                                                         const uint8_t* __restrict__ mask,
+                                                         const int64_t* __restrict__ pos,
+                                                         __nv_bfloat16* __restrict__ out, int n, int T, int C, int H) {
+  const int t = blockIdx.x;
+  const int n8 = H / 8;
+  for (int i = threadIdx.x; i < n8; i += 256) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int d = 0; d < n; ++d) {
+      if (!mask[static_cast<size_t>(d) * T + t]) continue;
+      const size_t row = static_cast<size_t>(d) * C + static_cast<size_t>(pos[static_cast<size_t>(d) * T + t]);
+      const uint4 v = *reinterpret_cast<const uint4*>(back + row * H + static_cast<size_t>(i) * 8);
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        acc[2 * j] += __uint_as_float(w[j] << 16);
+        acc[2 * j + 1] += __uint_as_float(w[j] & 0xFFFF0000u);
+      }
+    }
+    uint4 o;
+    uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const __nv_bfloat162 h = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+      ow[j] = *reinterpret_cast<const uint32_t*>(&h);
+    }
+    *reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * H + static_cast<size_t>(i) * 8) = o;
+  }
+}
+
 // --------------------------------------------------------------- bw probe
 // Every CTA streams its contiguous share of the buffer through a ring of bulk async
 // copies, one elected thread issuing, one warp consuming (twin of the reference's
@@ -990,6 +1024,18 @@ int msk_moe_attrs(int which, int token_tile, int* host_out) {
   host_out[2] = a.maxDynamicSharedSizeBytes;
   host_out[3] = static_cast<int>(a.localSizeBytes);
   return MSK_OK;
+}
+
+int msk_ep_combine(const void* back, const uint8_t* mask, const int64_t* pos, void* out, int n_ranks, int n_tokens,
+                   int capacity, int hidden, void* stream) {
+  if (!back || !mask || !pos || !out) return MSK_ERR_NULL;
+  if (n_ranks < 1 || n_tokens < 0 || capacity < 1 || hidden < 8 || hidden % 8 != 0) return MSK_ERR_SHAPE;
+  if (!aligned16(back) || !aligned16(out)) return MSK_ERR_ALIGN;
+  if (n_tokens == 0) return MSK_OK;
+  ep_combine_kernel<<<static_cast<unsigned>(n_tokens), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(back), mask, pos, static_cast<__nv_bfloat16*>(out), n_ranks, n_tokens, capacity,
+      hidden);
+  return static_cast<int>(cudaGetLastError());
 }
 
 int msk_bw_probe(const void* src, size_t bytes, int stages, int stage_bytes, int num_ctas, uint32_t* sink,

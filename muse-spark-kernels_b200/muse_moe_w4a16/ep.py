@@ -65,7 +65,26 @@ def ep_step(x, ids, weights, expert_fn, experts_per_rank, group=None):
     recv_w = _a2a(send_w.contiguous(), group).view(n * T, k)
     partial = expert_fn(recv_x, recv_ids, recv_w)                            # [n*T, H] bf16
     back = _a2a(partial.view(n, T, H).contiguous(), group)                   # back[d, p]: rank d's partial of my row p
-    out = torch.zeros((T, H), dtype=torch.float32, device=x.device)
+    return combine_partials(back, mask, pos)
+
+
+def combine_partials(back, mask, pos):
+    """out[t] = bf16(sum over ranks d, in rank order, of back[d, pos[d, t]] where mask[d, t]), FP32
+    accumulation. On CUDA tensors this is one library kernel (msk_ep_combine); the torch loop
+    below is the same arithmetic for the CPU (gloo) tests."""
+    n, T, H = back.shape
+    if back.is_cuda:
+        import ctypes
+
+        from . import _lib
+
+        out = torch.empty((T, H), dtype=torch.bfloat16, device=back.device)
+        m8 = mask.to(torch.uint8).contiguous()
+        p64 = pos.contiguous()
+        _lib.check(_lib.load().msk_ep_combine(_lib.ptr(back), _lib.ptr(m8), _lib.ptr(p64), _lib.ptr(out), n, T, T, H,
+                                              ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)), "msk_ep_combine")
+        return out
+    out = torch.zeros((T, H), dtype=torch.float32, device=back.device)
     rows = torch.where(mask, pos, torch.zeros_like(pos))                     # [n, T]
     for d in range(n):                                                       # rank order, FP32
         out += back[d][rows[d]].float() * mask[d].unsqueeze(-1)

@@ -208,3 +208,20 @@ def test_forward_decode_shape_T1_and_T8(cuda_dev):
     for T in (1, 8):
         out, ref, parts, views, st, _ = _run_forward(m, inputs, orc, cuda_dev, 4096, 1536, 16, 8, T, seed=10 + T)
         _check_forward(out, ref, parts, views)
+
+
+def test_ep_combine_kernel_matches_rank_order_sum(cuda_dev):
+    """msk_ep_combine against the same rank-order FP32 sum in torch (bit-exact: same order, same
+    arithmetic)."""
+    from muse_moe_w4a16 import ep
+
+    n, T, H = 4, 300, 512
+    g = torch.Generator(device=cuda_dev).manual_seed(9)
+    back = torch.randn((n, T, H), generator=g, device=cuda_dev).to(torch.bfloat16)
+    mask = torch.rand((n, T), generator=g, device=cuda_dev) < 0.6
+    mask[:, 0] = False  # a token with no route anywhere sums to zero
+    pos = mask.long().cumsum(1) - 1
+    got = ep.combine_partials(back, mask, pos)
+    want = ep.combine_partials(back.cpu(), mask.cpu(), pos.cpu())
+    assert torch.equal(got.cpu(), want)
+    assert float(got[0].float().abs().max()) == 0.0
