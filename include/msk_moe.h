@@ -185,13 +185,23 @@ int msk_moe_read_status(const void* workspace, int* host_status, void* stream);
  * 2 gate/up GEMM, 3 down GEMM, 4 combine. host_out: int[4] = regs, static smem, max dyn smem, local. */
 int msk_moe_attrs(int which, int token_tile, int* host_out);
 
-/* Expert-parallel combine at a token's home rank: out[t] = bf16(sum over ranks d in rank order of
- * back[d, pos[d, t]] where mask[d, t] != 0), FP32 accumulation. back: bf16 [n_ranks, capacity, hidden]
- * (the partial rows every rank sent back); mask: uint8 [n_ranks, n_tokens]; pos: int64 [n_ranks,
- * n_tokens]. No counterpart in the reference, which stops at per-rank partial sums and leaves the
- * exchange to its caller (muse_moe_w4a16/cuda/moe.cu:347-350, 2604). */
-int msk_ep_combine(const void* back, const uint8_t* mask, const int64_t* pos, void* out, int n_ranks, int n_tokens,
-                   int capacity, int hidden, void* stream);
+/* Expert-parallel combine at a token's home rank: out[t] = bf16(sum over ranks d, in rank order, of
+ * the partial row rank d returned for token t), FP32 accumulation; rank d contributes only when one
+ * of the token's ids lies in [d*experts_per_rank, (d+1)*experts_per_rank). back: bf16 [n_ranks,
+ * n_tokens, hidden] in rank order; self_rows (may be NULL): the home rank's own partial rows,
+ * read instead of back[self_rank]; ids: int32 [n_tokens, top_k] (global ids). n_ranks <= 64.
+ * No counterpart in the reference, which stops at per-rank partial sums and leaves the exchange
+ * to its caller (muse_moe_w4a16/cuda/moe.cu:347-350, 2604). */
+int msk_ep_combine(const void* back, const void* self_rows, int self_rank, const int32_t* ids, int top_k,
+                   int experts_per_rank, void* out, int n_ranks, int n_tokens, int hidden, void* stream);
+
+/* Cross-rank flags of the expert-parallel step, as stream memory operations (no kernel, no SM):
+ * write `value` to a 32-bit word (this GPU's or a peer-mapped one) once all earlier work of the
+ * stream is done and visible; make the stream wait until a word of this GPU is >= value. The wait
+ * is unbounded by design of the driver call: callers pair every wait with a write that a live
+ * peer is certain to issue, and run under a host-side time-out. No counterpart in the reference. */
+int msk_ep_flag_write(void* addr, uint32_t value, void* stream);
+int msk_ep_flag_wait(void* addr, uint32_t value, void* stream);
 
 /* HBM streaming probe: every CTA pulls its share of `bytes` from `src` through a ring of
  * bulk async copies, as the GEMM kernel's weight producer does, and adds a checksum to

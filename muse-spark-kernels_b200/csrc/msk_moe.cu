@@ -127,46 +127,65 @@ __global__ void __launch_bounds__(256) gather_rows_kernel(const __nv_bfloat16* _
 // eight warp partials, so the result does not depend on scheduling.
 constexpr int COMBINE_THREADS = 512;
 constexpr int COMBINE_MAX_F4 = 4;   // float4 per thread per row: H <= 8192
-constexpr int COMBINE_GROUP = 4;    // slots whose rows are loaded together
+constexpr int COMBINE_WIDE_TOKENS = 512;  // from here on two blocks per SM, two slots per group
 
-__global__ void __launch_bounds__(COMBINE_THREADS) combine_kernel(const float* __restrict__ y,
-                                                                  const int32_t* __restrict__ inv,
-                                                                  const float* __restrict__ tw,
-                                                                  __nv_bfloat16* __restrict__ out, int H, int k,
-                                                                  int post_norm, float eps) {
-  __shared__ float wsum[COMBINE_GROUP][COMBINE_THREADS / 32];
+// G = slots whose rows are loaded together (one memory latency per group instead of one per
+// slot; the sums still run in slot order). G = 4 for few tokens (latency), G = 2 with two blocks
+// per SM for many (one block's loads overlap the other's reduction and stores). Slots without a
+// local route (inv < 0) are squeezed out first, keeping their order, so an expert-parallel rank
+// that owns one or two of a token's eight routes pays for one group, and a token without any
+// local route only writes zeros.
+template <int G>
+__global__ void __launch_bounds__(COMBINE_THREADS, G == 2 ? 2 : 1)
+    combine_kernel(const float* __restrict__ y, const int32_t* __restrict__ inv, const float* __restrict__ tw,
+                   __nv_bfloat16* __restrict__ out, int H, int k, int post_norm, float eps) {
+  __shared__ float wsum[G][COMBINE_THREADS / 32];
+  __shared__ int s_q[MAX_TOP_K];
+  __shared__ float s_w[MAX_TOP_K];
+  __shared__ int s_n;
   const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   pdl_wait();  // y and inv come from the kernels before this one
+  if (warp == 0) {  // lane s takes slot s (k <= 16); a ballot keeps the order
+    const int q = lane < k ? inv[static_cast<size_t>(t) * k + lane] : -1;
+    const float w = lane < k ? tw[static_cast<size_t>(t) * k + lane] : 0.f;
+    const unsigned have = __ballot_sync(0xffffffffu, q >= 0);
+    if (q >= 0) {
+      const int at = __popc(have & ((1u << lane) - 1u));
+      s_q[at] = q;
+      s_w[at] = w;
+    }
+    if (lane == 0) s_n = __popc(have);
+  }
+  __syncthreads();
+  const int nv = s_n;
   const int n4 = H / 4;  // float4 per row; thread tid owns indices i*512 + tid
   float4 acc[COMBINE_MAX_F4];
 #pragma unroll
   for (int i = 0; i < COMBINE_MAX_F4; ++i) acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-  // Slots are taken COMBINE_GROUP at a time so that their row loads are in flight together (one
-  // memory latency per group instead of one per slot); the sums still run in slot order.
-  for (int s0 = 0; s0 < k; s0 += COMBINE_GROUP) {
-    int q[COMBINE_GROUP];
-    float wgt[COMBINE_GROUP];
+  for (int s0 = 0; s0 < nv; s0 += G) {
+    int q[G];
+    float wgt[G];
 #pragma unroll
-    for (int g = 0; g < COMBINE_GROUP; ++g) {
-      const bool in = s0 + g < k;
-      q[g] = in ? inv[static_cast<size_t>(t) * k + s0 + g] : -1;
-      wgt[g] = in ? tw[static_cast<size_t>(t) * k + s0 + g] : 0.f;
+    for (int g = 0; g < G; ++g) {
+      const bool in = s0 + g < nv;
+      q[g] = in ? s_q[s0 + g] : -1;
+      wgt[g] = in ? s_w[s0 + g] : 0.f;
     }
-    float4 v[COMBINE_GROUP][COMBINE_MAX_F4];
-    float ss[COMBINE_GROUP];
+    float4 v[G][COMBINE_MAX_F4];
+    float ss[G];
 #pragma unroll
-    for (int g = 0; g < COMBINE_GROUP; ++g) {
+    for (int g = 0; g < G; ++g) {
       ss[g] = 0.f;
       const float4* row = reinterpret_cast<const float4*>(y + static_cast<size_t>(q[g] < 0 ? 0 : q[g]) * H);
 #pragma unroll
       for (int i = 0; i < COMBINE_MAX_F4; ++i) {
         v[g][i] = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (q[g] >= 0 && i * COMBINE_THREADS + tid < n4) v[g][i] = row[i * COMBINE_THREADS + tid];
+        if (q[g] >= 0 && i * COMBINE_THREADS + tid < n4) v[g][i] = __ldcs(row + i * COMBINE_THREADS + tid);
       }
     }
     if (post_norm) {
 #pragma unroll
-      for (int g = 0; g < COMBINE_GROUP; ++g) {
+      for (int g = 0; g < G; ++g) {
 #pragma unroll
         for (int i = 0; i < COMBINE_MAX_F4; ++i)
           ss[g] += v[g][i].x * v[g][i].x + v[g][i].y * v[g][i].y + v[g][i].z * v[g][i].z + v[g][i].w * v[g][i].w;
@@ -176,11 +195,11 @@ __global__ void __launch_bounds__(COMBINE_THREADS) combine_kernel(const float* _
       __syncthreads();  // wsum of the previous group fully read
       if (lane == 0) {
 #pragma unroll
-        for (int g = 0; g < COMBINE_GROUP; ++g) wsum[g][warp] = ss[g];
+        for (int g = 0; g < G; ++g) wsum[g][warp] = ss[g];
       }
       __syncthreads();
 #pragma unroll
-      for (int g = 0; g < COMBINE_GROUP; ++g) {
+      for (int g = 0; g < G; ++g) {
         float tot = 0.f;
 #pragma unroll
         for (int w = 0; w < COMBINE_THREADS / 32; ++w) tot += wsum[g][w];  // fixed order
@@ -188,7 +207,7 @@ __global__ void __launch_bounds__(COMBINE_THREADS) combine_kernel(const float* _
       }
     }
 #pragma unroll
-    for (int g = 0; g < COMBINE_GROUP; ++g) {  // slot order within the group
+    for (int g = 0; g < G; ++g) {  // slot order within the group
       if (q[g] < 0) continue;
 #pragma unroll
       for (int i = 0; i < COMBINE_MAX_F4; ++i) {
@@ -212,20 +231,33 @@ __global__ void __launch_bounds__(COMBINE_THREADS) combine_kernel(const float* _
 
 // ------------------------------------------------------------- EP combine
 // Expert-parallel combine at the token's home rank: out[t] = bf16( sum over ranks d, in rank
-// order, of back[d, pos[d, t]] where mask[d, t] ), FP32 accumulation. back holds the partial rows
-// returned by every rank (equal-split buffers [n, C, H]); pos/mask are the dispatch plan.
+// order, of the partial row rank d returned for token t ), FP32 accumulation. Rank d contributes
+// only when one of the token's top-k ids lies in d's expert range, so rows of ranks without a
+// route are never read. back is [n, T, H] in rank order; the home rank's own partial may live
+// elsewhere (self_rows).
 __global__ void __launch_bounds__(256) ep_combine_kernel(const __nv_bfloat16* __restrict__ back,
-                                                         const uint8_t* __restrict__ mask,
-                                                         const int64_t* __restrict__ pos,
-                                                         __nv_bfloat16* __restrict__ out, int n, int T, int C, int H) {
+                                                         const __nv_bfloat16* __restrict__ self_rows, int self_rank,
+                                                         const int32_t* __restrict__ ids, int top_k, int per_rank,
+                                                         __nv_bfloat16* __restrict__ out, int n, int T, int H) {
+  __shared__ unsigned long long present;
   const int t = blockIdx.x;
+  if (threadIdx.x == 0) present = 0ull;
+  __syncthreads();
+  if (threadIdx.x < top_k) {
+    const int id = ids[static_cast<size_t>(t) * top_k + threadIdx.x];
+    if (id >= 0 && id / per_rank < n) atomicOr(&present, 1ull << (id / per_rank));
+  }
+  __syncthreads();
+  const unsigned long long have = present;
   const int n8 = H / 8;
   for (int i = threadIdx.x; i < n8; i += 256) {
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     for (int d = 0; d < n; ++d) {
-      if (!mask[static_cast<size_t>(d) * T + t]) continue;
-      const size_t row = static_cast<size_t>(d) * C + static_cast<size_t>(pos[static_cast<size_t>(d) * T + t]);
-      const uint4 v = *reinterpret_cast<const uint4*>(back + row * H + static_cast<size_t>(i) * 8);
+      if (!((have >> d) & 1ull)) continue;
+      const __nv_bfloat16* rows = (d == self_rank && self_rows != nullptr)
+                                      ? self_rows
+                                      : back + static_cast<size_t>(d) * T * static_cast<size_t>(H);
+      const uint4 v = *reinterpret_cast<const uint4*>(rows + static_cast<size_t>(t) * H + static_cast<size_t>(i) * 8);
       const uint32_t w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
@@ -242,6 +274,21 @@ __global__ void __launch_bounds__(256) ep_combine_kernel(const __nv_bfloat16* __
     }
     *reinterpret_cast<uint4*>(out + static_cast<size_t>(t) * H + static_cast<size_t>(i) * 8) = o;
   }
+}
+
+// Stream memory operations (executed by the stream's front end, no SM): the cross-rank flags of
+// the expert-parallel step. Looked up through the runtime, like the tensor-map encoder.
+typedef CUresult (*StreamValue32Fn)(CUstream, CUdeviceptr, cuuint32_t, unsigned int);
+
+static int stream_value32(const char* name, void* addr, uint32_t value, unsigned int flags, void* stream) {
+  void* ptr = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  const cudaError_t e = cudaGetDriverEntryPoint(name, &ptr, cudaEnableDefault, &qres);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (qres != cudaDriverEntryPointSuccess || ptr == nullptr) return static_cast<int>(cudaErrorNotSupported);
+  const CUresult r = reinterpret_cast<StreamValue32Fn>(ptr)(static_cast<CUstream>(stream),
+                                                            reinterpret_cast<CUdeviceptr>(addr), value, flags);
+  return r == CUDA_SUCCESS ? 0 : static_cast<int>(cudaErrorInvalidValue);
 }
 
 // --------------------------------------------------------------- bw probe
@@ -828,7 +875,8 @@ static int forward_impl(const MskMoeCfg* cfg, const void* packed13, const void* 
     at[0].val.programmaticStreamSerializationAllowed = 1;
     lc.attrs = at;
     lc.numAttrs = 1;
-    e = static_cast<int>(cudaLaunchKernelEx(&lc, combine_kernel, static_cast<const float*>(y),
+    auto* kern = n_tokens >= COMBINE_WIDE_TOKENS ? combine_kernel<2> : combine_kernel<4>;
+    e = static_cast<int>(cudaLaunchKernelEx(&lc, kern, static_cast<const float*>(y),
                                             static_cast<const int32_t*>(inv), topk_weights,
                                             static_cast<__nv_bfloat16*>(out), static_cast<int>(cfg->hidden),
                                             static_cast<int>(cfg->top_k), post_norm_w != nullptr ? 1 : 0,
@@ -972,7 +1020,7 @@ int msk_moe_forward_static(const MskMoeCfg* cfg, const void* packed13, const voi
   p.K = cfg->inter; p.out_ld = cfg->hidden; p.n_pairs = cfg->hidden / 256;
   e = launch_gemm_n<1>(16, p, grid, st);
   if (e != 0) return e;
-  combine_kernel<<<static_cast<unsigned>(n_tokens), COMBINE_THREADS, 0, st>>>(
+  combine_kernel<4><<<static_cast<unsigned>(n_tokens), COMBINE_THREADS, 0, st>>>(
       y, inv, topk_weights, static_cast<__nv_bfloat16*>(out), cfg->hidden, cfg->top_k, post_norm_w != nullptr ? 1 : 0,
       cfg->post_norm_eps);
   return static_cast<int>(cudaGetLastError());
@@ -1015,7 +1063,7 @@ int msk_moe_attrs(int which, int token_tile, int* host_out) {
       }
       break;
     }
-    case 4: e = cudaFuncGetAttributes(&a, combine_kernel); break;
+    case 4: e = cudaFuncGetAttributes(&a, combine_kernel<4>); break;
     default: return MSK_ERR_SHAPE;
   }
   if (e != cudaSuccess) return static_cast<int>(e);
@@ -1026,16 +1074,30 @@ int msk_moe_attrs(int which, int token_tile, int* host_out) {
   return MSK_OK;
 }
 
-int msk_ep_combine(const void* back, const uint8_t* mask, const int64_t* pos, void* out, int n_ranks, int n_tokens,
-                   int capacity, int hidden, void* stream) {
-  if (!back || !mask || !pos || !out) return MSK_ERR_NULL;
-  if (n_ranks < 1 || n_tokens < 0 || capacity < 1 || hidden < 8 || hidden % 8 != 0) return MSK_ERR_SHAPE;
-  if (!aligned16(back) || !aligned16(out)) return MSK_ERR_ALIGN;
+int msk_ep_combine(const void* back, const void* self_rows, int self_rank, const int32_t* ids, int top_k,
+                   int experts_per_rank, void* out, int n_ranks, int n_tokens, int hidden, void* stream) {
+  if (!back || !ids || !out) return MSK_ERR_NULL;
+  if (n_ranks < 1 || n_ranks > 64 || n_tokens < 0 || hidden < 8 || hidden % 8 != 0 || top_k < 1 ||
+      top_k > MAX_TOP_K || experts_per_rank < 1)
+    return MSK_ERR_SHAPE;
+  if (!aligned16(back) || !aligned16(out) || (self_rows && !aligned16(self_rows))) return MSK_ERR_ALIGN;
   if (n_tokens == 0) return MSK_OK;
   ep_combine_kernel<<<static_cast<unsigned>(n_tokens), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(back), mask, pos, static_cast<__nv_bfloat16*>(out), n_ranks, n_tokens, capacity,
-      hidden);
+      static_cast<const __nv_bfloat16*>(back), static_cast<const __nv_bfloat16*>(self_rows), self_rank, ids, top_k,
+      experts_per_rank, static_cast<__nv_bfloat16*>(out), n_ranks, n_tokens, hidden);
   return static_cast<int>(cudaGetLastError());
+}
+
+int msk_ep_flag_write(void* addr, uint32_t value, void* stream) {
+  if (!addr) return MSK_ERR_NULL;
+  if (reinterpret_cast<uintptr_t>(addr) % 4 != 0) return MSK_ERR_ALIGN;
+  return stream_value32("cuStreamWriteValue32", addr, value, CU_STREAM_WRITE_VALUE_DEFAULT, stream);
+}
+
+int msk_ep_flag_wait(void* addr, uint32_t value, void* stream) {
+  if (!addr) return MSK_ERR_NULL;
+  if (reinterpret_cast<uintptr_t>(addr) % 4 != 0) return MSK_ERR_ALIGN;
+  return stream_value32("cuStreamWaitValue32", addr, value, CU_STREAM_WAIT_VALUE_GEQ, stream);
 }
 
 int msk_bw_probe(const void* src, size_t bytes, int stages, int stage_bytes, int num_ctas, uint32_t* sink,

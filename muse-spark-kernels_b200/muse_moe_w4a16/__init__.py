@@ -113,8 +113,9 @@ def _route(data, state, x, T):
     return ids, tw
 
 
-def kernel_fn(data, state, return_routing=False):
-    """One routed-expert step. Fresh bf16 [T, H] output per call; launches only."""
+def kernel_fn(data, state, return_routing=False, out=None):
+    """One routed-expert step. Fresh bf16 [T, H] output per call (or `out`, a contiguous bf16 [T, H]
+    CUDA tensor of the caller); launches only."""
     cfg, lib = state["cfg"], state["lib"].lib
     x = data["hidden_states"].contiguous()
     if not x.is_cuda or x.dtype != torch.bfloat16:
@@ -123,7 +124,11 @@ def kernel_fn(data, state, return_routing=False):
     dcfg = data.get("config")
     if dcfg is not None and (dcfg["local_start"] != state["lo"] or dcfg["local_count"] != state["cnt"]):
         raise RuntimeError("muse_moe_w4a16.kernel_fn: config local range differs from the prepared state")
-    out = torch.empty((T, cfg.hidden), dtype=torch.bfloat16, device=x.device)
+    if out is None:
+        out = torch.empty((T, cfg.hidden), dtype=torch.bfloat16, device=x.device)
+    elif (not out.is_cuda or out.dtype != torch.bfloat16 or not out.is_contiguous()
+          or tuple(out.shape) != (T, cfg.hidden)):
+        raise RuntimeError("muse_moe_w4a16.kernel_fn: out must be a contiguous CUDA bfloat16 [T, H] tensor")
     logits = _logits(data, state, x, T)
     if logits is None:
         ids = data["topk_ids"].to(torch.int32).contiguous()

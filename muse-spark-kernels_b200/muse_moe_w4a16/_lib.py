@@ -77,7 +77,9 @@ SIGNATURES = {
     "msk_moe_workspace_view": [_CFG, _P, ctypes.c_int, ctypes.POINTER(_P)],
     "msk_moe_read_status": [_P, _INTP, _P],
     "msk_moe_attrs": [ctypes.c_int, ctypes.c_int, _INTP],
-    "msk_ep_combine": [_P, _P, _P, _P, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, _P],
+    "msk_ep_combine": [_P, _P, ctypes.c_int, _P, ctypes.c_int, ctypes.c_int, _P, ctypes.c_int, ctypes.c_int, ctypes.c_int, _P],
+    "msk_ep_flag_write": [_P, ctypes.c_uint32, _P],
+    "msk_ep_flag_wait": [_P, ctypes.c_uint32, _P],
     "msk_bw_probe": [_P, ctypes.c_size_t, ctypes.c_int, ctypes.c_int, ctypes.c_int, _P, _P],
 }
 

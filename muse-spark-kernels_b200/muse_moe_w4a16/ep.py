@@ -1,22 +1,31 @@
-"""Expert parallelism for the routed-expert step: token dispatch and combine over all-to-all.
+"""Expert parallelism for the routed-expert step.
 
 Rank r of n owns experts [r*E/n, (r+1)*E/n) (the reference's `local_start / local_count`
 convention, muse_moe_w4a16/py/00_moe_w4a16.py:108-109; the reference itself only filters ids
 and leaves the exchange to its caller, muse_moe_w4a16/cuda/moe.cu:347-350). Every rank holds
 T tokens. One step:
-  1. routing on the local tokens (ids, weights);
-  2. dispatch: for each destination rank the tokens with at least one expert there, compacted
-     in token order, travel with their ids/weights rows in equal-split buffers [n, C, ...],
-     C = T (a token goes to a rank at most once, so nothing is ever dropped); unused rows carry
-     ids = -1 and are ignored by the destination's sort. Equal splits need no host-side sizes:
-     the step has no host synchronisation;
-  3. the local expert step on the n*C received rows (kernel_fn with local_start), giving one
-     partial row per received token;
-  4. combine: the partial rows travel back the same way and each token sums its partial rows
-     in rank order in FP32 (deterministic).
-Collectives are torch.distributed all_to_all_single (NCCL on GPUs, over NVLink/NVSwitch; gloo in
-the CPU tests). Remote data always lands in this rank's own memory before a kernel reads it.
+  1. routing on the local tokens (global ids, weights);
+  2. dispatch: every rank receives every rank's token rows with their ids/weights rows. Sending
+     a token only to the ranks it routes to would need per-destination sizes on the host or
+     padded buffers of the same T rows per pair; with top-8 of 8 ranks two thirds of the pairs
+     are used anyway, so rows travel whole and the step has no host synchronisation;
+  3. the local expert step in the reference's filter mode: ids outside this rank's range are
+     skipped by the sort, giving one partial row per received token (zero without a route here);
+  4. combine: the partial rows return to the token's home rank, which sums them in rank order in
+     FP32 (deterministic), reading only the ranks the token routed to.
+
+Two transports:
+  * "collective": all_gather + all_to_all_single of torch.distributed (gloo in the CPU tests,
+    NCCL on GPUs), one chunk, nothing overlapped;
+  * "symm" (GPUs of one NVLink domain): buffers in symmetric memory, rows pulled from the peers
+    by the copy engines (plain device-to-device copies, no SM), cross-rank ordering by 32-bit
+    flags written and awaited with stream memory operations. The n source ranks are processed
+    in chunks, own rank first, so the expert kernels of one chunk run while the copy engines
+    fetch the next chunk and return the previous one. Remote data always lands in this rank's
+    own memory before a kernel reads it.
 """
+import ctypes
+
 import torch
 import torch.distributed as dist
 
@@ -25,89 +34,204 @@ def owner_rank(ids, experts_per_rank):
     return torch.div(ids, experts_per_rank, rounding_mode="floor")
 
 
-def plan_dispatch(ids, n_ranks, experts_per_rank):
-    """ids [T, k] (global) -> mask [n, T] (token t has a route on rank d), pos [n, T] (row of t in
-    d's buffer), src [n, T] (token stored at row p of d's buffer; rows >= count hold token 0),
-    count [n]."""
-    T = ids.shape[0]
-    dest = owner_rank(ids, experts_per_rank)                                  # [T, k]
+def route_mask(ids, n_ranks, experts_per_rank):
+    """ids [T, k] (global, negative = no route) -> bool [n, T]: token t has a route on rank d."""
+    dest = owner_rank(ids.long(), experts_per_rank)
     ranks = torch.arange(n_ranks, device=ids.device).view(n_ranks, 1, 1)
-    mask = (dest.unsqueeze(0) == ranks).any(-1)                              # [n, T]
-    pos = mask.long().cumsum(1) - 1                                          # [n, T]
-    count = mask.sum(1)
-    slot = torch.where(mask, pos, torch.full_like(pos, T))                   # row T = scratch row
-    src = torch.zeros((n_ranks, T + 1), dtype=torch.long, device=ids.device)
-    src.scatter_(1, slot, torch.arange(T, device=ids.device).expand(n_ranks, T))
-    return mask, pos, src[:, :T].contiguous(), count
+    return ((dest.unsqueeze(0) == ranks) & (ids.unsqueeze(0) >= 0)).any(-1)
 
 
-def _a2a(t, group):
-    out = torch.empty_like(t)
-    dist.all_to_all_single(out, t, group=group)
+def combine_partials(back, ids, experts_per_rank, self_rank=-1, self_rows=None):
+    """out[t] = bf16(sum over ranks d, in rank order, of rank d's partial row of token t, taken only
+    where the token routes to d), FP32 accumulation. back bf16 [n, T, H] in rank order; self_rows
+    replaces back[self_rank] when given. On CUDA tensors this is one library kernel
+    (msk_ep_combine); the torch loop is the same arithmetic for the CPU ranks of the tests."""
+    n, T, H = back.shape
+    if back.is_cuda:
+        from . import _lib
+
+        out = torch.empty((T, H), dtype=torch.bfloat16, device=back.device)
+        ids32 = ids.to(torch.int32).contiguous()
+        _lib.check(_lib.load().msk_ep_combine(_lib.ptr(back), _lib.ptr(self_rows), self_rank, _lib.ptr(ids32),
+                                              ids32.shape[1], experts_per_rank, _lib.ptr(out), n, T, H,
+                                              ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)),
+                   "msk_ep_combine")
+        return out
+    mask = route_mask(ids, n, experts_per_rank)
+    out = torch.zeros((T, H), dtype=torch.float32, device=back.device)
+    for d in range(n):                                                       # rank order, FP32
+        rows = self_rows if (d == self_rank and self_rows is not None) else back[d]
+        out += torch.where(mask[d].unsqueeze(-1), rows.float(), torch.zeros((), dtype=torch.float32))
+    return out.to(torch.bfloat16)
+
+
+def _all_gather(t, n, group):
+    out = torch.empty((n,) + tuple(t.shape), dtype=t.dtype, device=t.device)
+    if t.is_cuda:
+        dist.all_gather_into_tensor(out, t.contiguous(), group=group)
+    else:                                   # gloo: per-rank views, moved as bytes
+        dist.all_gather([out[d].view(torch.uint8) for d in range(n)], t.contiguous().view(torch.uint8), group=group)
     return out
 
 
 def ep_step(x, ids, weights, expert_fn, experts_per_rank, group=None):
-    """x bf16 [T, H], ids int [T, k] (global ids), weights fp32 [T, k]. expert_fn(rows bf16
-    [n*T, H], ids int32 [n*T, k], weights fp32 [n*T, k]) -> partial bf16 [n*T, H] computes this
-    rank's experts (ids outside its range or negative are skipped). Returns out bf16 [T, H]."""
+    """The step over torch.distributed collectives. x bf16 [T, H], ids int [T, k] (global ids),
+    weights fp32 [T, k]. expert_fn(rows bf16 [n*T, H], ids int32 [n*T, k], weights fp32 [n*T, k])
+    -> partial bf16 [n*T, H] computes this rank's experts (ids outside its range or negative are
+    skipped). Returns out bf16 [T, H]."""
     n = dist.get_world_size(group)
     T, H = x.shape
     k = ids.shape[1]
-    mask, pos, src, count = plan_dispatch(ids.long(), n, experts_per_rank)
-    valid = torch.arange(T, device=x.device).view(1, T) < count.view(n, 1)   # [n, C]
-    send_x = x[src]                                                          # [n, C, H]
-    send_ids = torch.where(valid.unsqueeze(-1), ids.to(torch.int32)[src], torch.full((1,), -1, dtype=torch.int32,
-                                                                                     device=x.device))
-    send_w = weights.float()[src]
-    recv_x = _a2a(send_x.contiguous(), group).view(n * T, H)
-    recv_ids = _a2a(send_ids.contiguous(), group).view(n * T, k)
-    recv_w = _a2a(send_w.contiguous(), group).view(n * T, k)
-    partial = expert_fn(recv_x, recv_ids, recv_w)                            # [n*T, H] bf16
-    back = _a2a(partial.view(n, T, H).contiguous(), group)                   # back[d, p]: rank d's partial of my row p
-    return combine_partials(back, mask, pos)
+    ids32 = ids.to(torch.int32)
+    rows = _all_gather(x, n, group).view(n * T, H)
+    rids = _all_gather(ids32, n, group).view(n * T, k)
+    rw = _all_gather(weights.float(), n, group).view(n * T, k)
+    partial = expert_fn(rows, rids, rw)                                      # [n*T, H] bf16
+    back = torch.empty((n, T, H), dtype=partial.dtype, device=partial.device)
+    dist.all_to_all_single(back, partial.view(n, T, H).contiguous(), group=group)   # back[d]: rank d's rows for my tokens
+    return combine_partials(back, ids32, experts_per_rank)
 
 
-def combine_partials(back, mask, pos):
-    """out[t] = bf16(sum over ranks d, in rank order, of back[d, pos[d, t]] where mask[d, t]), FP32
-    accumulation. On CUDA tensors this is one library kernel (msk_ep_combine); the torch loop
-    below is the same arithmetic for the CPU (gloo) tests."""
-    n, T, H = back.shape
-    if back.is_cuda:
-        import ctypes
+class SymmExchange:
+    """Buffers, flags and the copy stream of the "symm" transport for one rank.
+
+    Symmetric buffers (same shape on every rank, peers mapped into this address space), two
+    copies each, used by steps of alternating parity so a rank never overwrites rows a slower
+    peer may still be pulling:
+      gx/gids/gtw [2, n, T, ...]  slot 0: this rank's rows (what the peers pull); slot j: the rows
+                                  of rank (rank + j) % n, pulled by this rank;
+      part        [2, n, T, H]    slot j: this rank's partial rows for the tokens of rank
+                                  (rank + j) % n (what that rank pulls back);
+      flags       int32 [4 n]     word 2 p + b: rank p's inputs of a parity-b step are in place;
+                                  word 2 n + 2 q + b: rank q has written its partial rows for this
+                                  rank's tokens. Values are step numbers, compared with >=.
+    Why two copies are enough: a rank reaches step e + 2 only after it pulled every peer's
+    partial rows of step e + 1, and a peer produces those after its own pulls of step e + 1,
+    which its copy stream runs after its pulls of step e.
+    """
+
+    def __init__(self, rank, world, tokens, hidden, top_k, chunks, device, group=None):
+        import torch.distributed._symmetric_memory as symm
 
         from . import _lib
 
-        out = torch.empty((T, H), dtype=torch.bfloat16, device=back.device)
-        m8 = mask.to(torch.uint8).contiguous()
-        p64 = pos.contiguous()
-        _lib.check(_lib.load().msk_ep_combine(_lib.ptr(back), _lib.ptr(m8), _lib.ptr(p64), _lib.ptr(out), n, T, T, H,
-                                              ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)), "msk_ep_combine")
-        return out
-    out = torch.zeros((T, H), dtype=torch.float32, device=back.device)
-    rows = torch.where(mask, pos, torch.zeros_like(pos))                     # [n, T]
-    for d in range(n):                                                       # rank order, FP32
-        out += back[d][rows[d]].float() * mask[d].unsqueeze(-1)
-    return out.to(torch.bfloat16)
+        if world % chunks != 0:
+            raise ValueError("chunks must divide the number of ranks")
+        self.rank, self.n, self.T, self.H, self.k = rank, world, tokens, hidden, top_k
+        self.chunks, self.m = chunks, world // chunks
+        self.lib = _lib.load()
+        g = group if group is not None else dist.group.WORLD
 
+        def alloc(shape, dtype):
+            t = symm.empty(shape, dtype=dtype, device=device)
+            h = symm.rendezvous(t, g)
+            peers = [h.get_buffer(p, shape, dtype) for p in range(world)]
+            return t, h, peers
+
+        n, T, H, k = world, tokens, hidden, top_k
+        self.gx, _, self.peer_gx = alloc((2, n, T, H), torch.bfloat16)
+        self.gids, _, self.peer_gids = alloc((2, n, T, k), torch.int32)
+        self.gtw, _, self.peer_gtw = alloc((2, n, T, k), torch.float32)
+        self.part, _, self.peer_part = alloc((2, n, T, H), torch.bfloat16)
+        self.flags, hf, _ = alloc((4 * n,), torch.int32)
+        self.flags.zero_()
+        self.flag_base = [int(p) for p in hf.buffer_ptrs]
+        self.back = torch.empty((n, T, H), dtype=torch.bfloat16, device=device)
+        self.comm = torch.cuda.Stream(device)
+        self.epoch = 0
+        torch.cuda.synchronize(device)
+        dist.barrier(group)                      # every rank's flags are zero before anyone writes
+
+    def _write(self, peer, word, value, stream):
+        from . import _lib
+
+        _lib.check(self.lib.msk_ep_flag_write(ctypes.c_void_p(self.flag_base[peer] + 4 * word), value,
+                                              ctypes.c_void_p(stream.cuda_stream)), "msk_ep_flag_write")
+
+    def _wait(self, word, value, stream):
+        from . import _lib
+
+        _lib.check(self.lib.msk_ep_flag_wait(ctypes.c_void_p(self.flag_base[self.rank] + 4 * word), value,
+                                             ctypes.c_void_p(stream.cuda_stream)), "msk_ep_flag_wait")
+
+    def step(self, x, ids, tw, expert_fn, experts_per_rank):
+        """expert_fn(rows, ids, weights, out) as in ep_step, writing its partial rows into `out`."""
+        n, r, m, T, H, k = self.n, self.rank, self.m, self.T, self.H, self.k
+        self.epoch += 1
+        e, b = self.epoch, self.epoch & 1
+        gx, gids, gtw, part = self.gx[b], self.gids[b], self.gtw[b], self.part[b]
+        s0, s1 = torch.cuda.current_stream(), self.comm
+        gx[0].copy_(x)
+        gids[0].copy_(ids)
+        gtw[0].copy_(tw)
+        ev_in = torch.cuda.Event()
+        ev_in.record(s0)
+        for j in range(1, n):
+            self._write((r + j) % n, 2 * r + b, e, s0)
+        # copy stream: pull the other ranks' rows, nearest rank first
+        s1.wait_event(ev_in)
+        ready = {}
+        with torch.cuda.stream(s1):
+            for j in range(1, n):
+                p = (r + j) % n
+                self._wait(2 * p + b, e, s1)
+                gx[j].copy_(self.peer_gx[p][b, 0], non_blocking=True)
+                gids[j].copy_(self.peer_gids[p][b, 0], non_blocking=True)
+                gtw[j].copy_(self.peer_gtw[p][b, 0], non_blocking=True)
+                if (j + 1) % m == 0:
+                    ready[j // m] = torch.cuda.Event()
+                    ready[j // m].record(s1)
+        # main stream: the local expert step chunk by chunk, own rows first
+        for c in range(self.chunks):
+            if c in ready:
+                s0.wait_event(ready[c])
+            sl = slice(c * m, (c + 1) * m)
+            expert_fn(gx[sl].view(m * T, H), gids[sl].view(m * T, k), gtw[sl].view(m * T, k), part[sl].view(m * T, H))
+            for j in range(max(c * m, 1), (c + 1) * m):
+                self._write((r + j) % n, 2 * n + 2 * r + b, e, s0)
+        # copy stream: pull this rank's partial rows back, in the order the peers finish them
+        with torch.cuda.stream(s1):
+            for j in range(1, n):
+                q = (r - j) % n
+                self._wait(2 * n + 2 * q + b, e, s1)
+                self.back[q].copy_(self.peer_part[q][b, j], non_blocking=True)
+            ev_back = torch.cuda.Event()
+            ev_back.record(s1)
+        s0.wait_event(ev_back)
+        return combine_partials(self.back, gids[0], experts_per_rank, self_rank=r, self_rows=part[0])
 
 
 class EPModule:
     """prepare/kernel_fn for one rank of an expert-parallel group."""
 
-    def __init__(self, local_weights, rank, world, n_experts, top_k, tokens_per_rank, group=None, **prep):
+    def __init__(self, local_weights, rank, world, n_experts, top_k, tokens_per_rank, group=None, transport="symm",
+                 chunks=None, **prep):
         import muse_moe_w4a16 as moe
 
         self.moe, self.rank, self.world, self.group = moe, rank, world, group
         self.n_experts, self.top_k, self.per_rank = n_experts, top_k, n_experts // world
+        self.transport = transport
+        if transport == "symm":
+            # two chunks from four ranks on: half the exchange hides behind the expert kernels, and a
+            # chunk still brings enough rows per expert to fill its 128-token tiles
+            self.chunks = chunks if chunks is not None else (2 if world >= 4 and world % 2 == 0 else 1)
+            rows = (world // self.chunks) * tokens_per_rank
+        elif transport == "collective":
+            self.chunks, rows = 1, world * tokens_per_rank
+        else:
+            raise ValueError("transport must be 'symm' or 'collective'")
         self.state = moe.prepare(local_weights, local_start=rank * self.per_rank, n_experts=n_experts, top_k=top_k,
-                                 max_tokens=world * tokens_per_rank, **prep)
+                                 max_tokens=rows, **prep)
+        self.exchange = None
+        if transport == "symm":
+            dev = self.state["packed13"].device
+            self.exchange = SymmExchange(rank, world, tokens_per_rank, self.state["cfg"].hidden, top_k, self.chunks, dev,
+                                         group)
 
-    def _experts(self, rows, ids, w):
-        return self.moe.kernel_fn({"hidden_states": rows, "topk_ids": ids, "topk_weights": w}, self.state)
+    def _experts(self, rows, ids, w, out=None):
+        return self.moe.kernel_fn({"hidden_states": rows, "topk_ids": ids, "topk_weights": w}, self.state, out=out)
 
     def route(self, logits):
-        import ctypes
         from . import _lib
 
         st, T = self.state, logits.shape[0]
@@ -124,6 +248,8 @@ class EPModule:
             ids, tw = data["topk_ids"], data["topk_weights"]
         else:
             ids, tw = self.route(data["router_logits"].float().contiguous())
+        if self.exchange is not None:
+            return self.exchange.step(x, ids, tw, self._experts, self.per_rank)
         return ep_step(x, ids, tw, self._experts, self.per_rank, self.group)
 
 
@@ -191,15 +317,15 @@ def bench_ep(args, spec, dev, rank, world, metric, unit, clock_sampler_cls, load
             "data": "synthetic",
             "config": {"workload": spec["name"], "tokens_per_gpu": T, "hidden": H, "inter": I, "experts": E,
                        "top_k": k, "parallelism": f"ep{world}", "l2": "inputs and weights exceed L2 (792 MB of weights per rank at 8 ranks)",
-                       "dispatch": "all_to_all_single, equal splits C = T"},
+                       "dispatch": f"{mod.transport}, {mod.chunks} chunk(s) of source ranks"},
             "e2e": {"value": T * world * args.steps / (ms_e2e * 1e-3), "unit": unit,
                     "h2d_bytes_per_step": (T * H * 2 + T * E * 4) * world, "d2h_bytes_per_step": T * H * 2 * world,
                     "ms_per_step": ms_e2e / args.steps},
-            "gpu_launches": 5 * args.steps * world,
+            "gpu_launches": (2 + 5 * mod.chunks) * args.steps * world,
             "roofline": {"bound": "tensor", "achieved": flops / world / (ms * 1e-3) / 1e12,
                          "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
                          "frac": flops / world / (ms * 1e-3) / 1e12 / peaks["bf16_tflops_sustained"], "traffic": None,
-                         "kernel": "whole EP step per GPU (GEMMs + all-to-all)",
+                         "kernel": "whole EP step per GPU (expert kernels + exchange)",
                          "peak_source": peaks["source"] + " (sustained)"},
             "cpu_baseline": None,
             "clocks": clocks,

@@ -37,16 +37,20 @@ def _worker(rank, world, port, ret):
     w = inputs.make_weights(H, I, E, 9, dev)                      # same seed on every rank
     per = E // world
     local = {key: v[rank * per:(rank + 1) * per].contiguous() for key, v in w.items()}
-    mod = ep.EPModule(local, rank, world, E, k, T)
-    g = torch.Generator(device=dev).manual_seed(70 + rank)
-    x = torch.randn((T, H), generator=g, device=dev).to(torch.bfloat16)
-    logits = torch.randn((T, E), generator=g, device=dev)
-    out = mod.kernel_fn({"hidden_states": x, "router_logits": logits})
     full = moe.prepare(w, n_experts=E, top_k=k, max_tokens=T)
-    ref = moe.kernel_fn({"hidden_states": x, "router_logits": logits}, full)
-    torch.cuda.synchronize()
-    err = float((out.float() - ref.float()).abs().max() / ref.float().abs().max())
-    ret[rank] = (err, moe.read_status(mod.state), moe.read_status(full))
+    errs, stats = [], []
+    for transport in ("symm", "collective"):
+        mod = ep.EPModule(local, rank, world, E, k, T, transport=transport)
+        for step in range(3):                                     # both buffer parities and their reuse
+            g = torch.Generator(device=dev).manual_seed(70 + rank + 10 * step)
+            x = torch.randn((T, H), generator=g, device=dev).to(torch.bfloat16)
+            logits = torch.randn((T, E), generator=g, device=dev)
+            out = mod.kernel_fn({"hidden_states": x, "router_logits": logits})
+            ref = moe.kernel_fn({"hidden_states": x, "router_logits": logits}, full)
+            torch.cuda.synchronize()
+            errs.append(float((out.float() - ref.float()).abs().max() / ref.float().abs().max()))
+        stats.append(moe.read_status(mod.state))
+    ret[rank] = (max(errs), max(stats), moe.read_status(full))
     dist.barrier()
     dist.destroy_process_group()
 

@@ -212,16 +212,20 @@ def test_forward_decode_shape_T1_and_T8(cuda_dev):
 
 def test_ep_combine_kernel_matches_rank_order_sum(cuda_dev):
     """msk_ep_combine against the same rank-order FP32 sum in torch (bit-exact: same order, same
-    arithmetic)."""
+    arithmetic); rows of ranks a token does not route to are never read."""
     from muse_moe_w4a16 import ep
 
-    n, T, H = 4, 300, 512
+    n, T, H, k, per = 4, 300, 512, 3, 8
     g = torch.Generator(device=cuda_dev).manual_seed(9)
     back = torch.randn((n, T, H), generator=g, device=cuda_dev).to(torch.bfloat16)
-    mask = torch.rand((n, T), generator=g, device=cuda_dev) < 0.6
-    mask[:, 0] = False  # a token with no route anywhere sums to zero
-    pos = mask.long().cumsum(1) - 1
-    got = ep.combine_partials(back, mask, pos)
-    want = ep.combine_partials(back.cpu(), mask.cpu(), pos.cpu())
+    ids = torch.stack([torch.randperm(n * per, generator=g, device=cuda_dev)[:k] for _ in range(T)]).to(torch.int32)
+    ids[0] = -1  # a token with no route anywhere sums to zero
+    mask = ep.route_mask(ids, n, per)
+    poisoned = back.clone()
+    poisoned[~mask] = float("nan")
+    got = ep.combine_partials(poisoned, ids, per)
+    want = ep.combine_partials(back.cpu(), ids.cpu(), per)
     assert torch.equal(got.cpu(), want)
     assert float(got[0].float().abs().max()) == 0.0
+    own = ep.combine_partials(poisoned, ids, per, self_rank=1, self_rows=back[1].contiguous())
+    assert torch.equal(own, got)
