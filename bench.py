@@ -289,7 +289,14 @@ def run_gpu(args, spec):
     R = T * k
     plan = moe.plan(state, T)
     hbm_bound = T <= 1024
-    if hbm_bound:
+    fused = plan[0] == 8   # the single-launch kernel for up to 8 tokens: it is the whole step
+    if fused:
+        alg = sum(inputs.algorithmic_bytes(H, I, E, k, T, touched[i % POOL]) for i in range(n_prof)) / n_prof
+        achieved = alg / (k_ms[1] * 1e-3) / 1e9
+        roof = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                "frac": achieved / peaks["hbm_gbs"], "traffic": None, "kernel": "moe_small_kernel (whole step)",
+                "peak_source": peaks["source"] + " (burst copy)"}
+    elif hbm_bound:
         # gate/up GEMM: touched experts' W13 tiles + the x rows it gathers + the inter rows it writes
         alg13 = mean_touched * (2 * I * H * 0.5625 + 4) + 2.0 * T * H + 2.0 * R * I
         achieved = alg13 / (k_ms[1] * 1e-3) / 1e9
@@ -319,7 +326,7 @@ def run_gpu(args, spec):
                    "touched_experts_mean": mean_touched},
         "e2e": {"value": T * args.steps / (sum(e2e_ms) * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "ms_per_step": sum(e2e_ms) / args.steps},
-        "gpu_launches": (4 if T <= 32 else 5) * args.steps,
+        "gpu_launches": (1 if fused else 4 if T <= 32 else 5) * args.steps,
         "roofline": roof,
         "step_roofline": {"hbm_frac": step_bytes / (total_ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
                           "tensor_frac": step_flops / (total_ms * 1e-3) / 1e12 / peaks["bf16_tflops_sustained"],

@@ -58,7 +58,8 @@ typedef struct MskMoeCfg {
   int32_t num_ctas;      /* persistent grid size; 0 = one CTA per SM of the current device */
   int32_t split_k13;     /* K splits of the gate/up GEMM; 0 = chosen from n_tokens */
   int32_t split_k2;      /* K splits of the down GEMM;    0 = chosen from n_tokens */
-  int32_t token_tile;    /* MMA N (tokens per tile): 16/32/64/128; 0 = chosen from n_tokens */
+  int32_t token_tile;    /* MMA N (tokens per tile): 16/32/64/128, or 8 = the single-launch kernel for
+                            up to 8 tokens; 0 = chosen from n_tokens */
   int32_t max_tokens;    /* token capacity the workspace is sized for (msk_moe_forward rejects more) */
   int32_t trace;         /* non-zero: the GEMM kernels stamp %globaltimer per CTA into the workspace (view 6) */
   int32_t stop_after;    /* measuring aid: 0 = whole step; 1/2/3 = return after sort / gate-up GEMM / down GEMM */
@@ -172,7 +173,7 @@ int msk_moe_forward_static(const MskMoeCfg* cfg, const void* packed13, const voi
 int msk_moe_plan(const MskMoeCfg* cfg, int n_tokens, int* host_out);
 
 /* Views into the workspace after msk_moe_forward (device pointers, for parity tests):
- * which: 0 cnt, 1 off, 2 perm, 3 inv, 4 inter (bf16 [R, I]), 5 y (fp32 [R, H]),
+ * which: 0 cnt, 1 off, 2 perm, 3 inv, 4 inter (fp16 [R, I], holding bf16-rounded values), 5 y (fp32 [R, H]),
  * 6 trace (uint64 [2 GEMMs][256 CTAs][16 stamps], ns; written when cfg->trace != 0). */
 int msk_moe_workspace_view(const MskMoeCfg* cfg, void* workspace, int which, void** host_ptr);
 

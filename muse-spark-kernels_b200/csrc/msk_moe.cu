@@ -12,6 +12,7 @@
 #include "../../include/msk_moe.h"
 #include "route_sort.cuh"
 #include "gemm.cuh"
+#include "small_tokens.cuh"
 
 namespace msk {
 
@@ -394,9 +395,45 @@ static int pick_split(double units, int n_stages, int grid) {
   return best;
 }
 
+// Few-token kernel: piece slots per output element. A share of the flat stage-tile list holds at
+// least `per` stage tiles, so a tile of nst stages meets at most ceil(nst / per) + 1 shares, two
+// parities each. The fewest stage tiles there can be is one expert's.
+static int small_pieces(int tiles, int nst, int grid) {
+  const int per = std::max(1, tiles * nst / std::max(grid, 1));
+  return 2 * ((nst + per - 1) / per + 1);
+}
+constexpr int SMALL_MAX_PIECES = 64;  // bits of the slot mask
+
+static size_t small_part_floats(const MskMoeCfg* c) {
+  // sized for any grid: per = 1, capped at what the kernel accepts
+  const int p1 = std::min(2 * (c->hidden / KS + 1), SMALL_MAX_PIECES);
+  const int p2 = std::min(2 * (c->inter / KS + 1), SMALL_MAX_PIECES);
+  return static_cast<size_t>(ST_MAX_ROWS) * (static_cast<size_t>(p1) * 2 * c->inter + static_cast<size_t>(p2) * c->hidden);
+}
+
+static size_t small_smem_bytes(const MskMoeCfg* c) {
+  return 2048 + 512 + static_cast<size_t>(ST_MAX_TOKENS) * (static_cast<size_t>(std::max(c->hidden, c->inter)) * 2 + 32);
+}
+
+// The few-token kernel takes the step when it fits: at most 8 tokens and 64 routed rows, the
+// piece slots within the mask, the activation rows within shared memory, the whole grid resident.
+static bool small_fits(const MskMoeCfg* c, int T, int grid) {
+  if (T > ST_MAX_TOKENS || T * c->top_k > ST_MAX_ROWS) return false;
+  if (small_pieces(2 * c->inter / 128, c->hidden / KS, grid) > SMALL_MAX_PIECES) return false;
+  if (small_pieces(c->hidden / 128, c->inter / KS, grid) > SMALL_MAX_PIECES) return false;
+  if (small_smem_bytes(c) > 200 * 1024) return false;
+  return grid <= sm_count();
+}
+
 static Plan make_plan(const MskMoeCfg* c, int T) {
   Plan p;
   p.grid = c->num_ctas > 0 ? c->num_ctas : sm_count();
+  // on request only: at 1 to 8 tokens the chain of launches below is still the faster one
+  if (c->token_tile == 8 && small_fits(c, T, p.grid)) {
+    p.N = 8;  // the few-token kernel
+    p.s13 = p.s2 = 1;
+    return p;
+  }
   if (c->token_tile > 0) {
     p.N = c->token_tile;
   } else {
@@ -414,7 +451,7 @@ static Plan make_plan(const MskMoeCfg* c, int T) {
 
 // Workspace carving. Everything is sized for max_tokens with the worst plan.
 struct Carve {
-  size_t status, trace, cnt, off, perm, inv, tickets, inter, y, partial, xs, total;
+  size_t status, trace, cnt, off, perm, inv, tickets, small_ctl, inter, y, partial, xs, small_part, total;
 };
 constexpr size_t MAX_SPLIT = 8;
 constexpr size_t TRACE_CTAS = 256;
@@ -454,10 +491,12 @@ static Carve carve(const MskMoeCfg* c, int T) {
   k.inv = o; o += round_up(R * 4, 256);
   const size_t pairs = std::max(c->inter / 128, c->hidden / 256);
   k.tickets = o; o += 2 * round_up(max_tiles(c, T) * pairs * 4, 256);  // one region per GEMM
+  k.small_ctl = o; o += 1024;  // few-token kernel: grid barrier (2 words), per-token tickets at +64, row weights at +256
   k.inter = o; o += round_up(R * c->inter * 2, 256);
   k.y = o; o += round_up(R * c->hidden * 4, 256);
   k.partial = o; o += 2 * round_up(partial_floats(c, T) * 4, 256);  // one region per GEMM
   k.xs = o; o += round_up(R * c->hidden * 2, 256);  // sorted copy of the token rows (wide token tiles only)
+  k.small_part = o; o += round_up(small_part_floats(c) * 4, 256);  // pieces of the few-token kernel
   k.total = o;
   return k;
 }
@@ -774,6 +813,53 @@ static int forward_impl(const MskMoeCfg* cfg, const void* packed13, const void* 
   __half* xs = reinterpret_cast<__half*>(b + k.xs);
 
   Plan plan = make_plan(cfg, n_tokens);
+  if (plan.N == 8) {
+    if (cfg->stop_after != 0) return MSK_ERR_SHAPE;  // the stage hooks belong to the chain of launches
+    SmallParams sp{};
+    sp.w13 = static_cast<const uint8_t*>(packed13); sp.w2 = static_cast<const uint8_t*>(packed2);
+    sp.gs13 = gs13; sp.gs2 = gs2; sp.post_norm_w = static_cast<const __nv_bfloat16*>(post_norm_w);
+    sp.x = static_cast<const __nv_bfloat16*>(x);
+    sp.ids_in = logits ? nullptr : topk_ids; sp.tw_in = logits ? nullptr : topk_weights;
+    sp.logits = logits; sp.bias = bias; sp.ids_out = ids_out; sp.tw_out = tw_out;
+    sp.out = static_cast<__nv_bfloat16*>(out);
+    sp.cnt = cnt; sp.off = off; sp.perm = perm; sp.inv = inv; sp.inter = inter; sp.y = y;
+    sp.P1 = small_pieces(2 * cfg->inter / 128, cfg->hidden / KS, plan.grid);
+    sp.P2 = small_pieces(cfg->hidden / 128, cfg->inter / KS, plan.grid);
+    sp.part1 = reinterpret_cast<float*>(b + k.small_part);
+    sp.part2 = sp.part1 + static_cast<size_t>(ST_MAX_ROWS) * sp.P1 * 2 * cfg->inter;
+    sp.bar = reinterpret_cast<unsigned int*>(b + k.small_ctl);
+    sp.tickets = reinterpret_cast<int32_t*>(b + k.small_ctl + 64);
+    sp.row_w = reinterpret_cast<float*>(b + k.small_ctl + 256);
+    sp.status = status;
+    sp.trace = (cfg->trace != 0 && plan.grid <= static_cast<int>(TRACE_CTAS))
+                   ? reinterpret_cast<unsigned long long*>(b + k.trace) : nullptr;
+    sp.H = cfg->hidden; sp.I = cfg->inter; sp.E = cfg->n_experts; sp.lo = cfg->local_start; sp.nloc = cfg->local_count;
+    sp.k = cfg->top_k; sp.T = n_tokens; sp.mode = cfg->routing_mode;
+    sp.route_scale = cfg->route_scale; sp.eps = cfg->post_norm_eps;
+    const size_t smem = small_smem_bytes(cfg);
+    static bool attr_set[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+      const cudaError_t ae = cudaFuncSetAttribute(moe_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+      if (ae != cudaSuccess) return static_cast<int>(ae);
+      attr_set[dev] = true;
+    }
+    if (ev) { cudaEventRecord(ev[0], st); cudaEventRecord(ev[1], st); }
+    cudaLaunchConfig_t lc{};
+    lc.gridDim = dim3(static_cast<unsigned>(plan.grid));
+    lc.blockDim = dim3(ST_THREADS);
+    lc.dynamicSmemBytes = smem;
+    lc.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeCooperative;   // every CTA resident: the grid barriers rely on it
+    at[0].val.cooperative = 1;
+    lc.attrs = at;
+    lc.numAttrs = 1;
+    const int le = static_cast<int>(cudaLaunchKernelEx(&lc, moe_small_kernel, sp));
+    if (ev) { cudaEventRecord(ev[2], st); cudaEventRecord(ev[3], st); cudaEventRecord(ev[4], st); }
+    return le;
+  }
   if (plan.N != 16 && plan.N != 32 && plan.N != 64 && plan.N != 128) return MSK_ERR_SHAPE;
   if (plan.s13 < 1 || plan.s2 < 1 || plan.s13 > static_cast<int>(MAX_SPLIT) || plan.s2 > static_cast<int>(MAX_SPLIT))
     return MSK_ERR_SHAPE;

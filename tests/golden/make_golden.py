@@ -18,7 +18,9 @@ import types
 import numpy as np
 import torch
 
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+if len(sys.argv) < 2:
+    sys.exit("usage: make_golden.py <path of the reference checkout>")
+REF = sys.argv[1]
 OUT = os.path.join(os.path.dirname(os.path.abspath(__file__)), "reference_vectors.npz")
 
 

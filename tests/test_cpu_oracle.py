@@ -182,7 +182,7 @@ def test_host_side_validation_rejects_bad_arguments():
     assert lib.msk_moe_forward(ctypes.byref(cfg), odd, fake, fake, fake, None, fake, fake, fake, fake, fake,
                                ws.value, 4, None) == -3
     plan = (ctypes.c_int * 4)()
-    assert lib.msk_moe_plan(ctypes.byref(cfg), 4, plan) == 0 and plan[0] in (16, 32, 64, 128)
+    assert lib.msk_moe_plan(ctypes.byref(cfg), 4, plan) == 0 and plan[0] in (8, 16, 32, 64, 128)
 
 
 def test_module_refuses_cpu_tensors():

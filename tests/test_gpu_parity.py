@@ -229,3 +229,93 @@ def test_ep_combine_kernel_matches_rank_order_sum(cuda_dev):
     assert float(got[0].float().abs().max()) == 0.0
     own = ep.combine_partials(poisoned, ids, per, self_rank=1, self_rows=back[1].contiguous())
     assert torch.equal(own, got)
+
+
+@pytest.mark.parametrize("T,post,ctas", [(1, False, 0), (1, True, 5), (3, True, 37), (8, False, 0), (8, True, 148),
+                                         (2, False, 1)])
+def test_forward_few_token_kernel(cuda_dev, T, post, ctas):
+    """The single-launch kernel for up to 8 tokens (token_tile=8 forces it), on several grid sizes:
+    the shares of the weight stream, and with them the pieces each output sums, change with the
+    grid; the result must not."""
+    m, inputs, _lib, orc = _mods()
+    out, ref, parts, views, st, (x, ids, tw, w) = _run_forward(m, inputs, orc, cuda_dev, 1024, 512, 16, 4, T,
+                                                               seed=20 + T, post_norm=post, token_tile=8, num_ctas=ctas)
+    assert m.plan(st, T)[0] == 8
+    _check_forward(out, ref, parts, views)
+    # given routing instead of logits, and the chain of launches on the same inputs
+    again = m.kernel_fn({"hidden_states": x, "topk_ids": ids, "topk_weights": tw}, st)
+    assert torch.equal(again, out)
+    chain = m.prepare(w, n_experts=16, top_k=4, max_tokens=T, token_tile=16)
+    other = m.kernel_fn({"hidden_states": x, "topk_ids": ids, "topk_weights": tw}, chain)
+    assert _rel(out, other) <= 8e-3   # same products, different summation order: a bf16 ulp or two of the output
+    assert m.read_status(st) == 0 and m.read_status(chain) == 0
+
+
+@pytest.mark.parametrize("tile", [8, 16])
+def test_forward_local_range_negative_ids_and_empty_tokens(cuda_dev, tile):
+    """Experts [4, 12) of 16 resident: routes outside the range and negative ids are dropped (the
+    reference's filter, muse_moe_w4a16/cuda/moe.cu:347-350); a token left without any route is zero."""
+    m, inputs, _lib, orc = _mods()
+    H, I, E, k, T, lo, nloc = 512, 256, 16, 4, 6, 4, 8
+    w = inputs.make_weights(H, I, nloc, 31, cuda_dev, post_norm=True)
+    st = m.prepare(w, local_start=lo, n_experts=E, top_k=k, max_tokens=T, token_tile=tile)
+    g = torch.Generator(device=cuda_dev).manual_seed(5)
+    x = torch.randn((T, H), generator=g, device=cuda_dev).to(torch.bfloat16)
+    ids = torch.stack([torch.randperm(E, generator=g, device=cuda_dev)[:k] for _ in range(T)]).to(torch.int32)
+    ids[1] = torch.tensor([0, 1, 14, 15], dtype=torch.int32)      # nothing local
+    ids[2, 0] = -1
+    ids[3] = -1                                                   # no route at all
+    tw = torch.rand((T, k), generator=g, device=cuda_dev)
+    out = m.kernel_fn({"hidden_states": x, "topk_ids": ids, "topk_weights": tw}, st)
+    torch.cuda.synchronize()
+    assert m.read_status(st) == 0
+    ref, parts = orc.moe_forward(x, ids, tw, w, local_start=lo, return_parts=True)
+    _check_forward(out, ref, parts, m.workspace_views(st, T))
+    assert float(out[1].float().abs().max()) == 0.0 and float(out[3].float().abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("T", [1, 8, 40])
+def test_forward_is_deterministic_and_graph_capturable(cuda_dev, T):
+    """Same inputs, same bits: across calls, and between an eager call and a CUDA-graph replay."""
+    m, inputs, _lib, orc = _mods()
+    H, I, E, k = 1024, 512, 16, 4
+    w = inputs.make_weights(H, I, E, 41, cuda_dev, post_norm=True)
+    st = m.prepare(w, n_experts=E, top_k=k, max_tokens=T)
+    g = torch.Generator(device=cuda_dev).manual_seed(6)
+    data = {"hidden_states": torch.randn((T, H), generator=g, device=cuda_dev).to(torch.bfloat16),
+            "router_logits": torch.randn((T, E), generator=g, device=cuda_dev)}
+    first = m.kernel_fn(data, st).clone()
+    for _ in range(3):
+        assert torch.equal(m.kernel_fn(data, st), first)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        m.kernel_fn(data, st)
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        captured = m.kernel_fn(data, st)
+    for _ in range(2):
+        captured.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(captured, first)
+    assert m.read_status(st) == 0
+
+
+def test_forward_zero_tokens_and_state_deepcopy(cuda_dev):
+    import copy
+
+    m, inputs, _lib, orc = _mods()
+    H, I, E, k = 512, 256, 8, 2
+    w = inputs.make_weights(H, I, E, 43, cuda_dev)
+    st = m.prepare(w, n_experts=E, top_k=k, max_tokens=4)
+    empty = m.kernel_fn({"hidden_states": torch.empty((0, H), dtype=torch.bfloat16, device=cuda_dev),
+                         "topk_ids": torch.empty((0, k), dtype=torch.int32, device=cuda_dev),
+                         "topk_weights": torch.empty((0, k), device=cuda_dev)}, st)
+    assert tuple(empty.shape) == (0, H)
+    st2 = copy.deepcopy(st)
+    g = torch.Generator(device=cuda_dev).manual_seed(8)
+    data = {"hidden_states": torch.randn((3, H), generator=g, device=cuda_dev).to(torch.bfloat16),
+            "router_logits": torch.randn((3, E), generator=g, device=cuda_dev)}
+    assert torch.equal(m.kernel_fn(data, st), m.kernel_fn(data, st2))
