@@ -182,7 +182,7 @@ def run_gpu(args, spec):
         spec = dict(spec, name=spec["name"] + f"_E{E}resident")
     peaks = load_peaks()
     weights = inputs.make_weights(H, I, E, 0, dev)
-    state = moe.prepare(weights, n_experts=E, top_k=k, max_tokens=T)
+    state = moe.prepare(weights, n_experts=E, top_k=k, max_tokens=T, token_tile=args.token_tile)
     del weights
     torch.cuda.empty_cache()
     if args.profile_only:
@@ -346,6 +346,7 @@ def main():
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--workload", default="auto")
     ap.add_argument("--experts", type=int, default=0, help="resident experts (smaller case for profiler captures)")
+    ap.add_argument("--token-tile", type=int, default=0, help="force a kernel: 16/32/64/128, 8 = single-launch kernel")
     ap.add_argument("--profile-only", action="store_true", help="run warmup+steps eager steps and exit (for ncu)")
     args = ap.parse_args()
     spec = workload_spec(args.workload, args.gpus)

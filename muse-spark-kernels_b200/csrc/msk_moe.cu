@@ -396,23 +396,38 @@ static int pick_split(double units, int n_stages, int grid) {
 }
 
 // Few-token kernel: piece slots per output element. A share of the flat stage-tile list holds at
-// least `per` stage tiles, so a tile of nst stages meets at most ceil(nst / per) + 1 shares, two
-// parities each. The fewest stage tiles there can be is one expert's.
+// least `per` stage tiles, so a tile of nst stages meets at most ceil(nst / per) + 1 shares,
+// one piece per group of consumer warps each. The fewest stage tiles there can be is one expert's.
 static int small_pieces(int tiles, int nst, int grid) {
   const int per = std::max(1, tiles * nst / std::max(grid, 1));
-  return 2 * ((nst + per - 1) / per + 1);
+  return ST_GROUPS * ((nst + per - 1) / per + 1);
 }
 constexpr int SMALL_MAX_PIECES = 64;  // bits of the slot mask
 
 static size_t small_part_floats(const MskMoeCfg* c) {
   // sized for any grid: per = 1, capped at what the kernel accepts
-  const int p1 = std::min(2 * (c->hidden / KS + 1), SMALL_MAX_PIECES);
-  const int p2 = std::min(2 * (c->inter / KS + 1), SMALL_MAX_PIECES);
+  const int p1 = std::min(ST_GROUPS * (c->hidden / KS + 1), SMALL_MAX_PIECES);
+  const int p2 = std::min(ST_GROUPS * (c->inter / KS + 1), SMALL_MAX_PIECES);
   return static_cast<size_t>(ST_MAX_ROWS) * (static_cast<size_t>(p1) * 2 * c->inter + static_cast<size_t>(p2) * c->hidden);
 }
 
+constexpr size_t SMALL_SMEM_LIMIT = 227 * 1024;
+
+static size_t small_fixed_smem(const MskMoeCfg* c) {
+  return ST_OFF_ACT + static_cast<size_t>(ST_MAX_TOKENS) * (static_cast<size_t>(std::max(c->hidden, c->inter)) * 2 + 32);
+}
+
+// Ring slots: as many as fit, a multiple of the consumer groups (a slot always serves the same
+// group, which therefore sees every phase of the slot's barrier), at most 8.
+static int small_slots(const MskMoeCfg* c) {
+  const size_t fixed = small_fixed_smem(c);
+  if (fixed + ST_GROUPS * ST_SLOT_BYTES > SMALL_SMEM_LIMIT) return 0;
+  const int n = std::min(ST_MAX_SLOTS, static_cast<int>((SMALL_SMEM_LIMIT - fixed) / ST_SLOT_BYTES));
+  return n / ST_GROUPS * ST_GROUPS;
+}
+
 static size_t small_smem_bytes(const MskMoeCfg* c) {
-  return 2048 + 512 + static_cast<size_t>(ST_MAX_TOKENS) * (static_cast<size_t>(std::max(c->hidden, c->inter)) * 2 + 32);
+  return small_fixed_smem(c) + static_cast<size_t>(small_slots(c)) * ST_SLOT_BYTES;
 }
 
 // The few-token kernel takes the step when it fits: at most 8 tokens and 64 routed rows, the
@@ -421,7 +436,7 @@ static bool small_fits(const MskMoeCfg* c, int T, int grid) {
   if (T > ST_MAX_TOKENS || T * c->top_k > ST_MAX_ROWS) return false;
   if (small_pieces(2 * c->inter / 128, c->hidden / KS, grid) > SMALL_MAX_PIECES) return false;
   if (small_pieces(c->hidden / 128, c->inter / KS, grid) > SMALL_MAX_PIECES) return false;
-  if (small_smem_bytes(c) > 200 * 1024) return false;
+  if (small_slots(c) < ST_GROUPS) return false;
   return grid <= sm_count();
 }
 
@@ -836,19 +851,21 @@ static int forward_impl(const MskMoeCfg* cfg, const void* packed13, const void* 
     sp.H = cfg->hidden; sp.I = cfg->inter; sp.E = cfg->n_experts; sp.lo = cfg->local_start; sp.nloc = cfg->local_count;
     sp.k = cfg->top_k; sp.T = n_tokens; sp.mode = cfg->routing_mode;
     sp.route_scale = cfg->route_scale; sp.eps = cfg->post_norm_eps;
+    sp.slots = small_slots(cfg);
     const size_t smem = small_smem_bytes(cfg);
     static bool attr_set[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-      const cudaError_t ae = cudaFuncSetAttribute(moe_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+      const cudaError_t ae = cudaFuncSetAttribute(moe_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                  static_cast<int>(SMALL_SMEM_LIMIT));
       if (ae != cudaSuccess) return static_cast<int>(ae);
       attr_set[dev] = true;
     }
     if (ev) { cudaEventRecord(ev[0], st); cudaEventRecord(ev[1], st); }
     cudaLaunchConfig_t lc{};
     lc.gridDim = dim3(static_cast<unsigned>(plan.grid));
-    lc.blockDim = dim3(ST_THREADS);
+    lc.blockDim = dim3(ST_THREADS_ALL);
     lc.dynamicSmemBytes = smem;
     lc.stream = st;
     cudaLaunchAttribute at[1];

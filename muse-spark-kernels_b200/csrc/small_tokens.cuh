@@ -32,17 +32,16 @@
 
 namespace msk {
 
-constexpr int ST_THREADS = 512;
-constexpr int ST_WARPS = ST_THREADS / 32;
+#ifndef MSK_ST_VARIANT
+#define MSK_ST_VARIANT 0   // 1, 2: measuring builds, never shipped
+#endif
+#ifndef MSK_ST_GROUPS
+#define MSK_ST_GROUPS 2
+#endif
+constexpr int ST_GROUPS = MSK_ST_GROUPS;      // groups of 8 consumer warps; group i takes every ST_GROUPS-th stage tile
+constexpr int ST_WARPS = 8 * ST_GROUPS;       // consumer warps; one more warp feeds the weight ring
 constexpr int ST_MAX_TOKENS = 8;   // columns of one MMA: rows per expert never exceed the tokens
 constexpr int ST_MAX_ROWS = 64;    // routed rows (tokens x top_k)
-#ifndef MSK_ST_VARIANT
-#define MSK_ST_VARIANT 0   // 1, 2: measuring builds (stream only / math only), never shipped
-#endif
-#ifndef MSK_ST_DEPTH
-#define MSK_ST_DEPTH 3
-#endif
-constexpr int ST_DEPTH = MSK_ST_DEPTH;   // stage tiles in flight per warp
 
 struct SmallParams {
   const uint8_t* w13; const uint8_t* w2;
@@ -62,6 +61,7 @@ struct SmallParams {
   int32_t* status;
   unsigned long long* trace;                                  // optional: 16 time stamps per CTA
   int H, I, E, lo, nloc, k, T, mode, P1, P2;
+  int slots;                                                  // weight ring slots (a multiple of ST_GROUPS)
   float route_scale, eps;
 };
 
@@ -106,17 +106,10 @@ __device__ __forceinline__ int share_of(long long x, long long L, int G) {
   return static_cast<int>(((x + 1) * G - 1) / L);
 }
 
-// Position, inside one 256-K stage, of element k of an activation row in shared memory: the 4
-// elements lane q needs for MMA step s of chunk column j sit together, the 4 lanes side by side.
-__device__ __forceinline__ int b_pos(int k_in_stage) {
-  const int c = k_in_stage >> 5, s = (k_in_stage >> 2) & 7, i = k_in_stage & 3;
-  return (((c >> 2) * 8 + s) * 4 + (c & 3)) * 4 + i;
-}
-
 // Grid barrier with a generation word; self-resetting, so it needs no host work between launches.
 // Returns false when the wait ran out (one second): the caller leaves the kernel.
 __device__ __forceinline__ bool grid_barrier(unsigned int* bar, int32_t* status, SmallTables& tb) {
-  __syncthreads();
+  asm volatile("bar.sync 1, %0;" ::"n"(32 * ST_WARPS) : "memory");   // the consumer threads; the producer warp streams on
   if (threadIdx.x == 0) {
     volatile unsigned int* gen = bar + 1;
     const unsigned int my_gen = *gen;   // cannot advance before this CTA has arrived
@@ -138,13 +131,16 @@ __device__ __forceinline__ bool grid_barrier(unsigned int* bar, int32_t* status,
     __threadfence();
     tb.flag = ok;
   }
-  __syncthreads();
+  asm volatile("bar.sync 1, %0;" ::"n"(32 * ST_WARPS) : "memory");
   return tb.flag != 0;
 }
 
-// Which piece slots of flat tile TI hold data: slot 2 (c - c0) + parity for every share c that
-// overlaps the tile's stages [TI nst, (TI + 1) nst) and every parity (stage index minus the
-// share's begin, mod 2) that occurs in the overlap. Bit i of the result = slot i.
+// Group `grp` takes the stage tiles whose distance from the share's begin is grp modulo ST_GROUPS;
+// the first such tile at or after distance d is d + group_offset(grp, d).
+__device__ __forceinline__ int group_offset(int grp, int d) { return ((grp - d) % ST_GROUPS + ST_GROUPS) % ST_GROUPS; }
+
+// Which piece slots of flat tile TI hold data: slot ST_GROUPS (c - c0) + group for every share c that
+// overlaps the tile's stages [TI nst, (TI + 1) nst) and every warp group that has a stage in the overlap. Bit i of the result = slot i.
 __device__ __forceinline__ unsigned long long piece_mask(int TI, int nst, int L, int G) {
   const int s0 = TI * nst, s1 = s0 + nst;
   const int c0 = share_of(s0, L, G), c1 = share_of(s1 - 1, L, G);
@@ -152,9 +148,9 @@ __device__ __forceinline__ unsigned long long piece_mask(int TI, int nst, int L,
   for (int c = c0; c <= c1; ++c) {
     const int a = static_cast<int>(share_begin(c, L, G)), b = static_cast<int>(share_begin(c + 1, L, G));
     const int lo = max(a, s0), hi = min(b, s1);
-    for (int par = 0; par < 2; ++par) {
-      const int first = lo + ((par - (lo - a)) & 1);
-      if (first < hi) m |= 1ull << (2 * (c - c0) + par);
+    for (int grp = 0; grp < ST_GROUPS; ++grp) {
+      const int first = lo + group_offset(grp, lo - a);
+      if (first < hi) m |= 1ull << (ST_GROUPS * (c - c0) + grp);
     }
   }
   return m;
@@ -182,85 +178,159 @@ __device__ __forceinline__ float4 sum_pieces4(const float* p, int ld, unsigned l
   return acc;
 }
 
-struct StageRegs {
-  uint4 q[4];       // chunks (q, row g), (q, row g + 8), (q + 4, row g), (q + 4, row g + 8)
-  uint32_t sf[4];   // their two scale bytes each
+// ---- the weight ring in shared memory
+// One slot holds one stage tile exactly as it lies in global memory (one bulk copy of 18 KB;
+// nine 2 KB copies into a padded layout were measured at half the rate).
+constexpr int ST_SLOT_BYTES = TILE_BYTES;
+constexpr int ST_MAX_SLOTS = 8;
+constexpr int ST_CONSUMERS = 32 * ST_WARPS;                         // the warp after them is the producer
+
+struct SmallCtl {
+  uint64_t full[ST_MAX_SLOTS];
+  uint64_t empty[ST_MAX_SLOTS];
+  int abort_word;
 };
 
-__device__ __forceinline__ void load_stage(StageRegs& s, const uint8_t* tile, int row, int q) {
-  s.q[0] = ldg_stream16(tile + (q * 128 + row) * 16);
-  s.q[1] = ldg_stream16(tile + (q * 128 + row + 8) * 16);
-  s.q[2] = ldg_stream16(tile + ((q + 4) * 128 + row) * 16);
-  s.q[3] = ldg_stream16(tile + ((q + 4) * 128 + row + 8) * 16);
-  const uint8_t* sf = tile + TILE_CODE_BYTES;
-  s.sf[0] = ldg_stream_u16(sf + row * 16 + 2 * q);
-  s.sf[1] = ldg_stream_u16(sf + (row + 8) * 16 + 2 * q);
-  s.sf[2] = ldg_stream_u16(sf + row * 16 + 2 * (q + 4));
-  s.sf[3] = ldg_stream_u16(sf + (row + 8) * 16 + 2 * (q + 4));
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(ST_CONSUMERS) : "memory"); }
+
+__device__ __forceinline__ uint4 lds128(const uint8_t* p) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(smem_u32(p)));
+  return v;
+}
+// Four 8 x 16-byte matrices: lanes 8 i .. 8 i + 7 give the row addresses of matrix i; lane
+// (g, q) receives bytes [4 q, 4 q + 4) of row g of each matrix.
+__device__ __forceinline__ void ldmatrix_x4(const uint8_t* row_addr, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(row_addr)));
+}
+
+// What a lane holds of one stage tile (16 weight rows x 256 K of its warp): for each of the 8
+// chunks, the 8 codes K = 32 c + 8 q .. + 7 of rows g and g + 8 (one word each, fetched with
+// ldmatrix: a matrix = 8 rows x one chunk, 128 contiguous bytes, no bank conflict), and the
+// rows' 16 scale bytes.
+struct StageRegs {
+  uint32_t w[4][4];   // [chunk pair][chunk 2 p row g, chunk 2 p row g + 8, chunk 2 p + 1 row g, chunk 2 p + 1 row g + 8]
+  uint4 sf[2];        // scale bytes of rows g and g + 8
+};
+
+__device__ __forceinline__ void read_stage(StageRegs& s, const uint8_t* slot, int slab, int lane) {
+  // lane l addresses row (l & 7) of matrix (l >> 3): matrix 0/1 = chunk 2 p, rows 0-7 / 8-15 of the
+  // slab; matrix 2/3 = chunk 2 p + 1
+  const int m = lane >> 3;
+  const uint8_t* base = slot + (((m >> 1) * 128) + slab * 16 + (m & 1) * 8 + (lane & 7)) * 16;
+#pragma unroll
+  for (int pr = 0; pr < 4; ++pr) ldmatrix_x4(base + pr * (2 * 128 * 16), s.w[pr]);
+  const int g = lane >> 2;
+  const uint8_t* sf = slot + TILE_CODE_BYTES + (slab * 16 + g) * 16;
+  s.sf[0] = lds128(sf);
+  s.sf[1] = lds128(sf + 8 * 16);
+}
+
+// Position, inside one 256-K stage, of element k of an activation row in shared memory: MMA step
+// (chunk c, half t) reads the 4 elements K = 32 c + 8 q + 4 t .. + 3 of lane q, the 4 lanes side
+// by side.
+__device__ __forceinline__ int b_pos(int k_in_stage) {
+  const int c = k_in_stage >> 5, q = (k_in_stage >> 3) & 3, t = (k_in_stage >> 2) & 1, i = k_in_stage & 3;
+  return (((c * 2 + t) * 4) + q) * 4 + i;
 }
 
 // 16 rows x 256 K of weights against the 8 activation rows at `brow` (this lane's row g of the
-// stage, permuted order): 16 MMAs into acc.
-__device__ __forceinline__ void consume_stage(const StageRegs& s, const uint8_t* brow, int q, float (&acc)[4][4]) {
+// stage, permuted order): 16 MMAs on two accumulation chains. sel0 / sel1: byte selectors that
+// duplicate this lane's scale byte of an even / odd chunk (byte 2 c + q / 2 of the scale row).
+__device__ __forceinline__ void consume_stage(const StageRegs& s, const uint8_t* brow, int q, uint32_t sel0,
+                                              uint32_t sel1, float (&acc)[2][4]) {
+  const uint32_t sfa[4] = {s.sf[0].x, s.sf[0].y, s.sf[0].z, s.sf[0].w};
+  const uint32_t sfb[4] = {s.sf[1].x, s.sf[1].y, s.sf[1].z, s.sf[1].w};
 #pragma unroll
-  for (int j = 0; j < 2; ++j) {
-    uint32_t lo[16], hi[16];
-    {
-      const uint32_t w0[4] = {s.q[2 * j].x, s.q[2 * j].y, s.q[2 * j].z, s.q[2 * j].w};
-      const uint32_t w1[4] = {s.q[2 * j + 1].x, s.q[2 * j + 1].y, s.q[2 * j + 1].z, s.q[2 * j + 1].w};
-      decode_chunk(w0, s.sf[2 * j], lo);
-      decode_chunk(w1, s.sf[2 * j + 1], hi);
+  for (int c = 0; c < 8; ++c) {
+    const uint32_t sel = (c & 1) ? sel1 : sel0;
+    const uint32_t sa = cvt_e4m3x2_f16(static_cast<uint16_t>(prmt(sfa[c >> 1], 0u, sel)));
+    const uint32_t sb = cvt_e4m3x2_f16(static_cast<uint16_t>(prmt(sfb[c >> 1], 0u, sel)));
+    uint32_t a[4], b[4];
+    cvt_e2m1x8_f16(s.w[c >> 1][(c & 1) * 2], a[0], a[1], a[2], a[3]);
+    cvt_e2m1x8_f16(s.w[c >> 1][(c & 1) * 2 + 1], b[0], b[1], b[2], b[3]);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      a[i] = hmul2_f16(a[i], sa);
+      b[i] = hmul2_f16(b[i], sb);
     }
 #pragma unroll
-    for (int s8 = 0; s8 < 8; ++s8) {
-      const uint2 b = *reinterpret_cast<const uint2*>(brow + ((j * 8 + s8) * 4 + q) * 8);
-      mma_m16n8k16(acc[2 * j + (s8 & 1)], lo[2 * s8], hi[2 * s8], lo[2 * s8 + 1], hi[2 * s8 + 1], b.x, b.y);
+    for (int t = 0; t < 2; ++t) {
+      const uint2 x = *reinterpret_cast<const uint2*>(brow + ((c * 2 + t) * 4 + q) * 8);
+      mma_m16n8k16(acc[t], a[2 * t], b[2 * t], a[2 * t + 1], b[2 * t + 1], x.x, x.y);
     }
   }
 }
 
-// One GEMM phase for this CTA: its share of the flat stage-tile list of the touched experts.
-// PHASE 0: weights w13, activations = token rows of x, pieces to part1 (columns: gate [0, I),
-// up [I, 2 I)). PHASE 1: weights w2, activations = SwiGLU of the summed part1 pieces, pieces to
-// part2. `bs` is the activation buffer in shared memory: 8 rows of K F16 in permuted order,
-// row stride K * 2 + 32 bytes.
+// Shapes of one GEMM phase. PHASE 0: weights w13, K = H, pieces to part1 (columns: gate [0, I),
+// up [I, 2 I)). PHASE 1: weights w2, K = I, pieces to part2.
+struct PhaseShape {
+  int K, tiles, nst, per_exp, L, G, a, b;
+};
+__device__ __forceinline__ PhaseShape phase_shape(const SmallParams& p, int U, int phase) {
+  PhaseShape s;
+  s.K = phase == 0 ? p.H : p.I;
+  s.tiles = phase == 0 ? 2 * p.I / 128 : p.H / 128;
+  s.nst = s.K / KS;
+  s.per_exp = s.tiles * s.nst;
+  s.L = U * s.per_exp;
+  s.G = min(static_cast<int>(gridDim.x), s.L);   // shares are never empty: CTAs past L idle
+  const int cta = blockIdx.x;
+  s.a = cta < s.G ? static_cast<int>(share_begin(cta, s.L, s.G)) : 0;
+  s.b = cta < s.G ? static_cast<int>(share_begin(cta + 1, s.L, s.G)) : 0;
+  return s;
+}
+
+// Producer (one lane): this CTA's share of both phases, in order, through the ring. `it` counts
+// the stage tiles since the kernel began; slot = it % slots. The weights do not depend on the
+// first phase's results, so the second phase's tiles are already landing while the grid barrier
+// between the phases is being crossed.
+__device__ void produce(const SmallParams& p, const SmallTables& tb, SmallCtl& ctl, uint8_t* ring, int slots) {
+  const uint64_t pol = policy_evict_first();
+  int it = 0;
+  for (int phase = 0; phase < 2; ++phase) {
+    const PhaseShape s = phase_shape(p, tb.U, phase);
+    const uint8_t* w = phase == 0 ? p.w13 : p.w2;
+    for (int idx = s.a; idx < s.b; ++idx, ++it) {
+      const int slot = it % slots, pass = it / slots;
+      if (!mbar_wait(&ctl.empty[slot], (pass & 1) ^ 1, &ctl.abort_word)) return;
+      const int u = idx / s.per_exp;
+      const uint8_t* tile = w + (static_cast<size_t>(tb.u_exp[u]) * s.per_exp + (idx - u * s.per_exp)) * TILE_BYTES;
+      uint8_t* dst = ring + static_cast<size_t>(slot) * ST_SLOT_BYTES;
+      mbar_arrive_expect_tx(&ctl.full[slot], TILE_BYTES);
+      bulk_g2s(dst, tile, TILE_BYTES, &ctl.full[slot], pol);
+    }
+  }
+}
+
+// Consumers (16 warps): one GEMM phase of this CTA's share. `it0` is the ordinal of the share's
+// first stage tile in the ring (the producer counts the same way). `bs` is the activation buffer:
+// 8 rows of K F16 in permuted order, row stride K * 2 + 32 bytes. After a failed wait (`ok`
+// false) the control flow goes on, so every thread still meets every barrier, but nothing is read.
 template <int PHASE>
-__device__ void stream_phase(const SmallParams& p, SmallTables& tb, uint8_t* bs, unsigned long long* masks) {
+__device__ void consume_phase(const SmallParams& p, SmallTables& tb, SmallCtl& ctl, const uint8_t* ring, int slots,
+                              uint8_t* bs, unsigned long long* masks, int& it0, bool& ok) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, q = lane & 3;
-  const int par = warp >> 3, slab = warp & 7;
+  const int grp = warp >> 3, slab = warp & 7;
   const int cta = blockIdx.x;
-  const int K = PHASE == 0 ? p.H : p.I;
-  const int tiles = PHASE == 0 ? 2 * p.I / 128 : p.H / 128;
-  const int nst = K / KS;
-  const int per_exp = tiles * nst;
-  const int L = tb.U * per_exp;
-  const int G = min(static_cast<int>(gridDim.x), L);   // shares are never empty: CTAs past L idle
+  const PhaseShape s = phase_shape(p, tb.U, PHASE);
+  const int K = s.K, nst = s.nst;
   const int P = PHASE == 0 ? p.P1 : p.P2;
   const int ld = PHASE == 0 ? 2 * p.I : p.H;
   float* part = PHASE == 0 ? p.part1 : p.part2;
-  const uint8_t* w = PHASE == 0 ? p.w13 : p.w2;
   const int rs = K * 2 + 32;   // activation row stride in bytes
-  const int a = cta < G ? static_cast<int>(share_begin(cta, L, G)) : 0;
-  const int b = cta < G ? static_cast<int>(share_begin(cta + 1, L, G)) : 0;
-  for (int sa = a; sa < b;) {
-    const int u = sa / per_exp;
-    const int sb = min(b, (u + 1) * per_exp);
+  const uint32_t sel0 = static_cast<uint32_t>(q >> 1) * 0x11u, sel1 = static_cast<uint32_t>(2 + (q >> 1)) * 0x11u;
+  for (int sa = s.a; sa < s.b;) {
+    const int u = sa / s.per_exp;
+    const int sb = min(s.b, (u + 1) * s.per_exp);
     const int e = tb.u_exp[u], row0 = tb.u_off[u], cnt = tb.u_off[u + 1] - row0;
-    const uint8_t* wexp = w + static_cast<size_t>(e) * per_exp * TILE_BYTES - static_cast<size_t>(u) * per_exp * TILE_BYTES;
-    const int wrow = slab * 16 + g;
-    const int first = sa + ((par - (sa - a)) & 1);
-    StageRegs ring[ST_DEPTH];
-#pragma unroll
-    for (int d = 0; d < ST_DEPTH; ++d) {
-      const int idx = first + 2 * d;
-      if (idx < sb) load_stage(ring[d], wexp + static_cast<size_t>(idx) * TILE_BYTES, wrow, q);
-    }
-    __syncthreads();   // the previous segment's readers are done with the activation buffer
+    consumer_sync();   // the previous segment's readers are done with the activation buffer
     if (PHASE == 0) {
       // token rows of this expert, BF16 -> F16, permuted; rows past cnt are zero
       const int groups = K / 8;
-      for (int i = tid; i < ST_MAX_TOKENS * groups; i += ST_THREADS) {
+      for (int i = tid; i < ST_MAX_TOKENS * groups; i += ST_CONSUMERS) {
         const int n = i / groups, k8 = (i - n * groups) * 8;
         uint4 v = make_uint4(0u, 0u, 0u, 0u);
         if (n < cnt) {
@@ -277,11 +347,11 @@ __device__ void stream_phase(const SmallParams& p, SmallTables& tb, uint8_t* bs,
       const int tiles1 = 2 * p.I / 128, nst1 = p.H / KS;
       const int L1 = tb.U * tiles1 * nst1;
       const int G1 = min(static_cast<int>(gridDim.x), L1);
-      for (int i = tid; i < tiles1; i += ST_THREADS) masks[i] = piece_mask(u * tiles1 + i, nst1, L1, G1);
-      __syncthreads();
+      for (int i = tid; i < tiles1; i += ST_CONSUMERS) masks[i] = piece_mask(u * tiles1 + i, nst1, L1, G1);
+      consumer_sync();
       const float gsc = p.gs13[e];
-      const bool writer = sa == u * per_exp;   // the CTA that starts this expert also stores inter
-      for (int i = tid; i < ST_MAX_TOKENS * (K / 4); i += ST_THREADS) {
+      const bool writer = sa == u * s.per_exp;   // the CTA that starts this expert also stores inter
+      for (int i = tid; i < ST_MAX_TOKENS * (K / 4); i += ST_CONSUMERS) {
         const int n = i / (K / 4), col = (i - n * (K / 4)) * 4;
         float4 ga = make_float4(0.f, 0.f, 0.f, 0.f), up = ga;
         if (n < cnt) {
@@ -301,66 +371,67 @@ __device__ void stream_phase(const SmallParams& p, SmallTables& tb, uint8_t* bs,
         if (writer && n < cnt) *reinterpret_cast<uint2*>(p.inter + static_cast<size_t>(row0 + n) * K + col) = pk;
       }
     }
-    __syncthreads();
+    consumer_sync();
     const uint8_t* brow = bs + g * rs;
+    const int first = sa + group_offset(grp, sa - s.a);
+    int TI = first / nst, st = first - TI * nst;
+    const int ord0 = it0 + (first - s.a);
+    int slot = ord0 % slots, pass = ord0 / slots;
     int cur_tile = -1;
-    float acc[4][4];   // four independent accumulation chains, added in a fixed order at the flush
-#pragma unroll
-    for (int i = 0; i < 4; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
-    auto flush = [&](int TI) {
-      float c[4];
-#pragma unroll
-      for (int i = 0; i < 4; ++i) c[i] = (acc[0][i] + acc[1][i]) + (acc[2][i] + acc[3][i]);
-      const int slot = 2 * (cta - share_of(TI * nst, L, G)) + par;
-      const int tt = TI - u * tiles;
+    float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+    auto flush = [&](int tile) {
+      const int piece = ST_GROUPS * (cta - share_of(tile * nst, s.L, s.G)) + grp;
+      const int tt = tile - u * s.tiles;
       const int col = (PHASE == 0 ? ((tt & 1) * p.I + (tt >> 1) * 128) : tt * 128) + slab * 16 + g;
       const int n0 = 2 * q, n1 = 2 * q + 1;
       if (n0 < cnt) {
-        float* d = part + (static_cast<size_t>(row0 + n0) * P + slot) * ld + col;
-        d[0] = c[0];
-        d[8] = c[2];
+        float* d = part + (static_cast<size_t>(row0 + n0) * P + piece) * ld + col;
+        d[0] = acc[0][0] + acc[1][0];
+        d[8] = acc[0][2] + acc[1][2];
       }
       if (n1 < cnt) {
-        float* d = part + (static_cast<size_t>(row0 + n1) * P + slot) * ld + col;
-        d[0] = c[1];
-        d[8] = c[3];
+        float* d = part + (static_cast<size_t>(row0 + n1) * P + piece) * ld + col;
+        d[0] = acc[0][1] + acc[1][1];
+        d[8] = acc[0][3] + acc[1][3];
       }
     };
-    for (int base = first; base < sb; base += 2 * ST_DEPTH) {
+    for (int idx = first; idx < sb; idx += ST_GROUPS) {
+      if (TI != cur_tile) {
+        if (cur_tile >= 0 && ok) flush(cur_tile);
+        cur_tile = TI;
 #pragma unroll
-      for (int d = 0; d < ST_DEPTH; ++d) {
-        const int idx = base + 2 * d;
-        if (idx < sb) {
-          const int TI = idx / nst;
-          if (TI != cur_tile) {
-            if (cur_tile >= 0) flush(cur_tile);
-            cur_tile = TI;
-#pragma unroll
-            for (int i = 0; i < 4; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
-          }
-          const StageRegs cur = ring[d];
-          const int nxt = idx + 2 * ST_DEPTH;
-#if MSK_ST_VARIANT != 2
-          if (nxt < sb) load_stage(ring[d], wexp + static_cast<size_t>(nxt) * TILE_BYTES, wrow, q);
-#endif
-#if MSK_ST_VARIANT == 1
-          acc[0][0] += __uint_as_float((cur.q[0].x ^ cur.q[1].y ^ cur.q[2].z ^ cur.q[3].w ^ cur.sf[0] ^ cur.sf[1] ^ cur.sf[2] ^ cur.sf[3]) & 0x3FFFFFFFu);
-#else
-          consume_stage(cur, brow + (idx - TI * nst) * (KS * 2), q, acc);
-#endif
-        }
+        for (int i = 0; i < 4; ++i) acc[0][i] = acc[1][i] = 0.f;
       }
+      StageRegs r;
+      if (ok) ok = mbar_wait(&ctl.full[slot], pass & 1, &ctl.abort_word);
+      if (ok) read_stage(r, ring + static_cast<size_t>(slot) * ST_SLOT_BYTES, slab, lane);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&ctl.empty[slot]);   // the slot's bytes are in registers
+      if (ok) consume_stage(r, brow + st * (KS * 2), q, sel0, sel1, acc);
+      st += ST_GROUPS;
+      while (st >= nst) { st -= nst; ++TI; }
+      slot += ST_GROUPS;
+      if (slot >= slots) { slot -= slots; ++pass; }
     }
-    if (cur_tile >= 0) flush(cur_tile);
+    if (cur_tile >= 0 && ok) flush(cur_tile);
     sa = sb;
   }
+  it0 += s.b - s.a;
 }
 
-__global__ void __launch_bounds__(ST_THREADS, 1) moe_small_kernel(const __grid_constant__ SmallParams p) {
-  extern __shared__ __align__(16) uint8_t st_smem[];
+// Shared memory: tables | masks | ring control | activation buffer | weight ring.
+constexpr int ST_OFF_MASKS = 2048;
+constexpr int ST_OFF_CTL = ST_OFF_MASKS + 512;
+constexpr int ST_OFF_ACT = ST_OFF_CTL + 256;
+constexpr int ST_THREADS_ALL = ST_CONSUMERS + 32;
+
+__global__ void __launch_bounds__(ST_THREADS_ALL, 1) moe_small_kernel(const __grid_constant__ SmallParams p) {
+  extern __shared__ __align__(128) uint8_t st_smem[];
   SmallTables& tb = *reinterpret_cast<SmallTables*>(st_smem);
-  unsigned long long* masks = reinterpret_cast<unsigned long long*>(st_smem + 2048);   // 64 entries
-  uint8_t* bs = st_smem + 2048 + 512;
+  unsigned long long* masks = reinterpret_cast<unsigned long long*>(st_smem + ST_OFF_MASKS);   // 64 entries
+  SmallCtl& ctl = *reinterpret_cast<SmallCtl*>(st_smem + ST_OFF_CTL);
+  uint8_t* bs = st_smem + ST_OFF_ACT;
+  uint8_t* ring = bs + ST_MAX_TOKENS * (max(p.H, p.I) * 2 + 32);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int G = gridDim.x, cta = blockIdx.x;
   const int n_entries = p.T * p.k;
@@ -368,6 +439,14 @@ __global__ void __launch_bounds__(ST_THREADS, 1) moe_small_kernel(const __grid_c
     if (p.trace != nullptr && tid == 0) p.trace[static_cast<size_t>(cta) * 16 + i] = globaltimer_ns();
   };
   stamp(0);
+  if (tid == 0) {
+    for (int i = 0; i < p.slots; ++i) {
+      mbar_init(&ctl.full[i], 1);
+      mbar_init(&ctl.empty[i], 8);   // the eight consumer warps of a stage tile
+    }
+    ctl.abort_word = 0;
+    fence_mbar_init();
+  }
 
   // ---- phase 0: routing and the stable sort by local expert, the same in every CTA
   if (p.logits != nullptr) {
@@ -409,10 +488,14 @@ __global__ void __launch_bounds__(ST_THREADS, 1) moe_small_kernel(const __grid_c
     tb.U = U;
     tb.R = R;
   }
-  __syncthreads();
+  __syncthreads();   // the last barrier the producer warp takes part in
+  if (warp == ST_CONSUMERS / 32) {
+    if (lane == 0) produce(p, tb, ctl, ring, p.slots);
+    return;
+  }
   const int R = tb.R;
   if (cta == 0) {   // the tables as the general path leaves them, and the routing result
-    for (int e = tid; e <= p.nloc; e += ST_THREADS) {
+    for (int e = tid; e <= p.nloc; e += ST_CONSUMERS) {
       int below = 0, same = 0;
       for (int r = 0; r < R; ++r) {
         below += tb.s_exp[r] < e ? 1 : 0;
@@ -432,28 +515,34 @@ __global__ void __launch_bounds__(ST_THREADS, 1) moe_small_kernel(const __grid_c
   }
 
   // ---- phase 1 and 2: the two weight streams
+  int it0 = 0;
+  bool ok = true;
   stamp(1);
-  stream_phase<0>(p, tb, bs, masks);
+  consume_phase<0>(p, tb, ctl, ring, p.slots, bs, masks, it0, ok);
   stamp(2);
   if (!grid_barrier(p.bar, p.status, tb)) return;
   stamp(3);
-  stream_phase<1>(p, tb, bs, masks);
+  consume_phase<1>(p, tb, ctl, ring, p.slots, bs, masks, it0, ok);
   stamp(4);
   if (!grid_barrier(p.bar, p.status, tb)) return;
   stamp(5);
+  if (ctl.abort_word != 0) {   // a wait on the weight ring ran out somewhere in this CTA
+    if (tid == 0) atomicExch(p.status, 1);
+    return;
+  }
 
   // ---- phase 3: one CTA per routed row finishes y; the last one of a token sums its slots
   const int tiles2 = p.H / 128, nst2 = p.I / KS;
   const int L2 = tb.U * tiles2 * nst2;
   const int G2 = min(G, L2);
   for (int r = cta; r < R + p.T; r += G) {
-    __syncthreads();   // tb.flag, tb.wsum and masks of the previous round are free
+    consumer_sync();   // tb.flag, tb.wsum and masks of the previous round are free
     if (r >= R) {      // a token without any local expert gets a zero row
       const int t = r - R;
       bool any = false;
       for (int s = 0; s < p.k; ++s) any |= tb.inv[t * p.k + s] >= 0;
       if (!any)
-        for (int i = tid; i < p.H / 8; i += ST_THREADS)
+        for (int i = tid; i < p.H / 8; i += ST_CONSUMERS)
           *reinterpret_cast<uint4*>(p.out + static_cast<size_t>(t) * p.H + i * 8) = make_uint4(0u, 0u, 0u, 0u);
       continue;
     }
@@ -461,12 +550,12 @@ __global__ void __launch_bounds__(ST_THREADS, 1) moe_small_kernel(const __grid_c
     const int e = tb.s_exp[r];
     int u = 0;
     while (tb.u_exp[u] != e) ++u;
-    for (int i = tid; i < tiles2; i += ST_THREADS) masks[i] = piece_mask(u * tiles2 + i, nst2, L2, G2);
-    __syncthreads();
+    for (int i = tid; i < tiles2; i += ST_CONSUMERS) masks[i] = piece_mask(u * tiles2 + i, nst2, L2, G2);
+    consumer_sync();
     const float gsc = p.gs2[e];
     const float* pr = p.part2 + static_cast<size_t>(r) * p.P2 * p.H;
     float ss = 0.f;
-    for (int col = tid * 4; col < p.H; col += ST_THREADS * 4) {
+    for (int col = tid * 4; col < p.H; col += ST_CONSUMERS * 4) {
       float4 v = sum_pieces4(pr + col, p.H, masks[col >> 7]);
       float o0 = gsc, o1 = gsc, o2 = gsc, o3 = gsc;
       if (p.post_norm_w != nullptr) {
@@ -483,14 +572,14 @@ __global__ void __launch_bounds__(ST_THREADS, 1) moe_small_kernel(const __grid_c
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
       if (lane == 0) tb.wsum[warp] = ss;
-      __syncthreads();
+      consumer_sync();
       float tot = 0.f;
 #pragma unroll
       for (int w2 = 0; w2 < ST_WARPS; ++w2) tot += tb.wsum[w2];   // fixed order
       wgt *= rsqrtf(tot / static_cast<float>(p.H) + p.eps);
     }
     __threadfence();   // this row of y is visible before the ticket
-    __syncthreads();
+    consumer_sync();
     if (tid == 0) {
       p.row_w[r] = wgt;
       int target = 0;
@@ -502,10 +591,10 @@ __global__ void __launch_bounds__(ST_THREADS, 1) moe_small_kernel(const __grid_c
       __threadfence();
       tb.flag = last;
     }
-    __syncthreads();
+    consumer_sync();
     if (tb.flag) {
       // out[t] = bf16(sum over the token's slots, in slot order, of y * (weight * norm))
-      for (int c4 = tid; c4 < p.H / 4; c4 += ST_THREADS) {
+      for (int c4 = tid; c4 < p.H / 4; c4 += ST_CONSUMERS) {
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
         for (int s = 0; s < p.k; ++s) {
           const int rr = tb.inv[t * p.k + s];
