@@ -346,6 +346,7 @@ def main():
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--workload", default="auto")
     ap.add_argument("--experts", type=int, default=0, help="resident experts (smaller case for profiler captures)")
+    ap.add_argument("--ep-chunks", type=int, default=0, help="expert-parallel runs: chunks of source ranks (0 = default)")
     ap.add_argument("--token-tile", type=int, default=0, help="force a kernel: 16/32/64/128, 8 = single-launch kernel")
     ap.add_argument("--profile-only", action="store_true", help="run warmup+steps eager steps and exit (for ncu)")
     args = ap.parse_args()

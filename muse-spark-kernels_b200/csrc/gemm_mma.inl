@@ -16,6 +16,9 @@
       if (!mbar_wait(&ctl.d_empty[db], (duse & 1u) ^ 1u, abortw)) { ok = false; break; }
       tc_fence_after();
       const uint32_t d_tmem = tmem + db * (2 * N) + mg * N;
+      // a ragged last token tile of an expert only pays for the columns it has (MMA N in steps of 16):
+      // at N = 128 an MMA costs 64 cycles, at N = 16 nine
+      const uint32_t idesc_u = N >= 64 ? idesc_f16(FMT_F16, FMT_F16, 128, static_cast<uint32_t>((ui.rows + 15) & ~15)) : idesc;
       const uint32_t a_base = tmem + C::A_BASE + mg * C::A_GROUP_COLS;
       for (int ks = ks0; ks < ks1 && ok; ++ks, ++it) {
         const uint32_t slot = it % NST, par = (it / NST) & 1u;
@@ -33,7 +36,7 @@
               const uint64_t bdesc = C::TMA_B ? smem_desc_kmajor_sw128(b_addr + (k16 >> 2) * (N * 128) + (k16 & 3) * 32)
                                               : smem_desc_kmajor_noswz(b_addr + k16 * 256, B_LBO, B_SBO);
               const uint32_t acc = (ks > ks0 || k16 > 0) ? 1u : 0u;
-              mma_ts(d_tmem, a_base + as * C::SLOT_COLS + kk * 8, bdesc, idesc, acc);
+              mma_ts(d_tmem, a_base + as * C::SLOT_COLS + kk * 8, bdesc, idesc_u, acc);
             }
             tc_commit(&ctl.a_empty[mg][as]);
           }

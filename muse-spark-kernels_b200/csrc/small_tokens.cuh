@@ -14,13 +14,21 @@
 // it produces are partial sums ("pieces"); the consumer adds the pieces of an output element in
 // a fixed order that depends only on the shapes and the grid, never on timing.
 //
-// Math: a warp owns 16 weight rows of a stage tile. Lane (g, q) (g = lane / 4, q = lane % 4)
-// loads the 16-byte chunks q and q + 4 of rows g and g + 8, decodes them with the hardware
-// converts (layout.cuh) straight into the A fragments of mma.sync.m16n8k16 (F16 x F16 -> FP32,
-// the same exact products and FP32 accumulation as the tcgen05 path), the up to 8 token rows of
-// the expert are the B fragment's 8 columns. The K order inside an MMA is whatever the lanes
-// hold, so the activations are laid out in shared memory in the matching permuted order and a
-// lane reads its B fragment with one conflict-free 8-byte load.
+// Data flow: warp 16 is the producer: one lane copies this CTA's stage tiles, in order, into a
+// ring of shared-memory slots (one 18 KB bulk copy per tile, completing on an mbarrier; the
+// second stream's first tiles are already landing while the grid barrier between the streams is
+// crossed). The 16 consumer warps work in two groups of 8; group i takes every second stage tile
+// and its 8 warps take 16 weight rows each.
+//
+// Math: lane (g, q) (g = lane / 4, q = lane % 4) of a consumer warp fetches with ldmatrix, for each
+// of the tile's 8 chunks, the 8 codes K = 32 c + 8 q .. + 7 of rows g and g + 8 (a matrix = 8
+// rows x one 16-byte chunk = 128 contiguous bytes of the packed layout: no bank conflicts),
+// decodes them with the hardware converts (layout.cuh) straight into the A fragments of
+// mma.sync.m16n8k16 (F16 x F16 -> FP32, the same exact products and FP32 accumulation as the
+// tcgen05 path); the up to 8 token rows of the expert are the B fragment's 8 columns. The K
+// order inside an MMA is whatever the lanes hold, so the activations are laid out in shared
+// memory in the matching permuted order and a lane reads its B fragment with one conflict-free
+// 8-byte load.
 #pragma once
 #include <cstdint>
 #include <cuda_bf16.h>
@@ -32,9 +40,6 @@
 
 namespace msk {
 
-#ifndef MSK_ST_VARIANT
-#define MSK_ST_VARIANT 0   // 1, 2: measuring builds, never shipped
-#endif
 #ifndef MSK_ST_GROUPS
 #define MSK_ST_GROUPS 2
 #endif

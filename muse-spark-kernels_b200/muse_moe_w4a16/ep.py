@@ -263,7 +263,7 @@ def bench_ep(args, spec, dev, rank, world, metric, unit, clock_sampler_cls, load
     H, I, E, k, T = s["H"], s["I"], s["E"], s["k"], spec["T"]
     per = E // world
     weights = inputs.make_weights_random_bytes(H, I, per, 1000 + rank, dev)
-    mod = EPModule(weights, rank, world, E, k, T)
+    mod = EPModule(weights, rank, world, E, k, T, chunks=(getattr(args, "ep_chunks", 0) or None))
     del weights
     torch.cuda.empty_cache()
     pool = [inputs.make_inputs(spec["shape"], T, 17 * rank + i, dev)[0] for i in range(4)]

@@ -39,8 +39,8 @@ def _worker(rank, world, port, ret):
     local = {key: v[rank * per:(rank + 1) * per].contiguous() for key, v in w.items()}
     full = moe.prepare(w, n_experts=E, top_k=k, max_tokens=T)
     errs, stats = [], []
-    for transport in ("symm", "collective"):
-        mod = ep.EPModule(local, rank, world, E, k, T, transport=transport)
+    for transport, chunks in (("symm", 1), ("symm", 2), ("collective", None)):
+        mod = ep.EPModule(local, rank, world, E, k, T, transport=transport, chunks=chunks)
         for step in range(3):                                     # both buffer parities and their reuse
             g = torch.Generator(device=dev).manual_seed(70 + rank + 10 * step)
             x = torch.randn((T, H), generator=g, device=dev).to(torch.bfloat16)
