@@ -212,9 +212,9 @@ class EPModule:
         self.n_experts, self.top_k, self.per_rank = n_experts, top_k, n_experts // world
         self.transport = transport
         if transport == "symm":
-            # two chunks from four ranks on: half the exchange hides behind the expert kernels, and a
-            # chunk still brings enough rows per expert to fill its 128-token tiles
-            self.chunks = chunks if chunks is not None else (2 if world >= 4 and world % 2 == 0 else 1)
+            # from four ranks on, chunks of two source ranks: measured on 8 GPUs, 4 chunks 4.63 ms per step,
+            # 2 chunks 5.45 ms (less of the exchange hidden), 8 chunks lose more in half-filled token tiles
+            self.chunks = chunks if chunks is not None else (world // 2 if world >= 4 and world % 2 == 0 else 1)
             rows = (world // self.chunks) * tokens_per_rank
         elif transport == "collective":
             self.chunks, rows = 1, world * tokens_per_rank
