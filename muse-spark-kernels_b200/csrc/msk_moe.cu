@@ -453,7 +453,10 @@ static Plan make_plan(const MskMoeCfg* c, int T) {
     p.N = c->token_tile;
   } else {
     const double rpe = static_cast<double>(T) * c->top_k / c->n_experts;  // mean tokens per expert
-    p.N = rpe <= 8 ? 16 : rpe <= 16 ? 32 : rpe <= 32 ? 64 : 128;
+    // measured at H4096 I1536 E128: T = 128 (rpe 8): 270 / 290 / 296 us with 16 / 32 / 64-token tiles;
+    // T = 256 (rpe 16): 375 / 326 / 314 us; T = 512 (rpe 32): 618 / 506 / 345 us. A tile costs about the
+    // same up to 64 tokens (the weight decode bounds it), so past a few rows per expert wider is better
+    p.N = rpe <= 8 ? 16 : rpe <= 12 ? 32 : rpe <= 32 ? 64 : 128;
   }
   const double tiles = expected_tiles(c, T, p.N);
   p.s13 = c->split_k13 > 0 ? c->split_k13 : pick_split(tiles * (c->inter / 128), c->hidden / KS, p.grid);
