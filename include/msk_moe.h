@@ -173,7 +173,8 @@ int msk_moe_forward_static(const MskMoeCfg* cfg, const void* packed13, const voi
 int msk_moe_plan(const MskMoeCfg* cfg, int n_tokens, int* host_out);
 
 /* Views into the workspace after msk_moe_forward (device pointers, for parity tests):
- * which: 0 cnt, 1 off, 2 perm, 3 inv, 4 inter (fp16 [R, I], holding bf16-rounded values), 5 y (fp32 [R, H]),
+ * which: 0 cnt, 1 off, 2 perm, 3 inv, 4 inter (fp16 [R, I], holding bf16-rounded values), 5 y (fp32 [R, H]; bf16 [R, H] when the plan's
+ * token tile is 128),
  * 6 trace (uint64 [2 GEMMs][256 CTAs][16 stamps], ns; written when cfg->trace != 0). */
 int msk_moe_workspace_view(const MskMoeCfg* cfg, void* workspace, int which, void** host_ptr);
 

@@ -95,6 +95,7 @@ struct GemmParams {
   int top_k;
   int splits;
   int evict_first;
+  int y_bf16;                // PHASE 1 without K splits: y rows as BF16 instead of FP32
 };
 
 // Trace slots (per CTA, nanoseconds): the counterpart of the reference's DBG(k) stamps
@@ -190,14 +191,21 @@ __device__ __forceinline__ void epilogue_columns(const GemmParams& p, const Unit
     float osc = gsc;
     if (p.post_norm_w != nullptr) osc *= 1.0f + __bfloat162float(p.post_norm_w[col]);
     float* outp = static_cast<float*>(p.outp) + static_cast<size_t>(ui.row0) * p.out_ld + col;
+    __nv_bfloat16* outb = static_cast<__nv_bfloat16*>(p.outp) + static_cast<size_t>(ui.row0) * p.out_ld + col;
     for (int c0 = c_beg; c0 < c_end; c0 += 32) {
       if (c0 >= ui.rows) break;
       uint32_t r[32];
       tmem_ld32(d_tmem + tile * N + c0, r);
       tmem_wait_ld();
+      if (p.y_bf16) {   // wide token tiles: y rows in BF16, as the reference's wide-tile build keeps them
 #pragma unroll
-      for (int j = 0; j < 32; ++j)
-        if (c0 + j < ui.rows) outp[static_cast<size_t>(c0 + j) * p.out_ld] = __uint_as_float(r[j]) * osc;
+        for (int j = 0; j < 32; ++j)
+          if (c0 + j < ui.rows) outb[static_cast<size_t>(c0 + j) * p.out_ld] = __float2bfloat16_rn(__uint_as_float(r[j]) * osc);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (c0 + j < ui.rows) outp[static_cast<size_t>(c0 + j) * p.out_ld] = __uint_as_float(r[j]) * osc;
+      }
     }
   }
 }

@@ -132,12 +132,36 @@ constexpr int COMBINE_WIDE_TOKENS = 512;  // from here on two blocks per SM, two
 
 // G = slots whose rows are loaded together (one memory latency per group instead of one per
 // slot; the sums still run in slot order). G = 4 for few tokens (latency), G = 2 with two blocks
-// per SM for many (one block's loads overlap the other's reduction and stores). Slots without a
+// per SM for many (one block's loads overlap the other's reduction and stores); BF16 rows need
+// half the registers while in flight, so they get G = 4 and two blocks per SM. Slots without a
 // local route (inv < 0) are squeezed out first, keeping their order, so an expert-parallel rank
 // that owns one or two of a token's eight routes pays for one group, and a token without any
 // local route only writes zeros.
-template <int G>
-__global__ void __launch_bounds__(COMBINE_THREADS, G == 2 ? 2 : 1)
+// Four consecutive y values of a row as they sit in registers while their group is in flight:
+// FP32 (16 bytes) or BF16 (8 bytes, for the wide token tile), expanded when used.
+template <bool YB> struct YQuad;
+template <> struct YQuad<false> {
+  float4 v;
+  __device__ __forceinline__ void zero() { v = make_float4(0.f, 0.f, 0.f, 0.f); }
+  __device__ __forceinline__ void load(const float* y, size_t row_elems, int j) {
+    v = __ldcs(reinterpret_cast<const float4*>(y + row_elems) + j);
+  }
+  __device__ __forceinline__ float4 get() const { return v; }
+};
+template <> struct YQuad<true> {
+  uint2 b;
+  __device__ __forceinline__ void zero() { b = make_uint2(0u, 0u); }
+  __device__ __forceinline__ void load(const float* y, size_t row_elems, int j) {
+    b = __ldcs(reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(y) + row_elems) + j);
+  }
+  __device__ __forceinline__ float4 get() const {
+    return make_float4(__uint_as_float(b.x << 16), __uint_as_float(b.x & 0xFFFF0000u), __uint_as_float(b.y << 16),
+                       __uint_as_float(b.y & 0xFFFF0000u));
+  }
+};
+
+template <int G, bool YB, int MINB>
+__global__ void __launch_bounds__(COMBINE_THREADS, MINB)
     combine_kernel(const float* __restrict__ y, const int32_t* __restrict__ inv, const float* __restrict__ tw,
                    __nv_bfloat16* __restrict__ out, int H, int k, int post_norm, float eps) {
   __shared__ float wsum[G][COMBINE_THREADS / 32];
@@ -172,24 +196,26 @@ __global__ void __launch_bounds__(COMBINE_THREADS, G == 2 ? 2 : 1)
       q[g] = in ? s_q[s0 + g] : -1;
       wgt[g] = in ? s_w[s0 + g] : 0.f;
     }
-    float4 v[G][COMBINE_MAX_F4];
+    YQuad<YB> v[G][COMBINE_MAX_F4];
     float ss[G];
 #pragma unroll
     for (int g = 0; g < G; ++g) {
       ss[g] = 0.f;
-      const float4* row = reinterpret_cast<const float4*>(y + static_cast<size_t>(q[g] < 0 ? 0 : q[g]) * H);
+      const size_t r = static_cast<size_t>(q[g] < 0 ? 0 : q[g]) * H;
 #pragma unroll
       for (int i = 0; i < COMBINE_MAX_F4; ++i) {
-        v[g][i] = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (q[g] >= 0 && i * COMBINE_THREADS + tid < n4) v[g][i] = __ldcs(row + i * COMBINE_THREADS + tid);
+        v[g][i].zero();
+        if (q[g] >= 0 && i * COMBINE_THREADS + tid < n4) v[g][i].load(y, r, i * COMBINE_THREADS + tid);
       }
     }
     if (post_norm) {
 #pragma unroll
       for (int g = 0; g < G; ++g) {
 #pragma unroll
-        for (int i = 0; i < COMBINE_MAX_F4; ++i)
-          ss[g] += v[g][i].x * v[g][i].x + v[g][i].y * v[g][i].y + v[g][i].z * v[g][i].z + v[g][i].w * v[g][i].w;
+        for (int i = 0; i < COMBINE_MAX_F4; ++i) {
+          const float4 f = v[g][i].get();
+          ss[g] += f.x * f.x + f.y * f.y + f.z * f.z + f.w * f.w;
+        }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) ss[g] += __shfl_xor_sync(0xffffffffu, ss[g], o);
       }
@@ -212,8 +238,9 @@ __global__ void __launch_bounds__(COMBINE_THREADS, G == 2 ? 2 : 1)
       if (q[g] < 0) continue;
 #pragma unroll
       for (int i = 0; i < COMBINE_MAX_F4; ++i) {
-        acc[i].x += v[g][i].x * wgt[g]; acc[i].y += v[g][i].y * wgt[g];
-        acc[i].z += v[g][i].z * wgt[g]; acc[i].w += v[g][i].w * wgt[g];
+        const float4 f = v[g][i].get();
+        acc[i].x += f.x * wgt[g]; acc[i].y += f.y * wgt[g];
+        acc[i].z += f.z * wgt[g]; acc[i].w += f.w * wgt[g];
       }
     }
   }
@@ -469,7 +496,7 @@ static Plan make_plan(const MskMoeCfg* c, int T) {
 
 // Workspace carving. Everything is sized for max_tokens with the worst plan.
 struct Carve {
-  size_t status, trace, cnt, off, perm, inv, tickets, small_ctl, inter, y, partial, xs, small_part, total;
+  size_t status, trace, cnt, off, perm, inv, tickets, small_ctl, sort_blk, inter, y, partial, xs, small_part, total;
 };
 constexpr size_t MAX_SPLIT = 8;
 constexpr size_t TRACE_CTAS = 256;
@@ -510,6 +537,7 @@ static Carve carve(const MskMoeCfg* c, int T) {
   const size_t pairs = std::max(c->inter / 128, c->hidden / 256);
   k.tickets = o; o += 2 * round_up(max_tiles(c, T) * pairs * 4, 256);  // one region per GEMM
   k.small_ctl = o; o += 1024;  // few-token kernel: grid barrier (2 words), per-token tickets at +64, row weights at +256
+  k.sort_blk = o; o += static_cast<size_t>(SORT_MULTI_BLOCKS) * MAX_LOCAL_EXPERTS * 4;  // per-CTA counts of the multi-CTA sort
   k.inter = o; o += round_up(R * c->inter * 2, 256);
   k.y = o; o += round_up(R * c->hidden * 4, 256);
   k.partial = o; o += 2 * round_up(partial_floats(c, T) * 4, 256);  // one region per GEMM
@@ -687,7 +715,18 @@ int msk_moe_route(const MskMoeCfg* cfg, const float* logits, const float* bias, 
 
 static int launch_sort(const MskMoeCfg* cfg, const int32_t* ids, int n_tokens, int32_t* cnt, int32_t* off,
                        int32_t* perm, int32_t* inv, cudaStream_t st, const __nv_bfloat16* x = nullptr,
-                       __half* xh = nullptr) {
+                       __half* xh = nullptr, int32_t* blk = nullptr) {
+  const int n_entries = n_tokens * cfg->top_k;
+  if (blk != nullptr && xh == nullptr && n_entries >= SORT_MULTI_MIN) {
+    // many entries: the same stable sort on several CTAs (count, scan, scatter)
+    const int nb = SORT_MULTI_BLOCKS;
+    sort_multi_count_kernel<<<nb, SORT_THREADS, sizeof(SortSmem), st>>>(ids, n_entries, cfg->local_start,
+                                                                        cfg->local_count, blk);
+    sort_multi_scan_kernel<<<1, MAX_LOCAL_EXPERTS, 0, st>>>(blk, nb, cfg->local_count, cnt, off);
+    sort_multi_scatter_kernel<<<nb, SORT_THREADS, sizeof(SortSmem), st>>>(ids, n_entries, cfg->local_start,
+                                                                          cfg->local_count, blk, perm, inv);
+    return static_cast<int>(cudaGetLastError());
+  }
   static bool attr_set[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -909,7 +948,8 @@ static int forward_impl(const MskMoeCfg* cfg, const void* packed13, const void* 
       e = static_cast<int>(cudaGetLastError());
       if (e != 0) return e;
     }
-    e = launch_sort(cfg, topk_ids, n_tokens, cnt, off, perm, inv, st, xin, xh_in_sort);
+    e = launch_sort(cfg, topk_ids, n_tokens, cnt, off, perm, inv, st, xin, xh_in_sort,
+                    reinterpret_cast<int32_t*>(b + k.sort_blk));
   }
   if (e != 0) return e;
   if (ev) cudaEventRecord(ev[1], st);
@@ -962,6 +1002,7 @@ static int forward_impl(const MskMoeCfg* cfg, const void* packed13, const void* 
   if (trace) p.trace = trace + TRACE_WORDS;
   p.post_norm_w = static_cast<const __nv_bfloat16*>(post_norm_w);
   p.K = cfg->inter; p.out_ld = cfg->hidden; p.n_pairs = cfg->hidden / 256; p.splits = plan.s2;
+  p.y_bf16 = (plan.N == 128 && plan.s2 == 1) ? 1 : 0;  // the wide tile: half the y bytes written and read back
   if (tma_b) {
     e = encode_act_map(&p.tmap_act, inter, r_max, cfg->inter, plan.N);
     if (e != 0) return e;
@@ -981,7 +1022,8 @@ static int forward_impl(const MskMoeCfg* cfg, const void* packed13, const void* 
     at[0].val.programmaticStreamSerializationAllowed = 1;
     lc.attrs = at;
     lc.numAttrs = 1;
-    auto* kern = n_tokens >= COMBINE_WIDE_TOKENS ? combine_kernel<2> : combine_kernel<4>;
+    const bool wide = n_tokens >= COMBINE_WIDE_TOKENS;
+    auto* kern = p.y_bf16 ? combine_kernel<4, true, 2> : (wide ? combine_kernel<2, false, 2> : combine_kernel<4, false, 1>);
     e = static_cast<int>(cudaLaunchKernelEx(&lc, kern, static_cast<const float*>(y),
                                             static_cast<const int32_t*>(inv), topk_weights,
                                             static_cast<__nv_bfloat16*>(out), static_cast<int>(cfg->hidden),
@@ -1126,7 +1168,7 @@ int msk_moe_forward_static(const MskMoeCfg* cfg, const void* packed13, const voi
   p.K = cfg->inter; p.out_ld = cfg->hidden; p.n_pairs = cfg->hidden / 256;
   e = launch_gemm_n<1>(16, p, grid, st);
   if (e != 0) return e;
-  combine_kernel<4><<<static_cast<unsigned>(n_tokens), COMBINE_THREADS, 0, st>>>(
+  combine_kernel<4, false, 1><<<static_cast<unsigned>(n_tokens), COMBINE_THREADS, 0, st>>>(
       y, inv, topk_weights, static_cast<__nv_bfloat16*>(out), cfg->hidden, cfg->top_k, post_norm_w != nullptr ? 1 : 0,
       cfg->post_norm_eps);
   return static_cast<int>(cudaGetLastError());
@@ -1169,7 +1211,7 @@ int msk_moe_attrs(int which, int token_tile, int* host_out) {
       }
       break;
     }
-    case 4: e = cudaFuncGetAttributes(&a, combine_kernel<4>); break;
+    case 4: e = cudaFuncGetAttributes(&a, combine_kernel<4, false, 1>); break;
     default: return MSK_ERR_SHAPE;
   }
   if (e != cudaSuccess) return static_cast<int>(e);

@@ -250,6 +250,123 @@ __global__ void __launch_bounds__(SORT_THREADS) sort_kernel(const int32_t* __res
   sort_entries_block(sm, ids, n, lo, nloc, cnt, off, perm, inv);
 }
 
+// ---- the same stable sort on several CTAs, for many entries (prefill, expert-parallel chunks)
+// CTA b owns the contiguous entry range [b chunk, (b + 1) chunk). Three launches:
+//   count    per-CTA per-expert counts                                   -> blk[b][e]
+//   scan     one CTA: exclusive prefix over (expert, CTA) in that order  -> cnt, off, blk[b][e] = first
+//            sorted position of CTA b's entries of expert e
+//   scatter  each CTA ranks its entries as the single-CTA sort does (warps own ascending
+//            sub-ranges, in-warp rank by match/popc) on top of its bases
+// Entries of one expert keep ascending entry order across CTAs, warps and lanes: the same
+// permutation as the single-CTA sort, bit for bit.
+constexpr int SORT_MULTI_MIN = 16384;    // entries from which several CTAs sort
+constexpr int SORT_MULTI_BLOCKS = 64;
+
+// Pass 1 of a CTA over its range: sm.wcnt[w][e] = entries of expert e in warp w's sub-range.
+__device__ __forceinline__ void sort_count_range(SortSmem& sm, const int32_t* ids, int beg, int end, int lo, int nloc,
+                                                 int& wbeg, int& wend) {
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int n = max(end - beg, 0);
+  const int chunk = ((n + SORT_WARPS - 1) / SORT_WARPS + 31) & ~31;
+  wbeg = beg + warp * chunk;
+  wend = min(end, wbeg + chunk);
+  for (int i = tid; i < SORT_WARPS * MAX_LOCAL_EXPERTS; i += SORT_THREADS) (&sm.wcnt[0][0])[i] = 0;
+  __syncthreads();
+  for (int base = wbeg; base < wend; base += 32) {
+    const int i = base + lane;
+    const int l = i < wend ? local_expert(ids[i], lo, nloc) : -1;
+    const unsigned peers = __match_any_sync(0xffffffffu, l);
+    if (l >= 0 && (peers & ((1u << lane) - 1u)) == 0u) sm.wcnt[warp][l] += __popc(peers);
+    __syncwarp();
+  }
+  __syncthreads();
+}
+
+__global__ void __launch_bounds__(SORT_THREADS) sort_multi_count_kernel(const int32_t* __restrict__ ids, int n, int lo,
+                                                                        int nloc, int32_t* __restrict__ blk) {
+  extern __shared__ __align__(16) unsigned char sort_smem_raw[];
+  SortSmem& sm = *reinterpret_cast<SortSmem*>(sort_smem_raw);
+  const int per = (n + gridDim.x - 1) / gridDim.x;
+  const int beg = min(n, static_cast<int>(blockIdx.x) * per), end = min(n, beg + per);
+  int wbeg, wend;
+  sort_count_range(sm, ids, beg, end, lo, nloc, wbeg, wend);
+  const int tid = threadIdx.x;
+  if (tid < nloc) {
+    int acc = 0;
+    for (int w = 0; w < SORT_WARPS; ++w) acc += sm.wcnt[w][tid];
+    blk[blockIdx.x * MAX_LOCAL_EXPERTS + tid] = acc;
+  }
+}
+
+__global__ void __launch_bounds__(MAX_LOCAL_EXPERTS) sort_multi_scan_kernel(int32_t* __restrict__ blk, int n_blocks,
+                                                                            int nloc, int32_t* __restrict__ cnt,
+                                                                            int32_t* __restrict__ off) {
+  __shared__ int wsum[MAX_LOCAL_EXPERTS / 32];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  int total = 0;
+  if (tid < nloc) {
+    for (int b = 0; b < n_blocks; ++b) {
+      const int c = blk[b * MAX_LOCAL_EXPERTS + tid];
+      blk[b * MAX_LOCAL_EXPERTS + tid] = total;
+      total += c;
+    }
+    cnt[tid] = total;
+  }
+  int incl = total;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int v = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += v;
+  }
+  if (lane == 31) wsum[warp] = incl;
+  __syncthreads();
+  int ex = incl - total;
+  for (int w = 0; w < warp; ++w) ex += wsum[w];
+  if (tid < nloc) {
+    off[tid] = ex;
+    if (tid == nloc - 1) off[nloc] = ex + total;
+    for (int b = 0; b < n_blocks; ++b) blk[b * MAX_LOCAL_EXPERTS + tid] += ex;
+  }
+}
+
+__global__ void __launch_bounds__(SORT_THREADS) sort_multi_scatter_kernel(const int32_t* __restrict__ ids, int n, int lo,
+                                                                          int nloc, const int32_t* __restrict__ blk,
+                                                                          int32_t* __restrict__ perm,
+                                                                          int32_t* __restrict__ inv) {
+  extern __shared__ __align__(16) unsigned char sort_smem_raw[];
+  SortSmem& sm = *reinterpret_cast<SortSmem*>(sort_smem_raw);
+  const int per = (n + gridDim.x - 1) / gridDim.x;
+  const int beg = min(n, static_cast<int>(blockIdx.x) * per), end = min(n, beg + per);
+  int wbeg, wend;
+  sort_count_range(sm, ids, beg, end, lo, nloc, wbeg, wend);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid < nloc) {   // exclusive prefix over the warps, and this CTA's base of the expert
+    int acc = 0;
+    for (int w = 0; w < SORT_WARPS; ++w) {
+      const int c = sm.wcnt[w][tid];
+      sm.wcnt[w][tid] = acc;
+      acc += c;
+    }
+    sm.tot[tid] = blk[blockIdx.x * MAX_LOCAL_EXPERTS + tid];
+  }
+  __syncthreads();
+  for (int base = wbeg; base < wend; base += 32) {
+    const int i = base + lane;
+    const int l = i < wend ? local_expert(ids[i], lo, nloc) : -1;
+    const unsigned peers = __match_any_sync(0xffffffffu, l);
+    const int rank = __popc(peers & ((1u << lane) - 1u));
+    int q = -1;
+    if (l >= 0) q = sm.tot[l] + sm.wcnt[warp][l] + rank;
+    __syncwarp();
+    if (l >= 0 && rank == 0) sm.wcnt[warp][l] += __popc(peers);
+    __syncwarp();
+    if (i < wend) {
+      inv[i] = q;
+      if (q >= 0) perm[q] = i;
+    }
+  }
+}
+
 // Routing and sort in one launch for small token counts: every warp routes the tokens
 // t = warp, warp + 32, ...; after a block barrier the same CTA sorts the entries it just wrote.
 __global__ void __launch_bounds__(SORT_THREADS) route_sort_kernel(const float* __restrict__ logits,

@@ -230,7 +230,11 @@ def workspace_views(state, T):
     perm = view(2, T * k * 4, torch.int32)
     inv = view(3, T * k * 4, torch.int32)
     inter = view(4, R * cfg.inter * 2, torch.float16).view(R, cfg.inter)
-    y = view(5, R * cfg.hidden * 4, torch.float32).view(R, cfg.hidden)
+    n_tile, _, s2, _ = plan(state, T)
+    if n_tile == 128 and s2 == 1:      # the wide token tile keeps y in BF16
+        y = view(5, R * cfg.hidden * 2, torch.bfloat16).view(R, cfg.hidden)
+    else:
+        y = view(5, R * cfg.hidden * 4, torch.float32).view(R, cfg.hidden)
     return {"cnt": cnt, "off": off, "perm": perm, "inv": inv, "inter": inter, "y": y}
 
 

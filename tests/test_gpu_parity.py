@@ -194,7 +194,8 @@ def test_forward_tiny_config0(cuda_dev):
 
 @pytest.mark.parametrize("T,tile,s13,s2,post", [(1, 0, 0, 0, False), (5, 16, 1, 1, True), (5, 16, 2, 2, False),
                                                 (40, 32, 1, 1, False), (70, 64, 1, 1, True),
-                                                (300, 128, 1, 1, False), (9, 16, 2, 1, True)])
+                                                (300, 128, 1, 1, False), (9, 16, 2, 1, True),
+                                                (600, 0, 0, 0, True), (300, 128, 1, 1, True)])
 def test_forward_small_shapes(cuda_dev, T, tile, s13, s2, post):
     m, inputs, _lib, orc = _mods()
     out, ref, parts, views, st, _ = _run_forward(m, inputs, orc, cuda_dev, 512, 256, 8, 2, T, seed=T, post_norm=post,
@@ -319,3 +320,14 @@ def test_forward_zero_tokens_and_state_deepcopy(cuda_dev):
     data = {"hidden_states": torch.randn((3, H), generator=g, device=cuda_dev).to(torch.bfloat16),
             "router_logits": torch.randn((3, E), generator=g, device=cuda_dev)}
     assert torch.equal(m.kernel_fn(data, st), m.kernel_fn(data, st2))
+
+
+@pytest.mark.parametrize("T,E,k,lo,nloc", [(8192, 8, 2, 0, 8), (4096, 16, 4, 4, 8)])
+def test_forward_many_entries_sorted_on_several_ctas(cuda_dev, T, E, k, lo, nloc):
+    """From 16384 routed entries on, the stable sort runs on several CTAs (count, scan, scatter); the
+    tables must still equal the oracle's stable sort bit for bit, with and without a local range."""
+    m, inputs, _lib, orc = _mods()
+    out, ref, parts, views, st, _ = _run_forward(m, inputs, orc, cuda_dev, 512, 256, E, k, T, seed=77, post_norm=True,
+                                                 lo=lo, nloc=nloc, logits_kind="zipf")
+    assert T * k >= 16384
+    _check_forward(out, ref, parts, views)
