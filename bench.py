@@ -329,7 +329,9 @@ def run_gpu(args, spec):
                    "touched_experts_mean": mean_touched},
         "e2e": {"value": T * args.steps / (sum(e2e_ms) * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "ms_per_step": sum(e2e_ms) / args.steps},
-        "gpu_launches": (1 if fused else 4 if T <= 32 else 5) * args.steps,
+        # per step: fused top-k + sort | top-k, sort (three launches from 16384 entries on), F16 row copy;
+        # two GEMMs; combine
+        "gpu_launches": (1 if fused else 4 if T <= 32 else 6 + (2 if T * k >= 16384 else 0)) * args.steps,
         "roofline": roof,
         "step_roofline": {"hbm_frac": step_bytes / (total_ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
                           "tensor_frac": step_flops / (total_ms * 1e-3) / 1e12 / peaks["bf16_tflops_sustained"],

@@ -321,7 +321,9 @@ def bench_ep(args, spec, dev, rank, world, metric, unit, clock_sampler_cls, load
             "e2e": {"value": T * world * args.steps / (ms_e2e * 1e-3), "unit": unit,
                     "h2d_bytes_per_step": (T * H * 2 + T * E * 4) * world, "d2h_bytes_per_step": T * H * 2 * world,
                     "ms_per_step": ms_e2e / args.steps},
-            "gpu_launches": (2 + 5 * mod.chunks) * args.steps * world,
+            # per rank and step: top-k, the final rank-order sum, and per chunk the sort (three launches from
+            # 16384 entries on), the F16 row copy, two GEMMs and the combine
+            "gpu_launches": (2 + (7 if (world // mod.chunks) * T * k >= 16384 else 5) * mod.chunks) * args.steps * world,
             "roofline": {"bound": "tensor", "achieved": flops / world / (ms * 1e-3) / 1e12,
                          "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
                          "frac": flops / world / (ms * 1e-3) / 1e12 / peaks["bf16_tflops_sustained"], "traffic": None,
