@@ -152,6 +152,63 @@ def kernel_fn(data, state, return_routing=False, out=None):
     return out
 
 
+class GraphedStep:
+    """kernel_fn for a fixed token count, captured once into a CUDA graph over static device buffers
+    (how the decode layer consumes the module: its steps are graph replays). Calling it copies the
+    inputs into the static buffers, replays the graph on the current stream and returns the static
+    output tensor, which the next call overwrites. Device inputs are copied tensor by tensor; host
+    inputs are first packed into one pinned staging block (a ring of them, each guarded by an
+    event) so that they reach the device in a single asynchronous copy. Inputs: hidden_states and
+    either router_logits or topk_ids + topk_weights, whichever `like` holds."""
+
+    STAGES = 4
+
+    def __init__(self, state, like):
+        self.state = state
+        dev = state["packed13"].device
+        self.keys = [k for k in ("hidden_states", "router_logits", "topk_ids", "topk_weights") if like.get(k) is not None]
+        spans, total = {}, 0
+        for k in self.keys:
+            nbytes = like[k].numel() * like[k].element_size()
+            spans[k] = (total, nbytes)
+            total += (nbytes + 255) // 256 * 256
+        self.block = torch.empty(total, dtype=torch.uint8, device=dev)
+        self.static = {k: self.block[o:o + n].view(like[k].dtype).view(tuple(like[k].shape)) for k, (o, n) in spans.items()}
+        self.staging = [torch.empty(total, dtype=torch.uint8).pin_memory() for _ in range(self.STAGES)]
+        self.staged = [{k: b[o:o + n].view(like[k].dtype).view(tuple(like[k].shape)) for k, (o, n) in spans.items()}
+                       for b in self.staging]
+        self.copied = [None] * self.STAGES
+        self.turn = 0
+        for k in self.keys:
+            self.static[k].copy_(like[k])
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):                      # warm-up outside the capture
+            kernel_fn(self.static, state)
+        torch.cuda.current_stream(dev).wait_stream(side)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.out = kernel_fn(self.static, state)
+
+    def __call__(self, data):
+        if all(not data[k].is_cuda for k in self.keys):
+            i = self.turn
+            self.turn = (i + 1) % self.STAGES
+            if self.copied[i] is not None:
+                self.copied[i].synchronize()               # the copy that last used this block has finished
+            for k in self.keys:
+                self.staged[i][k].copy_(data[k])
+            self.block.copy_(self.staging[i], non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record()
+            self.copied[i] = ev
+        else:
+            for k in self.keys:
+                self.static[k].copy_(data[k], non_blocking=True)
+        self.graph.replay()
+        return self.out
+
+
 def kernel_fn_timed(data, state):
     """kernel_fn with CUDA events around each launch of the expert step; synchronises.
     Returns (out, [ms sort, ms gate/up GEMM, ms down GEMM, ms combine]). Measuring only."""

@@ -331,3 +331,24 @@ def test_forward_many_entries_sorted_on_several_ctas(cuda_dev, T, E, k, lo, nloc
                                                  lo=lo, nloc=nloc, logits_kind="zipf")
     assert T * k >= 16384
     _check_forward(out, ref, parts, views)
+
+
+def test_graphed_step_with_pinned_host_inputs(cuda_dev):
+    """GraphedStep (static buffers + CUDA graph) returns what kernel_fn returns, bit for bit, for
+    device inputs and for pinned host inputs, call after call."""
+    m, inputs, _lib, orc = _mods()
+    H, I, E, k, T = 1024, 512, 16, 4, 5
+    w = inputs.make_weights(H, I, E, 51, cuda_dev, post_norm=True)
+    st = m.prepare(w, n_experts=E, top_k=k, max_tokens=T)
+    g = torch.Generator(device=cuda_dev).manual_seed(9)
+    datas = [{"hidden_states": torch.randn((T, H), generator=g, device=cuda_dev).to(torch.bfloat16),
+              "router_logits": torch.randn((T, E), generator=g, device=cuda_dev)} for _ in range(3)]
+    step = m.GraphedStep(st, datas[0])
+    for d in datas + datas[:1]:
+        want = m.kernel_fn(d, st)
+        host = {key: v.cpu().pin_memory() for key, v in d.items()}
+        got_dev = step(d).clone()
+        got_host = step(host).clone()
+        torch.cuda.synchronize()
+        assert torch.equal(got_dev, want) and torch.equal(got_host, want)
+    assert m.read_status(st) == 0
