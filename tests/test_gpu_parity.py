@@ -352,3 +352,30 @@ def test_graphed_step_with_pinned_host_inputs(cuda_dev):
         torch.cuda.synchronize()
         assert torch.equal(got_dev, want) and torch.equal(got_host, want)
     assert m.read_status(st) == 0
+
+
+def test_okc_ext_runs_the_decode_layer_call_site(cuda_dev):
+    """The decode layer's call (muse_decode_layer/py/06_kernel_fn.py:140-149): local ids with -1 for
+    another GPU's expert, lo = 0, an output slice filled in place, in chunks."""
+    m, inputs, _lib, orc = _mods()
+    from muse_moe_w4a16.compat import OkcExt
+
+    H, I, nloc, k, T = 1024, 512, 8, 4, 11
+    w = inputs.make_weights(H, I, nloc, 61, cuda_dev, post_norm=True)
+    st = m.prepare(w, local_start=0, n_experts=nloc, top_k=k, max_tokens=8)
+    ext = OkcExt(st)
+    g = torch.Generator(device=cuda_dev).manual_seed(4)
+    x = torch.randn((T, H), generator=g, device=cuda_dev).to(torch.bfloat16)
+    lids = torch.randint(-1, nloc, (T, k), generator=g, device=cuda_dev, dtype=torch.int32)
+    wts = torch.rand((T, k), generator=g, device=cuda_dev)
+    out = torch.full((T, H), float("nan"), dtype=torch.bfloat16, device=cuda_dev)
+    ext.okc_set_pdl(1)
+    for m0 in range(0, T, 8):
+        m1 = min(T, m0 + 8)
+        ext.okc_run(None, None, x[m0:m1], lids[m0:m1], wts[m0:m1], out[m0:m1], 0, nloc, 148)
+    torch.cuda.synchronize()
+    ref = orc.moe_forward(x, lids, wts, w).float()
+    assert _rel(out, ref) <= TOL
+    assert len(ext.okc_attrs()) == 6
+    with pytest.raises(RuntimeError):
+        ext.okc_run(None, None, x[:1], lids[:1], wts[:1], out[:1], 1, nloc, 148)
