@@ -135,6 +135,18 @@ def cpu_oracle_run(spec, steps, sample_tokens=None, seed=0):
                       f"(numpy NVFP4 dequant + fp32 matmul), {tot:.2f} s"}, tot / len(times)
 
 
+def cpu_sample_tokens(spec):
+    """Tokens of the bounded CPU sample: the cost is the dequantisation of the touched experts, so
+    the sample is capped where it touches about 2.4e9 weights (64 tokens at H4096 I1536, 8 at
+    H7168 I2048 E256): some tens of seconds per step on the host cores."""
+    from muse_moe_w4a16 import inputs
+
+    s = inputs.SHAPES[spec["shape"]]
+    per_expert = 3 * s["I"] * s["H"]
+    cap = 64 if per_expert <= 20e6 else 8
+    return cap if spec["T"] > cap else None
+
+
 def run_reference(args, spec):
     """--impl reference: the reference has no CPU implementation of this op and its CUDA kernel is
     sm_90a-only, so the arm times the CPU restatement of the reference math (oracle/) on the host
@@ -142,7 +154,7 @@ def run_reference(args, spec):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    sample_tokens = 64 if spec["T"] > 64 else None
+    sample_tokens = cpu_sample_tokens(spec)
     steps = max(1, min(args.steps, 3))
     for _ in range(min(args.warmup, 1)):
         cpu_oracle_run(spec, 1, sample_tokens, seed=100)
@@ -312,8 +324,7 @@ def run_gpu(args, spec):
                 "kernel": "moe_gemm_kernel<N,0> (gate/up)", "peak_source": peaks["source"] + " (sustained)"}
     step_bytes = sum(inputs.algorithmic_bytes(H, I, E, k, T, touched[i % POOL]) for i in range(args.steps))
     step_flops = inputs.algorithmic_flops(H, I, R) * args.steps
-    sample_tokens = 64 if T > 64 else None
-    cpu_base, _ = cpu_oracle_run(spec, 2, sample_tokens)
+    cpu_base, _ = cpu_oracle_run(spec, 2, cpu_sample_tokens(spec))
 
     h2d = T * H * 2 + T * E * 4
     d2h = T * H * 2
