@@ -145,6 +145,19 @@ int msk_moe_forward_logits(const MskMoeCfg* cfg, const void* packed13, const voi
                            const float* bias, int32_t* topk_ids_out, float* topk_weights_out, void* out,
                            void* workspace, size_t workspace_bytes, int n_tokens, void* stream);
 
+/* The step with the pre-expert RMS norm of the layer callers fused in front: the expert input is
+ * bf16(x * rsqrt(mean(x^2) + pre_norm_eps) * (1 + pre_norm_w)), pre_norm_w bf16 [hidden], applied
+ * by the kernel that makes the F16 copy of the token rows (the reference's routing kernels do it
+ * before they store the expert input: muse_decode_layer/py/04_triton_kernels.py:556-568, eps 1e-5;
+ * muse_prefill_layer's gather takes g_pre_expert_norm, py/04_moe_forward.py:35). Routing is not
+ * affected: with `logits` (non-NULL) the routing runs here and topk_ids / topk_weights receive it;
+ * with logits == NULL they are inputs. hidden <= 8192. Not available with token_tile = 8. */
+int msk_moe_forward_prenorm(const MskMoeCfg* cfg, const void* packed13, const void* packed2, const float* gs13,
+                            const float* gs2, const void* post_norm_w, const void* pre_norm_w, float pre_norm_eps,
+                            const void* x, const float* logits, const float* bias, int32_t* topk_ids,
+                            float* topk_weights, void* out, void* workspace, size_t workspace_bytes, int n_tokens,
+                            void* stream);
+
 /* msk_moe_forward with a CUDA event before and after each of its four launches. Waits for the
  * last one and returns the elapsed milliseconds host_ms[4] = sort, gate/up GEMM, down GEMM,
  * combine. A measuring entry point: it synchronises and creates its events on first use; the

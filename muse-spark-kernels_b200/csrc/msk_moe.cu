@@ -102,10 +102,17 @@ __global__ void __launch_bounds__(128) dequant_packed_kernel(const uint8_t* pack
 // gather != 0: xs[q] = f16(x[perm[q] / top_k]) for q < off[nloc] (grid = T * top_k blocks);
 // gather == 0: xs[t] = f16(x[t]) (grid = T blocks), for the narrow token tiles that gather rows
 // through the permutation themselves.
+// With pre_w the pre-expert RMS norm of the layer callers is applied on the way:
+// x' = bf16( x * rsqrt(mean(x^2) + eps) * (1 + pre_w) ), FP32 arithmetic on the row the block holds in
+// registers (muse_decode_layer/py/04_triton_kernels.py:556-568: the reference's routing kernel does the
+// same before it stores the expert input). The sum of squares is a fixed shuffle tree followed by a
+// fixed-order sum of the eight warp partials.
 __global__ void __launch_bounds__(256) gather_rows_kernel(const __nv_bfloat16* __restrict__ x,
                                                           const int32_t* __restrict__ perm,
                                                           const int32_t* __restrict__ off, int nloc, int top_k, int H,
-                                                          int gather, __half* __restrict__ xs) {
+                                                          int gather, __half* __restrict__ xs,
+                                                          const __nv_bfloat16* __restrict__ pre_w, float pre_eps) {
+  __shared__ float wsum[8];
   pdl_wait();
   pdl_launch_dependents();
   const int q = blockIdx.x;
@@ -113,9 +120,53 @@ __global__ void __launch_bounds__(256) gather_rows_kernel(const __nv_bfloat16* _
   const size_t row = gather ? static_cast<size_t>(perm[q] / top_k) : static_cast<size_t>(q);
   const uint4* src = reinterpret_cast<const uint4*>(x + row * H);
   uint4* dst = reinterpret_cast<uint4*>(xs + static_cast<size_t>(q) * H);
-  for (int i = threadIdx.x; i < H / 8; i += 256) {
-    const uint4 v = src[i];
-    dst[i] = make_uint4(bf16x2_to_f16x2(v.x), bf16x2_to_f16x2(v.y), bf16x2_to_f16x2(v.z), bf16x2_to_f16x2(v.w));
+  if (pre_w == nullptr) {
+    for (int i = threadIdx.x; i < H / 8; i += 256) {
+      const uint4 v = src[i];
+      dst[i] = make_uint4(bf16x2_to_f16x2(v.x), bf16x2_to_f16x2(v.y), bf16x2_to_f16x2(v.z), bf16x2_to_f16x2(v.w));
+    }
+    return;
+  }
+  constexpr int MAXV = 4;   // 8 values per uint4, 256 threads: H <= 8192
+  uint4 v[MAXV];
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < MAXV; ++j) {
+    const int i = j * 256 + threadIdx.x;
+    v[j] = make_uint4(0u, 0u, 0u, 0u);
+    if (i < H / 8) v[j] = src[i];
+    const uint32_t w[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const float lo = __uint_as_float(w[c] << 16), hi = __uint_as_float(w[c] & 0xFFFF0000u);
+      ss += lo * lo + hi * hi;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if ((threadIdx.x & 31) == 0) wsum[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+#pragma unroll
+  for (int w8 = 0; w8 < 8; ++w8) tot += wsum[w8];
+  const float rs = rsqrtf(tot / static_cast<float>(H) + pre_eps);
+  const uint4* gsrc = reinterpret_cast<const uint4*>(pre_w);
+#pragma unroll
+  for (int j = 0; j < MAXV; ++j) {
+    const int i = j * 256 + threadIdx.x;
+    if (i >= H / 8) continue;
+    const uint4 gv = gsrc[i];
+    const uint32_t w[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
+    const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w};
+    uint32_t o4[4];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const float lo = __uint_as_float(w[c] << 16) * rs * (1.0f + __uint_as_float(gw[c] << 16));
+      const float hi = __uint_as_float(w[c] & 0xFFFF0000u) * rs * (1.0f + __uint_as_float(gw[c] & 0xFFFF0000u));
+      const __nv_bfloat162 b = __floats2bfloat162_rn(lo, hi);   // the expert input is BF16
+      o4[c] = bf16x2_to_f16x2(*reinterpret_cast<const uint32_t*>(&b));
+    }
+    dst[i] = make_uint4(o4[0], o4[1], o4[2], o4[3]);
   }
 }
 
@@ -837,7 +888,8 @@ static int forward_impl(const MskMoeCfg* cfg, const void* packed13, const void* 
                         const float* gs2, const void* post_norm_w, const void* x, const int32_t* topk_ids,
                         const float* topk_weights, void* out, void* workspace, size_t workspace_bytes, int n_tokens,
                         void* stream, cudaEvent_t* ev, const float* logits = nullptr, const float* bias = nullptr,
-                        int32_t* ids_out = nullptr, float* tw_out = nullptr) {
+                        int32_t* ids_out = nullptr, float* tw_out = nullptr, const void* pre_norm_w = nullptr,
+                        float pre_norm_eps = 1e-5f) {
   // with `logits` the routing runs here too: ids_out / tw_out receive it and feed the rest
   if (logits != nullptr) {
     if (!ids_out || !tw_out) return MSK_ERR_NULL;
@@ -871,7 +923,7 @@ static int forward_impl(const MskMoeCfg* cfg, const void* packed13, const void* 
 
   Plan plan = make_plan(cfg, n_tokens);
   if (plan.N == 8) {
-    if (cfg->stop_after != 0) return MSK_ERR_SHAPE;  // the stage hooks belong to the chain of launches
+    if (cfg->stop_after != 0 || pre_norm_w != nullptr) return MSK_ERR_SHAPE;  // the stage hooks and the pre-expert norm belong to the chain of launches  // the stage hooks belong to the chain of launches
     SmallParams sp{};
     sp.w13 = static_cast<const uint8_t*>(packed13); sp.w2 = static_cast<const uint8_t*>(packed2);
     sp.gs13 = gs13; sp.gs2 = gs2; sp.post_norm_w = static_cast<const __nv_bfloat16*>(post_norm_w);
@@ -936,7 +988,8 @@ static int forward_impl(const MskMoeCfg* cfg, const void* packed13, const void* 
   int e = 0;
   // narrow token tiles read an F16 copy of x; for few tokens the sorting CTA makes it
   const bool tma_b = plan.N >= 64;  // GemmCfg<N>::TMA_B
-  const bool convert_in_sort = !tma_b && n_tokens <= FUSED_ROUTE_MAX_TOKENS;
+  // (the pre-expert norm needs a block per row: it always goes through the row-copy kernel)
+  const bool convert_in_sort = !tma_b && n_tokens <= FUSED_ROUTE_MAX_TOKENS && pre_norm_w == nullptr;
   const __nv_bfloat16* xin = convert_in_sort ? static_cast<const __nv_bfloat16*>(x) : nullptr;
   __half* xh_in_sort = convert_in_sort ? xs : nullptr;
   if (logits != nullptr && n_tokens <= FUSED_ROUTE_MAX_TOKENS) {
@@ -983,7 +1036,8 @@ static int forward_impl(const MskMoeCfg* cfg, const void* packed13, const void* 
     e = static_cast<int>(cudaLaunchKernelEx(&lc, gather_rows_kernel, static_cast<const __nv_bfloat16*>(x),
                                             static_cast<const int32_t*>(perm), static_cast<const int32_t*>(off),
                                             static_cast<int>(cfg->local_count), static_cast<int>(cfg->top_k),
-                                            static_cast<int>(cfg->hidden), tma_b ? 1 : 0, xs));
+                                            static_cast<int>(cfg->hidden), tma_b ? 1 : 0, xs,
+                                            static_cast<const __nv_bfloat16*>(pre_norm_w), pre_norm_eps));
     if (e != 0) return e;
     p.act = xs;
     if (tma_b) {
@@ -1050,6 +1104,26 @@ int msk_moe_forward_logits(const MskMoeCfg* cfg, const void* packed13, const voi
   if (cfg != nullptr && cfg->top_k > cfg->n_experts) return MSK_ERR_SHAPE;
   return forward_impl(cfg, packed13, packed2, gs13, gs2, post_norm_w, x, nullptr, nullptr, out, workspace,
                       workspace_bytes, n_tokens, stream, nullptr, logits, bias, topk_ids_out, topk_weights_out);
+}
+
+int msk_moe_forward_prenorm(const MskMoeCfg* cfg, const void* packed13, const void* packed2, const float* gs13,
+                            const float* gs2, const void* post_norm_w, const void* pre_norm_w, float pre_norm_eps,
+                            const void* x, const float* logits, const float* bias, int32_t* topk_ids,
+                            float* topk_weights, void* out, void* workspace, size_t workspace_bytes, int n_tokens,
+                            void* stream) {
+  if (!pre_norm_w) return MSK_ERR_NULL;
+  if (!aligned16(pre_norm_w)) return MSK_ERR_ALIGN;
+  if (!(pre_norm_eps > 0.f)) return MSK_ERR_SHAPE;
+  if (cfg != nullptr && cfg->hidden > 8192) return MSK_ERR_TOO_LARGE;   // a row is held in registers by 256 threads
+  if (logits != nullptr) {
+    if (cfg != nullptr && cfg->top_k > cfg->n_experts) return MSK_ERR_SHAPE;
+    return forward_impl(cfg, packed13, packed2, gs13, gs2, post_norm_w, x, nullptr, nullptr, out, workspace,
+                        workspace_bytes, n_tokens, stream, nullptr, logits, bias, topk_ids, topk_weights, pre_norm_w,
+                        pre_norm_eps);
+  }
+  return forward_impl(cfg, packed13, packed2, gs13, gs2, post_norm_w, x, topk_ids, topk_weights, out, workspace,
+                      workspace_bytes, n_tokens, stream, nullptr, nullptr, nullptr, nullptr, nullptr, pre_norm_w,
+                      pre_norm_eps);
 }
 
 int msk_moe_forward_timed(const MskMoeCfg* cfg, const void* packed13, const void* packed2, const float* gs13,
@@ -1151,7 +1225,7 @@ int msk_moe_forward_static(const MskMoeCfg* cfg, const void* packed13, const voi
   int e = launch_sort(cfg, topk_ids, n_tokens, cnt, off, perm, inv, st);
   if (e != 0) return e;
   gather_rows_kernel<<<static_cast<unsigned>(n_tokens), 256, 0, st>>>(
-      static_cast<const __nv_bfloat16*>(x), perm, off, cfg->local_count, cfg->top_k, cfg->hidden, 0, xh);
+      static_cast<const __nv_bfloat16*>(x), perm, off, cfg->local_count, cfg->top_k, cfg->hidden, 0, xh, nullptr, 0.f);
   e = static_cast<int>(cudaGetLastError());
   if (e != 0) return e;
   GemmParams p{};

@@ -10,6 +10,7 @@ py/03_kernel_fn.py:18-45). Extensions, all optional:
   weights["route_bias"]   fp32 [E]      -> selection bias of the sigmoid routing mode
   data["router_logits"]   fp32 [T, E]   -> kernel_fn runs top-k itself (ids/weights not needed)
   post_norm_w may be absent             -> plain weighted combine, no post-expert RMS norm
+  pre_norm_w (bf16 [H]) may be present  -> the layer callers' pre-expert RMS norm is applied to x first
 There is no CPU path: tensors must be CUDA tensors and the native library must load.
 """
 import ctypes
@@ -36,7 +37,7 @@ def _stream():
 
 def prepare(weights, *, local_start=0, n_experts=None, top_k=8, max_tokens=8192, routing_mode="softmax_topk",
             route_scale=0.1767766952966369, post_norm_eps=1e-8, num_ctas=0, split_k13=0, split_k2=0, token_tile=0,
-            trace=0, stop_after=0):
+            trace=0, stop_after=0, pre_norm_eps=1e-5):
     """Repack the NVFP4 weights into the tile layout the GEMM kernel streams (bit and byte
     permutations only, never requantised) and allocate the workspace. Returns `state`."""
     w13 = _u8(weights["w13"])
@@ -69,6 +70,9 @@ def prepare(weights, *, local_start=0, n_experts=None, top_k=8, max_tokens=8192,
         _lib.check(lib.msk_moe_workspace_init(ctypes.byref(cfg), _lib.ptr(workspace), wsb.value, _stream()),
                    "msk_moe_workspace_init")
         torch.cuda.synchronize(dev)
+    prw = weights.get("pre_norm_w")
+    if prw is not None and (prw.dtype != torch.bfloat16 or prw.numel() != 2 * weights["w13"].shape[2]):
+        raise RuntimeError("muse_moe_w4a16.prepare: pre_norm_w must be bfloat16 [hidden]")
     pnw = weights.get("post_norm_w")
     if pnw is not None and pnw.dtype != torch.bfloat16:
         raise RuntimeError("muse_moe_w4a16.prepare: post_norm_w must stay bfloat16")
@@ -77,6 +81,8 @@ def prepare(weights, *, local_start=0, n_experts=None, top_k=8, max_tokens=8192,
         "packed13": packed13, "packed2": packed2,
         "gs13": weights["w13_gs"].contiguous(), "gs2": weights["w2_gs"].contiguous(),
         "post_norm_w": None if pnw is None else pnw.contiguous(),
+        "pre_norm_w": None if prw is None else prw.contiguous(),
+        "pre_norm_eps": float(pre_norm_eps),
         "router": None if weights.get("router") is None else weights["router"].float().contiguous(),
         "route_bias": None if weights.get("route_bias") is None else weights["route_bias"].float().contiguous(),
         "workspace": workspace, "workspace_bytes": wsb.value,
@@ -130,6 +136,22 @@ def kernel_fn(data, state, return_routing=False, out=None):
           or tuple(out.shape) != (T, cfg.hidden)):
         raise RuntimeError("muse_moe_w4a16.kernel_fn: out must be a contiguous CUDA bfloat16 [T, H] tensor")
     logits = _logits(data, state, x, T)
+    if state.get("pre_norm_w") is not None:
+        # the layer callers' pre-expert RMS norm, fused into the kernel that copies the token rows
+        if logits is None:
+            ids = data["topk_ids"].to(torch.int32).contiguous()
+            tw = data["topk_weights"].to(torch.float32).contiguous()
+        else:
+            ids = torch.empty((T, cfg.top_k), dtype=torch.int32, device=x.device)
+            tw = torch.empty((T, cfg.top_k), dtype=torch.float32, device=x.device)
+        _lib.check(lib.msk_moe_forward_prenorm(ctypes.byref(cfg), _lib.ptr(state["packed13"]), _lib.ptr(state["packed2"]),
+                                               _lib.ptr(state["gs13"]), _lib.ptr(state["gs2"]),
+                                               _lib.ptr(state["post_norm_w"]), _lib.ptr(state["pre_norm_w"]),
+                                               ctypes.c_float(state["pre_norm_eps"]), _lib.ptr(x), _lib.ptr(logits),
+                                               _lib.ptr(state["route_bias"]), _lib.ptr(ids), _lib.ptr(tw), _lib.ptr(out),
+                                               _lib.ptr(state["workspace"]), state["workspace_bytes"], T, _stream()),
+                   "msk_moe_forward_prenorm")
+        return (out, ids, tw) if return_routing else out
     if logits is None:
         ids = data["topk_ids"].to(torch.int32).contiguous()
         tw = data["topk_weights"].to(torch.float32).contiguous()

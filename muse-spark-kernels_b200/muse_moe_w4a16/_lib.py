@@ -69,6 +69,8 @@ SIGNATURES = {
     "msk_moe_workspace_bytes": [_CFG, _SZP],
     "msk_moe_workspace_init": [_CFG, _P, ctypes.c_size_t, _P],
     "msk_moe_forward": [_CFG, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, ctypes.c_size_t, ctypes.c_int, _P],
+    "msk_moe_forward_prenorm": [_CFG, _P, _P, _P, _P, _P, _P, ctypes.c_float, _P, _P, _P, _P, _P, _P, _P, ctypes.c_size_t,
+                                ctypes.c_int, _P],
     "msk_moe_forward_logits": [_CFG, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, ctypes.c_size_t, ctypes.c_int, _P],
     "msk_moe_forward_timed": [_CFG, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, ctypes.c_size_t, ctypes.c_int, _P,
                               ctypes.POINTER(ctypes.c_float)],

@@ -192,3 +192,26 @@ def test_module_refuses_cpu_tensors():
     w = inputs.make_weights(256, 256, 2, 0, "cpu")
     with pytest.raises(RuntimeError, match="CUDA"):
         moe.prepare(w)
+
+
+def test_oracle_pre_expert_norm_is_the_norm_in_front_of_the_step():
+    """pre_expert_norm follows muse_decode_layer/py/04_triton_kernels.py:556-568 (RMS over the row,
+    eps 1e-5, times 1 + g, one rounding to bf16), and moe_forward with weights["pre_norm_w"] equals
+    moe_forward on the normed rows."""
+    from muse_moe_w4a16 import inputs
+    from oracle import moe_oracle as orc
+
+    H, I, E, k, T = 256, 256, 4, 2, 5
+    w = inputs.make_weights(H, I, E, 3, "cpu", post_norm=True)
+    g = torch.Generator().manual_seed(2)
+    x = (torch.randn((T, H), generator=g) * 2.0).to(torch.bfloat16)
+    gw = (torch.randn((H,), generator=g) * 0.1).to(torch.bfloat16)
+    xn = orc.pre_expert_norm(x, gw)
+    xf = x.float()
+    want = xf / torch.sqrt((xf * xf).sum(-1, keepdim=True) / H + 1e-5) * (1.0 + gw.float())
+    assert xn.dtype == torch.bfloat16
+    assert float((xn.float() - want).abs().max()) <= 2.0 ** -8 * float(want.abs().max())
+    ids, tw = orc.route_topk(torch.randn((T, E), generator=g), k)
+    a = orc.moe_forward(x, ids, tw, dict(w, pre_norm_w=gw))
+    b = orc.moe_forward(xn, ids, tw, w)
+    assert torch.equal(a, b)

@@ -379,3 +379,29 @@ def test_okc_ext_runs_the_decode_layer_call_site(cuda_dev):
     assert len(ext.okc_attrs()) == 6
     with pytest.raises(RuntimeError):
         ext.okc_run(None, None, x[:1], lids[:1], wts[:1], out[:1], 1, nloc, 148)
+
+
+@pytest.mark.parametrize("T,given_ids", [(3, False), (40, True), (300, False), (600, True)])
+def test_forward_with_pre_expert_norm(cuda_dev, T, given_ids):
+    """weights["pre_norm_w"]: the layer callers' pre-expert RMS norm (eps 1e-5, x (1 + g)) fused into
+    the row-copy kernel, for every token-tile width; routing still sees the un-normed logits."""
+    m, inputs, _lib, orc = _mods()
+    H, I, E, k = 1024, 512, 8, 2
+    w = inputs.make_weights(H, I, E, 71, cuda_dev, post_norm=True)
+    g = torch.Generator(device=cuda_dev).manual_seed(12)
+    w["pre_norm_w"] = (torch.randn((H,), generator=g, device=cuda_dev) * 0.1).to(torch.bfloat16)
+    st = m.prepare(w, n_experts=E, top_k=k, max_tokens=T)
+    x = (torch.randn((T, H), generator=g, device=cuda_dev) * 3.0).to(torch.bfloat16)
+    logits = torch.randn((T, E), generator=g, device=cuda_dev)
+    out, ids, tw = m.kernel_fn({"hidden_states": x, "router_logits": logits}, st, return_routing=True)
+    if given_ids:
+        out = m.kernel_fn({"hidden_states": x, "topk_ids": ids, "topk_weights": tw}, st)
+    torch.cuda.synchronize()
+    assert m.read_status(st) == 0
+    rid, _ = orc.route_topk(logits.cpu(), k)
+    assert torch.equal(ids.cpu(), rid)
+    ref, parts = orc.moe_forward(x, ids, tw, w, return_parts=True)
+    _check_forward(out, ref, parts, m.workspace_views(st, T))
+    plain = dict(w)
+    del plain["pre_norm_w"]
+    assert _rel(out, orc.moe_forward(x, ids, tw, plain).float()) > 0.05   # the norm is not a no-op here
