@@ -766,7 +766,7 @@ int msk_moe_route(const MskMoeCfg* cfg, const float* logits, const float* bias, 
 
 static int launch_sort(const MskMoeCfg* cfg, const int32_t* ids, int n_tokens, int32_t* cnt, int32_t* off,
                        int32_t* perm, int32_t* inv, cudaStream_t st, const __nv_bfloat16* x = nullptr,
-                       __half* xh = nullptr, int32_t* blk = nullptr) {
+                       __half* xh = nullptr, int32_t* blk = nullptr, const void* pre_w = nullptr, float pre_eps = 0.f) {
   const int n_entries = n_tokens * cfg->top_k;
   if (blk != nullptr && xh == nullptr && n_entries >= SORT_MULTI_MIN) {
     // many entries: the same stable sort on several CTAs (count, scan, scatter)
@@ -799,14 +799,15 @@ static int launch_sort(const MskMoeCfg* cfg, const int32_t* ids, int n_tokens, i
   lc.numAttrs = 1;
   return static_cast<int>(cudaLaunchKernelEx(&lc, sort_kernel, ids, static_cast<int>(n_tokens * cfg->top_k),
                                              static_cast<int>(cfg->local_start), static_cast<int>(cfg->local_count),
-                                             cnt, off, perm, inv, x, xh, n_tokens, static_cast<int>(cfg->hidden)));
+                                             cnt, off, perm, inv, x, xh, n_tokens, static_cast<int>(cfg->hidden),
+                                             static_cast<const __nv_bfloat16*>(pre_w), pre_eps));
 }
 
 constexpr int FUSED_ROUTE_MAX_TOKENS = 32;  // up to here one CTA routes and sorts in a single launch
 
 static int launch_route_sort(const MskMoeCfg* cfg, const float* logits, const float* bias, int32_t* ids, float* tw,
                              int n_tokens, int32_t* cnt, int32_t* off, int32_t* perm, int32_t* inv, cudaStream_t st,
-                             const __nv_bfloat16* x, __half* xh) {
+                             const __nv_bfloat16* x, __half* xh, const void* pre_w = nullptr, float pre_eps = 0.f) {
   static bool attr_set[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -830,7 +831,8 @@ static int launch_route_sort(const MskMoeCfg* cfg, const float* logits, const fl
                                              static_cast<int>(cfg->n_experts), static_cast<int>(cfg->top_k),
                                              static_cast<int>(cfg->routing_mode), cfg->route_scale,
                                              static_cast<int>(cfg->local_start), static_cast<int>(cfg->local_count),
-                                             cnt, off, perm, inv, x, xh, static_cast<int>(cfg->hidden)));
+                                             cnt, off, perm, inv, x, xh, static_cast<int>(cfg->hidden),
+                                             static_cast<const __nv_bfloat16*>(pre_w), pre_eps));
 }
 
 int msk_moe_sort(const MskMoeCfg* cfg, const int32_t* topk_ids, int n_tokens, int32_t* cnt, int32_t* off,
@@ -988,12 +990,12 @@ static int forward_impl(const MskMoeCfg* cfg, const void* packed13, const void* 
   int e = 0;
   // narrow token tiles read an F16 copy of x; for few tokens the sorting CTA makes it
   const bool tma_b = plan.N >= 64;  // GemmCfg<N>::TMA_B
-  // (the pre-expert norm needs a block per row: it always goes through the row-copy kernel)
-  const bool convert_in_sort = !tma_b && n_tokens <= FUSED_ROUTE_MAX_TOKENS && pre_norm_w == nullptr;
+  const bool convert_in_sort = !tma_b && n_tokens <= FUSED_ROUTE_MAX_TOKENS;
   const __nv_bfloat16* xin = convert_in_sort ? static_cast<const __nv_bfloat16*>(x) : nullptr;
   __half* xh_in_sort = convert_in_sort ? xs : nullptr;
   if (logits != nullptr && n_tokens <= FUSED_ROUTE_MAX_TOKENS) {
-    e = launch_route_sort(cfg, logits, bias, ids_out, tw_out, n_tokens, cnt, off, perm, inv, st, xin, xh_in_sort);
+    e = launch_route_sort(cfg, logits, bias, ids_out, tw_out, n_tokens, cnt, off, perm, inv, st, xin, xh_in_sort,
+                          pre_norm_w, pre_norm_eps);
   } else {
     if (logits != nullptr) {
       route_topk_kernel<<<static_cast<unsigned>((n_tokens + 7) / 8), 256, 0, st>>>(
@@ -1002,7 +1004,7 @@ static int forward_impl(const MskMoeCfg* cfg, const void* packed13, const void* 
       if (e != 0) return e;
     }
     e = launch_sort(cfg, topk_ids, n_tokens, cnt, off, perm, inv, st, xin, xh_in_sort,
-                    reinterpret_cast<int32_t*>(b + k.sort_blk));
+                    reinterpret_cast<int32_t*>(b + k.sort_blk), pre_norm_w, pre_norm_eps);
   }
   if (e != 0) return e;
   if (ev) cudaEventRecord(ev[1], st);

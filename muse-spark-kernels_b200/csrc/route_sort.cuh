@@ -226,8 +226,45 @@ __device__ void sort_entries_block(SortSmem& sm, const int32_t* ids, int n, int 
 // F16 copy of the token rows by the sorting CTA (small token counts only: saves a launch in the
 // decode chain). xh may be null.
 __device__ __forceinline__ void convert_rows_block(const __nv_bfloat16* __restrict__ x, __half* __restrict__ xh,
-                                                   int T, int H) {
+                                                   int T, int H, const __nv_bfloat16* __restrict__ pre_w, float pre_eps) {
   if (xh == nullptr) return;
+  if (pre_w != nullptr) {
+    // with the pre-expert RMS norm (x * rsqrt(mean(x^2) + eps) * (1 + pre_w), one BF16 rounding): a warp
+    // per row, the sum of squares by a fixed shuffle tree, the row read a second time from L1/L2
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint4* g = reinterpret_cast<const uint4*>(pre_w);
+    for (int t = warp; t < T; t += SORT_WARPS) {
+      const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<size_t>(t) * H);
+      uint4* dst = reinterpret_cast<uint4*>(xh + static_cast<size_t>(t) * H);
+      float ss = 0.f;
+      for (int i = lane; i < H / 8; i += 32) {
+        const uint4 v = src[i];
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const float lo = __uint_as_float(w[c] << 16), hi = __uint_as_float(w[c] & 0xFFFF0000u);
+          ss += lo * lo + hi * hi;
+        }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      const float rs = rsqrtf(ss / static_cast<float>(H) + pre_eps);
+      for (int i = lane; i < H / 8; i += 32) {
+        const uint4 v = src[i], gv = g[i];
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w}, gw[4] = {gv.x, gv.y, gv.z, gv.w};
+        uint32_t o4[4];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const float lo = __uint_as_float(w[c] << 16) * rs * (1.0f + __uint_as_float(gw[c] << 16));
+          const float hi = __uint_as_float(w[c] & 0xFFFF0000u) * rs * (1.0f + __uint_as_float(gw[c] & 0xFFFF0000u));
+          const __nv_bfloat162 b = __floats2bfloat162_rn(lo, hi);
+          o4[c] = bf16x2_to_f16x2(*reinterpret_cast<const uint32_t*>(&b));
+        }
+        dst[i] = make_uint4(o4[0], o4[1], o4[2], o4[3]);
+      }
+    }
+    return;
+  }
   const uint4* src = reinterpret_cast<const uint4*>(x);
   uint4* dst = reinterpret_cast<uint4*>(xh);
   const int n = T * (H / 8);
@@ -241,12 +278,13 @@ __global__ void __launch_bounds__(SORT_THREADS) sort_kernel(const int32_t* __res
                                                             int32_t* __restrict__ cnt, int32_t* __restrict__ off,
                                                             int32_t* __restrict__ perm, int32_t* __restrict__ inv,
                                                             const __nv_bfloat16* __restrict__ x,
-                                                            __half* __restrict__ xh, int T, int H) {
+                                                            __half* __restrict__ xh, int T, int H,
+                                                            const __nv_bfloat16* __restrict__ pre_w, float pre_eps) {
   extern __shared__ __align__(16) unsigned char sort_smem_raw[];
   SortSmem& sm = *reinterpret_cast<SortSmem*>(sort_smem_raw);
   asm volatile("griddepcontrol.wait;" ::: "memory");               // topk_ids may come from the kernel before
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");  // let the GEMM kernel set itself up meanwhile
-  convert_rows_block(x, xh, T, H);
+  convert_rows_block(x, xh, T, H, pre_w, pre_eps);
   sort_entries_block(sm, ids, n, lo, nloc, cnt, off, perm, inv);
 }
 
@@ -377,12 +415,14 @@ __global__ void __launch_bounds__(SORT_THREADS) route_sort_kernel(const float* _
                                                                   int32_t* __restrict__ off, int32_t* __restrict__ perm,
                                                                   int32_t* __restrict__ inv,
                                                                   const __nv_bfloat16* __restrict__ x,
-                                                                  __half* __restrict__ xh, int H) {
+                                                                  __half* __restrict__ xh, int H,
+                                                                  const __nv_bfloat16* __restrict__ pre_w,
+                                                                  float pre_eps) {
   extern __shared__ __align__(16) unsigned char sort_smem_raw[];
   SortSmem& sm = *reinterpret_cast<SortSmem*>(sort_smem_raw);
   asm volatile("griddepcontrol.wait;" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  convert_rows_block(x, xh, T, H);
+  convert_rows_block(x, xh, T, H, pre_w, pre_eps);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   for (int t = warp; t < T; t += SORT_WARPS)
     route_token_dispatch(logits + static_cast<size_t>(t) * E, bias, ids + static_cast<size_t>(t) * k,

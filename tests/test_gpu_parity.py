@@ -381,7 +381,7 @@ def test_okc_ext_runs_the_decode_layer_call_site(cuda_dev):
         ext.okc_run(None, None, x[:1], lids[:1], wts[:1], out[:1], 1, nloc, 148)
 
 
-@pytest.mark.parametrize("T,given_ids", [(3, False), (40, True), (300, False), (600, True)])
+@pytest.mark.parametrize("T,given_ids", [(3, False), (7, True), (40, True), (300, False), (600, True)])
 def test_forward_with_pre_expert_norm(cuda_dev, T, given_ids):
     """weights["pre_norm_w"]: the layer callers' pre-expert RMS norm (eps 1e-5, x (1 + g)) fused into
     the row-copy kernel, for every token-tile width; routing still sees the un-normed logits."""
