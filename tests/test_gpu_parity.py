@@ -405,3 +405,53 @@ def test_forward_with_pre_expert_norm(cuda_dev, T, given_ids):
     plain = dict(w)
     del plain["pre_norm_w"]
     assert _rel(out, orc.moe_forward(x, ids, tw, plain).float()) > 0.05   # the norm is not a no-op here
+
+
+@pytest.mark.parametrize("T", [64, 8192])
+def test_full_size_properties(cuda_dev, T):
+    """Benchmark-size shapes (H4096 I1536 E128 top-8; T = 64 decode sweep point, T = 8192 prefill),
+    where the CPU oracle would take minutes: properties that hold whatever the size.
+    (1) A token's output does not depend on where the token sits: permuting the tokens permutes
+    the output rows, bit for bit. (2) Halving the top-k weights halves the output exactly.
+    (3) Tokens whose ids are all -1 come out zero. (4) A 64-token sample of the same call matches
+    the oracle."""
+    m, inputs, _lib, orc = _mods()
+    s = inputs.SHAPES["decode"]
+    H, I, E, k = s["H"], s["I"], s["E"], s["k"]
+    w = inputs.make_weights_random_bytes(H, I, E, 5, cuda_dev)
+    st = m.prepare(w, n_experts=E, top_k=k, max_tokens=T)
+    data, _ = inputs.make_inputs("prefill" if T > 256 else "decode", T, 3, cuda_dev)
+    x, logits = data["hidden_states"], data["router_logits"]
+    out, ids, tw = m.kernel_fn({"hidden_states": x, "router_logits": logits}, st, return_routing=True)
+    out = out.clone()
+    g = torch.Generator(device=cuda_dev).manual_seed(1)
+    p = torch.randperm(T, generator=g, device=cuda_dev)
+    out_p = m.kernel_fn({"hidden_states": x[p].contiguous(), "router_logits": logits[p].contiguous()}, st)
+    assert torch.equal(out_p, out[p])
+    half = m.kernel_fn({"hidden_states": x, "topk_ids": ids, "topk_weights": tw * 0.5}, st)
+    assert torch.equal(half.float() * 2.0, out.float())
+    ids2 = ids.clone()
+    ids2[::7] = -1
+    z = m.kernel_fn({"hidden_states": x, "topk_ids": ids2, "topk_weights": tw}, st)
+    assert float(z[::7].float().abs().max()) == 0.0
+    keep = torch.ones(T, dtype=torch.bool, device=cuda_dev)
+    keep[::7] = False
+    assert torch.equal(z[keep], out[keep])
+    torch.cuda.synchronize()
+    assert m.read_status(st) == 0
+    # a sample against the oracle: 64 tokens, their experts only (dense local table over the touched ones)
+    sel = torch.arange(0, T, max(T // 64, 1), device=cuda_dev)[:64]
+    touched = sorted(set(ids[sel].flatten().tolist()))[:24]
+    remap = {e: j for j, e in enumerate(touched)}
+    lids = torch.tensor([[remap.get(int(v), -1) for v in row] for row in ids[sel].tolist()], dtype=torch.int32)
+    def take(t):   # fp8 tensors are indexed through their bytes
+        if t.dtype == torch.float8_e4m3fn:
+            return t.view(torch.uint8)[touched].view(torch.float8_e4m3fn).cpu()
+        return t[touched].cpu()
+
+    sub = {key: take(w[key]) for key in ("w13", "w13_sf", "w13_gs", "w2", "w2_sf", "w2_gs")}
+    ref = orc.moe_forward(x[sel].cpu(), lids, tw[sel].cpu(), sub).float()
+    part = m.prepare({key: v.to(cuda_dev) for key, v in sub.items()}, n_experts=len(touched), top_k=k, max_tokens=64)
+    got = m.kernel_fn({"hidden_states": x[sel].contiguous(), "topk_ids": lids.to(cuda_dev), "topk_weights": tw[sel].contiguous()},
+                      part)
+    assert _rel(got, ref) <= TOL
