@@ -215,3 +215,63 @@ def test_oracle_pre_expert_norm_is_the_norm_in_front_of_the_step():
     a = orc.moe_forward(x, ids, tw, dict(w, pre_norm_w=gw))
     b = orc.moe_forward(xn, ids, tw, w)
     assert torch.equal(a, b)
+
+
+# ------------------------------- vectors produced by the reference's Triton kernels on a CPU
+def _bf16(a):
+    return torch.from_numpy(a.astype(np.int16)).view(torch.bfloat16)
+
+
+def test_routing_matches_reference_route_split():
+    """ids, local ids and weights of the reference's `_route_split` (sigmoid(logit / sqrt(32)) + bias,
+    eight rounds of arg-max, ties to the lowest index), on logits that hold exact ties."""
+    logits, bias = torch.from_numpy(GOLD["rs_logits"]), torch.from_numpy(GOLD["rs_bias"])
+    ids, w = orc.route_topk(logits, 8, "sigmoid_bias", bias)
+    assert np.array_equal(ids.numpy(), GOLD["rs_ids"])
+    assert np.allclose(w.numpy(), GOLD["rs_w"], rtol=2e-6, atol=1e-8)
+    # the constructed ties are there and went to the lower index
+    assert list(GOLD["rs_ids"][1]) == sorted(GOLD["rs_ids"][1].tolist(), key=lambda e: (-float(bias[e]), e))
+    assert not np.isin(GOLD["rs_ids"], np.arange(200, 208)).any() or np.isin(GOLD["rs_ids"], np.arange(8, 16)).any()
+    ls = int(GOLD["rs_local_start"][0])
+    assert np.array_equal(orc.local_ids(ids, ls, 32).numpy(), GOLD["rs_lids"])
+    # the stable sort drops exactly the entries the reference marks -1
+    cnt, off, perm, inv = orc.sort_routes(GOLD["rs_ids"], ls, 32)
+    assert np.array_equal(inv >= 0, GOLD["rs_lids"].reshape(-1) >= 0)
+    assert np.array_equal(GOLD["rs_lids"].reshape(-1)[perm], np.sort(GOLD["rs_lids"].reshape(-1)[perm], kind="stable"))
+
+
+def _trunc_bf16(f):
+    """FP32 -> BF16 by dropping the low 16 bits: how Triton's CPU interpreter converts (compiled for
+    a GPU the same kernels round to nearest even, as the oracle and the CUDA path do). The golden
+    BF16 outputs are therefore compared with the truncated FP32 values of the oracle, which pins the
+    FP32 arithmetic in front of the rounding."""
+    return (f.contiguous().view(torch.int32) & -65536).view(torch.float32)
+
+
+def test_pre_expert_norm_matches_reference_route_split():
+    """The expert input the reference's routing kernel stores: x * rsqrt(sum(x^2)/H + 1e-5) * (1 + g)."""
+    f = orc.pre_expert_norm(_bf16(GOLD["rs_pooled"]), _bf16(GOLD["rs_gpre"]), return_fp32=True)
+    want = _bf16(GOLD["rs_x"]).float()
+    same = _trunc_bf16(f) == want
+    # a row's sum of 4096 squares is taken in another order by the two programs: allow the last FP32 bit
+    # of the scale to move a value across a BF16 boundary on a handful of elements
+    assert float(same.float().mean()) > 0.999
+    assert bool(((f - want).abs() <= 2.0 ** -7 * want.abs() + 1e-30).all())
+    rn = orc.pre_expert_norm(_bf16(GOLD["rs_pooled"]), _bf16(GOLD["rs_gpre"]))
+    assert rn.dtype == torch.bfloat16 and bool(((rn.float() - f).abs() <= 2.0 ** -8 * f.abs()).all())
+
+
+def test_combine_matches_reference_pexp_norm_sum():
+    """Post-expert norm (1 + w first, RMS over the row, eps 1e-8) times the routing weight, summed in
+    slot order over the slots with a local expert; a token without one is zero."""
+    y = _bf16(GOLD["pn_y"]).float()
+    pw = _bf16(GOLD["pn_w"]).float()
+    s, lid = torch.from_numpy(GOLD["pn_s"]), torch.from_numpy(GOLD["pn_ids"])
+    T, K = lid.shape
+    inv = torch.where(lid >= 0, torch.arange(T * K, dtype=torch.int32).view(T, K), torch.full_like(lid, -1))
+    out = orc.combine_rows(y * (1.0 + pw), inv, s, True, 1e-8)
+    want = _bf16(GOLD["pn_out"]).float()
+    assert float(want[2].abs().max()) == 0.0 and float(out[2].abs().max()) == 0.0
+    same = _trunc_bf16(out) == want
+    assert float(same.float().mean()) > 0.995          # the rest straddle a BF16 boundary in their last FP32 bits
+    assert float((out - want).abs().max()) <= 2.0 ** -7 * float(want.abs().max())
