@@ -180,6 +180,12 @@ int msk_moe_forward_static(const MskMoeCfg* cfg, const void* packed13, const voi
                            const float* gs2, const void* post_norm_w, const void* x, const int32_t* topk_ids,
                            const float* topk_weights, void* out, int n_tokens, void* stream);
 
+/* Status word of msk_moe_forward_static's array on the current device, copied to *host_status after
+ * synchronising `stream`: 0 = no device-side wait of the last static call gave up. The caller of
+ * the static entry point holds no workspace pointer, so msk_moe_read_status cannot serve it.
+ * Allocates nothing; not for the timed path. No counterpart in the reference. */
+int msk_moe_static_status(int* host_status, void* stream);
+
 /* The launch plan msk_moe_forward uses for n_tokens: host_out[4] = token tile N, K splits of the
  * gate/up GEMM, K splits of the down GEMM, persistent grid size. The reference picks its build by
  * token count the same way (muse_moe_w4a16/py/03_kernel_fn.py:33-40). */
@@ -217,6 +223,10 @@ int msk_ep_combine(const void* back, const void* self_rows, int self_rank, const
  * peer is certain to issue, and run under a host-side time-out. No counterpart in the reference. */
 int msk_ep_flag_write(void* addr, uint32_t value, void* stream);
 int msk_ep_flag_wait(void* addr, uint32_t value, void* stream);
+
+/* Hash of the source files this library was built from (set by the build script); the Python
+ * binding compares it with the sources beside it and refuses a stale binary. */
+const char* msk_build_id(void);
 
 /* HBM streaming probe: every CTA pulls its share of `bytes` from `src` through a ring of
  * bulk async copies, as the GEMM kernel's weight producer does, and adds a checksum to

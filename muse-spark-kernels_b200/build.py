@@ -2,6 +2,8 @@
 
 usage: python muse-spark-kernels_b200/build.py [--force] [--verbose]
 """
+import ctypes
+import hashlib
 import os
 import shutil
 import subprocess
@@ -23,19 +25,38 @@ def _nvcc():
     return shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
 
 
+def source_id():
+    """Hash of every source and header the library is built from; compiled into the library
+    (msk_build_id) so that a stale binary can be told from the sources beside it."""
+    h = hashlib.sha256()
+    for f in sorted(SOURCES + HEADERS):
+        with open(os.path.join(CSRC, f), "rb") as fh:
+            h.update(f.encode() + b"\0" + fh.read() + b"\0")
+    return h.hexdigest()[:16]
+
+
+def built_id(path=OUT):
+    """msk_build_id() of a built library, or None when there is none / it cannot be loaded."""
+    if not os.path.exists(path):
+        return None
+    try:
+        lib = ctypes.CDLL(path)
+        fn = lib.msk_build_id
+        fn.restype = ctypes.c_char_p
+        return fn().decode()
+    except (OSError, AttributeError):
+        return None
+
+
 def _stale():
-    if not os.path.exists(OUT):
-        return True
-    t = os.path.getmtime(OUT)
-    deps = [os.path.join(CSRC, f) for f in SOURCES + HEADERS]
-    return any(os.path.getmtime(d) > t for d in deps)
+    return built_id() != source_id()
 
 
 def build_library(force=False, verbose=False):
     """Compile csrc/msk_moe.cu -> muse_moe_w4a16/libmsk_moe.so. Returns the .so path."""
     if not force and not _stale():
         return OUT
-    cmd = [_nvcc()] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-o", OUT] + [
+    cmd = [_nvcc()] + NVCC_FLAGS + [f'-DMSK_BUILD_ID="{source_id()}"'] + (["-Xptxas", "-v"] if verbose else []) + ["-o", OUT] + [
         os.path.join(CSRC, s) for s in SOURCES
     ]
     res = subprocess.run(cmd, capture_output=True, text=True)

@@ -1178,6 +1178,33 @@ constexpr size_t MSK_STATIC_WS_BYTES = 8u << 20;
 constexpr int MSK_STATIC_MAX_ROWS = 128;
 static __device__ __align__(256) unsigned char g_static_ws[MSK_STATIC_WS_BYTES];
 
+// Device address of the array on the current device, looked up once per device (in host code the
+// symbol's name is a host-side stand-in, not a device address).
+static int static_ws_base(unsigned char** out) {
+  static unsigned char* base_of[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return MSK_ERR_RANGE;
+  if (base_of[dev] == nullptr) {
+    void* ptr = nullptr;
+    const cudaError_t ce = cudaGetSymbolAddress(&ptr, g_static_ws);
+    if (ce != cudaSuccess) return static_cast<int>(ce);
+    base_of[dev] = static_cast<unsigned char*>(ptr);
+  }
+  *out = base_of[dev];
+  return 0;
+}
+
+int msk_moe_static_status(int* host_status, void* stream) {
+  if (!host_status) return MSK_ERR_NULL;
+  unsigned char* b = nullptr;
+  const int ar = static_ws_base(&b);
+  if (ar != 0) return ar;
+  cudaError_t e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return static_cast<int>(e);
+  e = cudaMemcpy(host_status, b, sizeof(int), cudaMemcpyDeviceToHost);
+  return static_cast<int>(e);
+}
+
 int msk_moe_forward_static(const MskMoeCfg* cfg, const void* packed13, const void* packed2, const float* gs13,
                            const float* gs2, const void* post_norm_w, const void* x, const int32_t* topk_ids,
                            const float* topk_weights, void* out, int n_tokens, void* stream) {
@@ -1190,7 +1217,7 @@ int msk_moe_forward_static(const MskMoeCfg* cfg, const void* packed13, const voi
   if (!aligned16(packed13) || !aligned16(packed2) || !aligned16(x) || !aligned16(out)) return MSK_ERR_ALIGN;
   const size_t R = static_cast<size_t>(n_tokens) * cfg->top_k;
   if (R > static_cast<size_t>(MSK_STATIC_MAX_ROWS) || cfg->hidden > 8192 || cfg->inter > 4096) return MSK_ERR_TOO_LARGE;
-  // carve: [status 256][cnt][off][perm][inv][inter bf16 R x I][y fp32 R x H]
+  // carve: [status 256][cnt][off][perm][inv][inter f16 R x I][y fp32 R x H][x as f16 T x H]
   size_t o = 256;
   const size_t o_cnt = o; o += round_up(static_cast<size_t>(cfg->local_count) * 4, 256);
   const size_t o_off = o; o += round_up(static_cast<size_t>(cfg->local_count + 1) * 4, 256);
@@ -1201,17 +1228,9 @@ int msk_moe_forward_static(const MskMoeCfg* cfg, const void* packed13, const voi
   const size_t o_xh = o; o += round_up(static_cast<size_t>(n_tokens) * cfg->hidden * 2, 256);
   if (o > MSK_STATIC_WS_BYTES) return MSK_ERR_TOO_LARGE;
 
-  // device address of the array, once per device (the symbol's host-side name is not an address)
-  static unsigned char* base_of[64] = {nullptr};
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return MSK_ERR_RANGE;
-  if (base_of[dev] == nullptr) {
-    void* ptr = nullptr;
-    const cudaError_t ce = cudaGetSymbolAddress(&ptr, g_static_ws);
-    if (ce != cudaSuccess) return static_cast<int>(ce);
-    base_of[dev] = static_cast<unsigned char*>(ptr);
-  }
-  unsigned char* b = base_of[dev];
+  unsigned char* b = nullptr;
+  const int ar = static_ws_base(&b);
+  if (ar != 0) return ar;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   cudaError_t ce = cudaMemsetAsync(b, 0, 256, st);  // status word starts at zero
   if (ce != cudaSuccess) return static_cast<int>(ce);
@@ -1249,6 +1268,11 @@ int msk_moe_forward_static(const MskMoeCfg* cfg, const void* packed13, const voi
       cfg->post_norm_eps);
   return static_cast<int>(cudaGetLastError());
 }
+
+#ifndef MSK_BUILD_ID
+#define MSK_BUILD_ID "unknown"
+#endif
+const char* msk_build_id(void) { return MSK_BUILD_ID; }
 
 int msk_moe_plan(const MskMoeCfg* cfg, int n_tokens, int* host_out) {
   const int rc = check_cfg(cfg);

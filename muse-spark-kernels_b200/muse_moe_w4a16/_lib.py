@@ -75,6 +75,7 @@ SIGNATURES = {
     "msk_moe_forward_timed": [_CFG, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, ctypes.c_size_t, ctypes.c_int, _P,
                               ctypes.POINTER(ctypes.c_float)],
     "msk_moe_forward_static": [_CFG, _P, _P, _P, _P, _P, _P, _P, _P, _P, ctypes.c_int, _P],
+    "msk_moe_static_status": [_INTP, _P],
     "msk_moe_plan": [_CFG, ctypes.c_int, _INTP],
     "msk_moe_workspace_view": [_CFG, _P, ctypes.c_int, ctypes.POINTER(_P)],
     "msk_moe_read_status": [_P, _INTP, _P],
@@ -89,19 +90,29 @@ _lock = threading.Lock()
 _lib = None
 
 
+def _build_module():
+    import importlib.util
+
+    spec = importlib.util.spec_from_file_location("_msk_build", os.path.join(os.path.dirname(_HERE), "build.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
 def load():
-    """Load libmsk_moe.so once per process (building it with nvcc if it is absent)."""
+    """Load libmsk_moe.so once per process. The library carries a hash of the sources it was built
+    from (msk_build_id); when it differs from the sources beside it (or the library is absent) the
+    library is rebuilt with nvcc first, and if that is impossible the load fails: tests and
+    benchmarks never run a binary that is older than the source tree."""
     global _lib
     with _lock:
         if _lib is not None:
             return _lib
-        if not os.path.exists(LIB_PATH):
-            import importlib.util
-
-            spec = importlib.util.spec_from_file_location("_msk_build", os.path.join(os.path.dirname(_HERE), "build.py"))
-            mod = importlib.util.module_from_spec(spec)
-            spec.loader.exec_module(mod)
-            mod.build_library()
+        default_path = "MSK_MOE_LIB" not in os.environ
+        if default_path:
+            bm = _build_module()
+            if bm.built_id(LIB_PATH) != bm.source_id():
+                bm.build_library()      # raises when nvcc is missing or fails
         try:
             lib = ctypes.CDLL(LIB_PATH)
         except OSError as exc:  # no CPU fallback by design
@@ -110,8 +121,15 @@ def load():
             fn = getattr(lib, name)
             fn.argtypes = argtypes
             fn.restype = ctypes.c_int
+        lib.msk_build_id.restype = ctypes.c_char_p
+        lib.msk_build_id.argtypes = []
         _lib = lib
         return lib
+
+
+def build_id():
+    """Hash of the sources the loaded library was built from."""
+    return load().msk_build_id().decode()
 
 
 def check(status, what):

@@ -3,8 +3,9 @@
 A host that has given all device memory to its own pool, or that calls this library while its
 allocator is locked or from a thread that must not enter the driver's allocator, cannot provide the workspace
 msk_moe_forward asks for. The static variant keeps that scratch in a device array inside the
-library. This test calls it through the C ABI and compares it with msk_moe_forward on the same
-inputs, twice in a row (the second call finds the array as the first one left it).
+library. This test calls it through the C ABI and compares it with msk_moe_forward and with the
+CPU oracle on the same inputs, twice in a row (the second call finds the array as the first one
+left it), and reads the array's own status word back through msk_moe_static_status.
 
 Collected last on purpose (file name), so a failure here cannot hide any other test.
 """
@@ -25,6 +26,7 @@ def _stream():
 def test_forward_static_matches_forward_twice(cuda_dev):
     import muse_moe_w4a16 as moe
     from muse_moe_w4a16 import _lib, inputs
+    from oracle import moe_oracle as orc
 
     lib = _lib.load()
     H, I, E, k = 1024, 512, 16, 4
@@ -45,6 +47,12 @@ def test_forward_static_matches_forward_twice(cuda_dev):
         assert torch.isfinite(got.float()).all()
         err = float((got.float() - want.float()).abs().max() / want.float().abs().max())
         assert err <= TOL, (call, err)
+        ref = orc.moe_forward(x, ids, tw, w).float()
+        err_o = float((got.float().cpu() - ref).abs().max() / ref.abs().max())
+        assert err_o <= TOL, (call, err_o)
+        status = ctypes.c_int(-1)
+        assert lib.msk_moe_static_status(ctypes.byref(status), _stream()) == 0
+        assert status.value == 0          # no bounded wait of the static call gave up
     assert moe.read_status(st) == 0
 
 
