@@ -1,14 +1,22 @@
 """Benchmark of the routed-expert step (muse_moe_w4a16) on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload decode|sweepT<n>|prefill|ep]
-                    [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload auto|decode|sweepT<n>|prefill|ep]
+                    [--no-sweep] [--impl reference]
 
 One JSON line on stdout. A step is one routed-expert pass (top-k routing, sort, gate/up GEMM +
-SwiGLU, down GEMM, combine) over one batch of seeded synthetic input. Default workload at one
-GPU: the T=1 decode configuration (H=4096, I=1536, E=128, top-8, uniform router logits).
+SwiGLU, down GEMM, combine) over one batch of seeded synthetic input.
+  N = 1    headline workload: the T = 1 decode configuration (H4096 I1536 E128 top-8, uniform router
+           logits); the line also carries `sweep`: the other points of the metric (T = 8 .. 256 with
+           N(0,1) logits, and the T = 8192 Zipf-routed prefill), measured the same way on the same
+           prepared weights with fewer steps each.
+  N > 1    the expert-parallel configuration (H7168 I2048 E256 top-8, T = 4096 per GPU). Before the
+           timing rank 0 also runs the same shape with all 256 experts on its one GPU: every rank checks
+           its expert-parallel output against that (`ep_parity_max_rel`), and the line carries
+           `single_gpu_same_shape_ms` and `scaling_efficiency` = that / the N-GPU step.
   value      tokens/s, device-timed (CUDA events around CUDA-graph replays), inputs resident in HBM
-  e2e        tokens/s through kernel_fn with pinned host inputs: H2D copies, launches, D2H of `out`
-  roofline   dominant kernel (gate/up GEMM): algorithmic bytes or flops / its mean event-timed duration
+  e2e        tokens/s through the module's graphed step with pinned host inputs: H2D copy, launch,
+             D2H of `out`; event-timed, with the host wall-clock time per step beside it
+  roofline   dominant kernel: algorithmic bytes or flops / its mean event-timed duration
   cpu_baseline  the CPU oracle (PyTorch eager on the host cores) on a bounded sample of the same inputs
 L2 is flushed (a 256 MiB write) before every timed step, outside the timed interval, and the
 steps cycle through a pool of different routings.
@@ -27,7 +35,10 @@ sys.path[:0] = [ROOT, os.path.join(ROOT, "muse-spark-kernels_b200")]
 
 METRIC = "routed_expert_tokens_per_s"
 UNIT = "tokens/s"
+DTYPE = "bf16 x nvfp4 -> fp32 acc"
 POOL = 8  # distinct seeded inputs cycled through
+SWEEP = ("sweepT8", "sweepT32", "sweepT64", "sweepT128", "sweepT256", "prefill")
+NCU_TRAFFIC_RATIO = 1.015   # ncu: DRAM bytes read + written / algorithmic bytes of the weight-streaming GEMM kernel
 
 
 def workload_spec(name, n_gpus):
@@ -70,6 +81,7 @@ class ClockSampler:
     def start(self):
         self.thread = threading.Thread(target=self._run, daemon=True)
         self.thread.start()
+        return self
 
     def stop(self):
         self.stop_flag.set()
@@ -97,6 +109,7 @@ def load_peaks():
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
 
 
+# ------------------------------------------------------------------ CPU arm
 def cpu_oracle_run(spec, steps, sample_tokens=None, seed=0):
     """Times the CPU oracle (PyTorch eager + numpy dequant on the host cores) on a bounded sample:
     the touched experts of `steps` seeded inputs of the workload, capped at sample_tokens tokens."""
@@ -154,67 +167,39 @@ def run_reference(args, spec):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    from muse_moe_w4a16 import inputs
+
+    s = inputs.SHAPES[spec["shape"]]
     sample_tokens = cpu_sample_tokens(spec)
     steps = max(1, min(args.steps, 3))
     for _ in range(min(args.warmup, 1)):
         cpu_oracle_run(spec, 1, sample_tokens, seed=100)
     base, sec_per_step = cpu_oracle_run(spec, steps, sample_tokens)
+    config = {"workload": spec["name"], "hidden": s["H"], "inter": s["I"], "experts": s["E"], "top_k": s["k"]}
+    config["tokens_per_gpu" if spec["shape"] == "ep" else "tokens"] = spec["T"]
     line = {"impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": args.gpus,
             "steps": steps, "warmup": min(args.warmup, 1), "ms_per_step": sec_per_step * 1e3,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16 x nvfp4 -> fp32 acc",
-            "data": "synthetic", "config": {"workload": spec["name"]}, "cpu_baseline": base,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": DTYPE,
+            "data": "synthetic", "config": config, "cpu_baseline": base,
             "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
 
 
-def run_gpu(args, spec):
+# ------------------------------------------------------------ one GPU, one workload
+def measure(moe, inputs, state, spec, steps, warmup, peaks, dev, flush, with_e2e=True):
+    """Times one workload on a prepared state. Returns the dict that goes into the JSON line."""
     import torch
-    import torch.distributed as dist
-    import muse_moe_w4a16 as moe
-    from muse_moe_w4a16 import inputs
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
     s = inputs.SHAPES[spec["shape"]]
     H, I, E, k, T = s["H"], s["I"], s["E"], s["k"], spec["T"]
-    if world > 1:
-        from muse_moe_w4a16 import ep
-        return ep.bench_ep(args, spec, dev, rank, world, METRIC, UNIT, ClockSampler, load_peaks)
-
-    if args.experts:
-        # a smaller instance of the same kernels: fewer experts resident, same per-expert shapes
-        s = dict(s, E=args.experts)
-        inputs.SHAPES[spec["shape"]] = s
-        E = args.experts
-        spec = dict(spec, name=spec["name"] + f"_E{E}resident")
-    peaks = load_peaks()
-    weights = inputs.make_weights(H, I, E, 0, dev)
-    state = moe.prepare(weights, n_experts=E, top_k=k, max_tokens=T, token_tile=args.token_tile)
-    del weights
-    torch.cuda.empty_cache()
-    if args.profile_only:
-        flush = torch.empty(64 * 1024 * 1024, dtype=torch.int32, device=dev)
-        for i in range(max(args.warmup, 1) + args.steps):
-            data, _ = inputs.make_inputs(spec["shape"], T, i % POOL, dev)
-            flush.zero_()
-            moe.kernel_fn(data, state)
-        torch.cuda.synchronize()
-        print(json.dumps({"profile_only": spec["name"], "plan": moe.plan(state, T), "status": moe.read_status(state)}))
-        return
     pool, host_pool = [], []
     for i in range(POOL):
         data, _ = inputs.make_inputs(spec["shape"], T, i, dev)
         pool.append(data)
-        host_pool.append({"hidden_states": data["hidden_states"].cpu().pin_memory(),
-                          "router_logits": data["router_logits"].cpu().pin_memory()})
-    flush = torch.empty(64 * 1024 * 1024, dtype=torch.int32, device=dev)  # 256 MiB > 126 MB of L2
-
-    # touched experts / routed pairs of each pooled input (host side, outside any timed region)
+        if with_e2e:
+            host_pool.append({"hidden_states": data["hidden_states"].cpu().pin_memory(),
+                              "router_logits": data["router_logits"].cpu().pin_memory()})
+    # touched experts of each pooled input (host side, outside any timed region)
     touched = []
     for data in pool:
         _, ids, _ = moe.kernel_fn(data, state, return_routing=True)
@@ -224,7 +209,7 @@ def run_gpu(args, spec):
         raise RuntimeError("device status word is non-zero after warm-up")
 
     # CUDA graphs: one per pooled input
-    graphs, outs = [], []
+    graphs = []
     side = torch.cuda.Stream()
     side.wait_stream(torch.cuda.current_stream())
     with torch.cuda.stream(side):
@@ -234,12 +219,10 @@ def run_gpu(args, spec):
     for data in pool:
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g):
-            o = moe.kernel_fn(data, state)
+            moe.kernel_fn(data, state)
         graphs.append(g)
-        outs.append(o)
 
-    sampler = ClockSampler(local_rank)
-    sampler.start()
+    sampler = ClockSampler(dev.index or 0).start()
 
     def timed_graph_steps(n):
         evs = []
@@ -253,38 +236,55 @@ def run_gpu(args, spec):
         torch.cuda.synchronize()
         return [a.elapsed_time(b) for a, b in evs]
 
-    timed_graph_steps(max(args.warmup, 3))
-    torch.cuda.synchronize()
-    step_ms = timed_graph_steps(args.steps)
+    timed_graph_steps(max(warmup, 3))
+    step_ms = timed_graph_steps(steps)
     total_ms = sum(step_ms)
 
-    # end to end with host buffers through the module's graphed step (the decode layer's way of calling it):
-    # pinned host inputs -> static device buffers, graph replay, output back to pinned host memory
-    step = moe.GraphedStep(state, pool[0])
-    out_h = torch.empty((T, H), dtype=torch.bfloat16).pin_memory()
+    e2e = None
+    if with_e2e:
+        # end to end with host buffers through the module's graphed step (the decode layer's way of calling
+        # it): pinned host inputs -> static device buffers, graph replay, output back to pinned host memory
+        step = moe.GraphedStep(state, pool[0])
+        out_h = torch.empty((T, H), dtype=torch.bfloat16).pin_memory()
 
-    def e2e_steps(n):
-        evs = []
-        for i in range(n):
-            flush.zero_()
-            hp = host_pool[i % POOL]
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            o = step(hp)
-            out_h.copy_(o, non_blocking=True)
-            e1.record()
-            evs.append((e0, e1))
-            if i % 64 == 63:
+        def e2e_steps(n):
+            evs = []
+            for i in range(n):
+                flush.zero_()
+                hp = host_pool[i % POOL]
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                out_h.copy_(step(hp), non_blocking=True)
+                e1.record()
+                evs.append((e0, e1))
+                if i % 64 == 63:
+                    torch.cuda.synchronize()
+            torch.cuda.synchronize()
+            return [a.elapsed_time(b) for a, b in evs]
+
+        def wall_steps(n):
+            # what a caller that needs the result on the host feels: Python, staging copy, launch, D2H, sync
+            ts = []
+            for i in range(n):
+                flush.zero_()
                 torch.cuda.synchronize()
-        torch.cuda.synchronize()
-        return [a.elapsed_time(b) for a, b in evs]
+                hp = host_pool[i % POOL]
+                t0 = time.perf_counter()
+                out_h.copy_(step(hp), non_blocking=True)
+                torch.cuda.synchronize()
+                ts.append((time.perf_counter() - t0) * 1e3)
+            return ts
 
-    e2e_steps(max(args.warmup, 3))
-    e2e_ms = e2e_steps(args.steps)
+        e2e_steps(max(warmup, 3))
+        e2e_ms = e2e_steps(steps)
+        wall = wall_steps(min(steps, 100))
+        e2e = {"value": T * steps / (sum(e2e_ms) * 1e-3), "unit": UNIT, "h2d_bytes_per_step": T * H * 2 + T * E * 4,
+               "d2h_bytes_per_step": T * H * 2, "ms_per_step": sum(e2e_ms) / steps,
+               "wall_ms_per_step": statistics.median(wall), "wall_value": T / (statistics.median(wall) * 1e-3)}
 
-    # dominant kernel, event-timed inside the step
-    n_prof = max(3, min(args.steps, 200))
-    k_ms = [0.0, 0.0, 0.0, 0.0]
+    # the kernels, event-timed one by one inside the step
+    n_prof = max(3, min(steps, 200))
+    k_ms = [0.0] * 5
     for i in range(n_prof + 3):
         flush.zero_()
         _, ms = moe.kernel_fn_timed(pool[i % POOL], state)
@@ -298,61 +298,260 @@ def run_gpu(args, spec):
     mean_touched = sum(touched[i % POOL] for i in range(n_prof)) / n_prof
     R = T * k
     plan = moe.plan(state, T)
-    hbm_bound = T <= 1024
-    fused = plan[0] == 8   # the single-launch kernel for up to 8 tokens: it is the whole step
-    if fused:
+    one_launch = plan[0] == 8 or (plan[1] == 0 and T <= 32 and R <= 256)
+    step_bytes = sum(inputs.algorithmic_bytes(H, I, E, k, T, touched[i % POOL]) for i in range(steps)) / steps
+    step_flops = inputs.algorithmic_flops(H, I, R)
+    if one_launch:
         alg = sum(inputs.algorithmic_bytes(H, I, E, k, T, touched[i % POOL]) for i in range(n_prof)) / n_prof
-        achieved = alg / (k_ms[1] * 1e-3) / 1e9
+        achieved = alg / (k_ms[2] * 1e-3) / 1e9
         roof = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                "frac": achieved / peaks["hbm_gbs"], "traffic": None, "kernel": "moe_small_kernel (whole step)",
+                "frac": achieved / peaks["hbm_gbs"], "traffic": alg * NCU_TRAFFIC_RATIO,
+                "traffic_source": "ncu dram bytes of a weight-streaming GEMM capture / its algorithmic bytes (1.015), scaled",
+                "kernel": ("moe_small_kernel" if plan[0] == 8 else "moe_gemm_kernel<N,2>") + " (whole step in one launch)",
                 "peak_source": peaks["source"] + " (burst copy)"}
-    elif hbm_bound:
+    elif T <= 1024:
         # gate/up GEMM: touched experts' W13 tiles + the x rows it gathers + the inter rows it writes
         alg13 = mean_touched * (2 * I * H * 0.5625 + 4) + 2.0 * T * H + 2.0 * R * I
-        achieved = alg13 / (k_ms[1] * 1e-3) / 1e9
-        # DRAM traffic per launch: the ncu capture of this kernel on a 32-expert case read and
-        # wrote 1.015 x its algorithmic bytes; weights dominate both, so it scales with the touched experts
+        achieved = alg13 / (k_ms[2] * 1e-3) / 1e9
         roof = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                "frac": achieved / peaks["hbm_gbs"], "traffic": alg13 * NCU_TRAFFIC_RATIO_GATE_UP,
+                "frac": achieved / peaks["hbm_gbs"], "traffic": alg13 * NCU_TRAFFIC_RATIO,
                 "traffic_source": "ncu dram bytes of the 32-expert T=64 capture / its algorithmic bytes (1.015), scaled",
                 "kernel": "moe_gemm_kernel<N,0> (gate/up)", "peak_source": peaks["source"] + " (burst copy)"}
     else:
         fl13 = 2.0 * R * 2 * I * H
-        achieved = fl13 / (k_ms[1] * 1e-3) / 1e12
+        achieved = fl13 / (k_ms[2] * 1e-3) / 1e12
         roof = {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
-                "frac": achieved / peaks["bf16_tflops_sustained"], "traffic": None,
-                "kernel": "moe_gemm_kernel<N,0> (gate/up)", "peak_source": peaks["source"] + " (sustained)"}
-    step_bytes = sum(inputs.algorithmic_bytes(H, I, E, k, T, touched[i % POOL]) for i in range(args.steps))
-    step_flops = inputs.algorithmic_flops(H, I, R) * args.steps
+                "frac": achieved / peaks["bf16_tflops_sustained"], "frac_of_burst_peak": achieved / peaks["bf16_tflops"],
+                "peak_burst": peaks["bf16_tflops"], "traffic": None,
+                "kernel": "moe_gemm_kernel<N,0> (gate/up)", "peak_source": peaks["source"] + " (sustained; burst beside it)"}
+    sec = total_ms / steps * 1e-3
+    if one_launch:
+        launches = 1
+    elif plan[1] == 2 and T <= 32 and R <= 256:
+        launches = 3      # row copy, gate/up kernel (routes, sorts), down kernel (combines)
+    else:                 # [top-k +] sort (one launch up to 32 tokens, three from 16384 entries), row copy, two GEMMs, combine
+        launches = 4 if T <= 32 else 6 + (2 if T * k >= 16384 else 0)
+    return {
+        "workload": spec["name"], "tokens": T, "steps": steps, "ms_per_step": total_ms / steps,
+        "value": T / sec, "unit": UNIT,
+        "plan": {"token_tile": plan[0], "path": plan[1], "flat_shares": plan[2], "ctas": plan[3],
+                 "touched_experts_mean": mean_touched},
+        "gpu_launches_per_step": launches,
+        "roofline": roof,
+        "step_roofline": {"hbm_frac": step_bytes / sec / 1e9 / peaks["hbm_gbs"],
+                          "tensor_frac": step_flops / sec / 1e12 / peaks["bf16_tflops_sustained"],
+                          "tensor_frac_of_burst_peak": step_flops / sec / 1e12 / peaks["bf16_tflops"],
+                          "algorithmic_bytes_per_step": step_bytes, "algorithmic_flops_per_step": step_flops},
+        "kernel_ms": {"route_sort": k_ms[0], "row_copy": k_ms[1], "gemm_gate_up": k_ms[2], "gemm_down": k_ms[3],
+                      "combine": k_ms[4]},
+        "e2e": e2e, "clocks": clocks,
+    }
+
+
+def run_gpu(args, spec):
+    import torch
+    import muse_moe_w4a16 as moe
+    from muse_moe_w4a16 import _lib, inputs
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        return run_ep(args, spec, dev)
+
+    s = inputs.SHAPES[spec["shape"]]
+    if args.experts:
+        # a smaller instance of the same kernels: fewer experts resident, same per-expert shapes
+        for key in ("decode", "sweep", "prefill"):
+            inputs.SHAPES[key] = dict(inputs.SHAPES[key], E=args.experts)
+        s = inputs.SHAPES[spec["shape"]]
+        spec = dict(spec, name=spec["name"] + f"_E{args.experts}resident")
+    H, I, E, k, T = s["H"], s["I"], s["E"], s["k"], spec["T"]
+    peaks = load_peaks()
+    sweep_specs = []
+    if args.workload == "auto" and not args.no_sweep and not args.profile_only:
+        sweep_specs = [workload_spec(w, 1) for w in SWEEP]
+        if args.experts:
+            sweep_specs = [dict(w, name=w["name"] + f"_E{args.experts}resident") for w in sweep_specs]
+    max_tokens = max([T] + [w["T"] for w in sweep_specs])
+    weights = inputs.make_weights(H, I, E, 0, dev)
+    state = moe.prepare(weights, n_experts=E, top_k=k, max_tokens=max_tokens, token_tile=args.token_tile,
+                        decode_path=args.decode_path)
+    del weights
+    torch.cuda.empty_cache()
+    flush = torch.empty(64 * 1024 * 1024, dtype=torch.int32, device=dev)  # 256 MiB > 126 MB of L2
+    if args.profile_only:
+        for i in range(max(args.warmup, 1) + args.steps):
+            data, _ = inputs.make_inputs(spec["shape"], T, i % POOL, dev)
+            flush.zero_()
+            moe.kernel_fn(data, state)
+        torch.cuda.synchronize()
+        print(json.dumps({"profile_only": spec["name"], "plan": moe.plan(state, T), "status": moe.read_status(state)}))
+        return
+
+    head = measure(moe, inputs, state, spec, args.steps, args.warmup, peaks, dev, flush)
+    sweep = []
+    for w in sweep_specs:
+        n = max(5, min(args.steps, 20 if w["T"] > 1024 else 100))
+        sweep.append(measure(moe, inputs, state, w, n, min(args.warmup, 5), peaks, dev, flush))
     cpu_base, _ = cpu_oracle_run(spec, 2, cpu_sample_tokens(spec))
 
-    h2d = T * H * 2 + T * E * 4
-    d2h = T * H * 2
     line = {
-        "metric": METRIC, "value": T * args.steps / (total_ms * 1e-3), "unit": UNIT, "n_gpus": 1, "steps": args.steps,
-        "warmup": max(args.warmup, 3), "ms_per_step": total_ms / args.steps, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "bf16 x nvfp4 -> fp32 acc", "data": "synthetic",
+        "metric": METRIC, "value": head["value"], "unit": UNIT, "n_gpus": 1, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": head["ms_per_step"], "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": DTYPE, "data": "synthetic",
         "config": {"workload": spec["name"], "tokens": T, "hidden": H, "inter": I, "experts": E, "top_k": k,
-                   "l2": "flushed by a 256 MiB write before every timed step", "cuda_graph": True,
-                   "token_tile": plan[0], "split_k13": plan[1], "split_k2": plan[2], "ctas": plan[3],
-                   "touched_experts_mean": mean_touched},
-        "e2e": {"value": T * args.steps / (sum(e2e_ms) * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": d2h, "ms_per_step": sum(e2e_ms) / args.steps},
-        # per step: fused top-k + sort | top-k, sort (three launches from 16384 entries on), F16 row copy;
-        # two GEMMs; combine
-        "gpu_launches": (1 if fused else 4 if T <= 32 else 6 + (2 if T * k >= 16384 else 0)) * args.steps,
-        "roofline": roof,
-        "step_roofline": {"hbm_frac": step_bytes / (total_ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
-                          "tensor_frac": step_flops / (total_ms * 1e-3) / 1e12 / peaks["bf16_tflops_sustained"],
-                          "algorithmic_bytes_per_step": step_bytes / args.steps},
-        "kernel_ms": {"sort": k_ms[0], "gemm_gate_up": k_ms[1], "gemm_down": k_ms[2], "combine": k_ms[3]},
-        "cpu_baseline": cpu_base,
-        "clocks": clocks,
+                   "l2": "flushed by a 256 MiB write before every timed step; CUDA-graph replays"},
+        "plan": dict(head["plan"], workspace_bytes=state["workspace_bytes"], build_id=_lib.build_id()),
+        "e2e": head["e2e"],
+        "gpu_launches": head["gpu_launches_per_step"] * args.steps,
+        "roofline": head["roofline"], "step_roofline": head["step_roofline"], "kernel_ms": head["kernel_ms"],
+        "cpu_baseline": cpu_base, "clocks": head["clocks"],
+        "sweep": sweep,
     }
     print(json.dumps(line), flush=True)
 
 
-NCU_TRAFFIC_RATIO_GATE_UP = 1.015   # ncu: DRAM bytes read + written / algorithmic bytes, gate/up kernel, 32-expert T = 64 case
+# ------------------------------------------------------------ expert parallel, N GPUs
+def run_ep(args, spec, dev):
+    """--gpus N > 1: config 4 (H7168 I2048 E256 top-8, T = 4096 per GPU), one rank per GPU."""
+    import torch
+    import torch.distributed as dist
+    import muse_moe_w4a16 as moe
+    from muse_moe_w4a16 import _lib, ep, inputs
+
+    world, rank = int(os.environ["WORLD_SIZE"]), int(os.environ["RANK"])
+    dist.init_process_group("nccl", device_id=dev)
+    s = inputs.SHAPES[spec["shape"]]
+    H, I, E, k, T = s["H"], s["I"], s["E"], s["k"], spec["T"]
+    per = E // world
+    CHECK = max(8, 256 // world)   # tokens per rank checked against the one-GPU step
+
+    def rank_weights(r):
+        return inputs.make_weights_random_bytes(H, I, per, 1000 + r, dev)
+
+    def rank_input(r, i):
+        return inputs.make_inputs(spec["shape"], T, 17 * r + i, dev)[0]
+
+    # rank 0, alone: the same shape with all experts on one GPU -> reference rows for every rank, and the
+    # one-GPU step time of the same per-GPU token count
+    single_ms = torch.zeros(1, device=dev)
+    ref_rows = torch.zeros((world, CHECK, H), dtype=torch.bfloat16, device=dev)
+    if rank == 0:
+        parts = [rank_weights(r) for r in range(world)]
+        allw = {key: torch.cat([p[key].view(torch.uint8) if p[key].dtype == torch.float8_e4m3fn else p[key] for p in parts])
+                for key in parts[0]}
+        del parts
+        st1 = moe.prepare(allw, n_experts=E, top_k=k, max_tokens=T)
+        del allw
+        torch.cuda.empty_cache()
+        for r in range(world):
+            d = rank_input(r, 0)
+            ref_rows[r] = moe.kernel_fn({"hidden_states": d["hidden_states"][:CHECK].contiguous(),
+                                         "router_logits": d["router_logits"][:CHECK].contiguous()}, st1)
+        d = rank_input(0, 0)
+        for _ in range(3):
+            moe.kernel_fn(d, st1)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for i in range(5):
+            moe.kernel_fn(d, st1)
+        e1.record()
+        torch.cuda.synchronize()
+        single_ms[0] = e0.elapsed_time(e1) / 5
+        if moe.read_status(st1) != 0:
+            raise RuntimeError("device status word is non-zero in the one-GPU reference step")
+        del st1, d
+        torch.cuda.empty_cache()
+    dist.broadcast(single_ms, 0)
+    dist.broadcast(ref_rows, 0)
+
+    mod = ep.EPModule(rank_weights(rank), rank, world, E, k, T, chunks=(args.ep_chunks or None))
+    torch.cuda.empty_cache()
+    pool = [rank_input(rank, i) for i in range(4)]
+    host_pool = [{"hidden_states": d["hidden_states"].cpu().pin_memory(),
+                  "router_logits": d["router_logits"].cpu().pin_memory()} for d in pool]
+
+    # parity: this rank's first CHECK tokens of input 0 through the expert-parallel step
+    got = mod.kernel_fn(pool[0])[:CHECK].float()
+    want = ref_rows[rank].float()
+    rel = ((got - want).abs().max() / want.abs().max().clamp_min(1e-30)).reshape(1)
+    dist.all_reduce(rel, op=dist.ReduceOp.MAX)
+    ep_parity = float(rel.item())
+
+    sampler = ClockSampler(dev.index).start()
+
+    def run(n, e2e):
+        xd = torch.empty((T, H), dtype=torch.bfloat16, device=dev)
+        ld = torch.empty((T, E), dtype=torch.float32, device=dev)
+        out_h = torch.empty((T, H), dtype=torch.bfloat16).pin_memory()
+        dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(n):
+            if e2e:
+                hp = host_pool[i % len(pool)]
+                xd.copy_(hp["hidden_states"], non_blocking=True)
+                ld.copy_(hp["router_logits"], non_blocking=True)
+                o = mod.kernel_fn({"hidden_states": xd, "router_logits": ld})
+                out_h.copy_(o, non_blocking=True)
+            else:
+                mod.kernel_fn(pool[i % len(pool)])
+        e1.record()
+        torch.cuda.synchronize()
+        dist.barrier()
+        t = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    run(max(args.warmup, 3), False)
+    ms = run(args.steps, False)
+    run(max(args.warmup, 3), True)
+    ms_e2e = run(args.steps, True)
+    clocks = sampler.stop()
+    status = torch.tensor([moe.read_status(mod.state)], device=dev)
+    dist.all_reduce(status, op=dist.ReduceOp.MAX)
+    if int(status.item()) != 0:
+        raise RuntimeError("device status word is non-zero on some rank")
+    if ep_parity > 1e-2:
+        raise RuntimeError(f"expert-parallel output differs from the one-GPU step: max-abs-rel {ep_parity:.3e}")
+    if rank == 0:
+        peaks = load_peaks()
+        flops = inputs.algorithmic_flops(H, I, T * k * world) * args.steps
+        step_ms = ms / args.steps
+        line = {
+            "metric": METRIC, "value": T * world * args.steps / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": step_ms,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": DTYPE,
+            "data": "synthetic",
+            "config": {"workload": spec["name"], "tokens_per_gpu": T, "hidden": H, "inter": I, "experts": E,
+                       "top_k": k, "parallelism": f"ep{world}",
+                       "l2": "inputs and weights exceed L2 (792 MB of weights per rank at 8 ranks)",
+                       "dispatch": f"{mod.transport}, {mod.chunks} chunk(s) of source ranks", "build_id": _lib.build_id()},
+            "e2e": {"value": T * world * args.steps / (ms_e2e * 1e-3), "unit": UNIT,
+                    "h2d_bytes_per_step": (T * H * 2 + T * E * 4) * world, "d2h_bytes_per_step": T * H * 2 * world,
+                    "ms_per_step": ms_e2e / args.steps},
+            # per rank and step: top-k, the final rank-order sum, and per chunk the sort (three launches from
+            # 16384 entries on), the F16 row copy, two GEMMs and the combine
+            "gpu_launches": (2 + (7 if (world // mod.chunks) * T * k >= 16384 else 5) * mod.chunks) * args.steps * world,
+            "ep_parity_max_rel": ep_parity, "ep_parity_tokens_per_rank": CHECK,
+            "single_gpu_same_shape_ms": float(single_ms.item()),
+            "scaling_efficiency": float(single_ms.item()) / step_ms,
+            "roofline": {"bound": "tensor", "achieved": flops / world / (ms * 1e-3) / 1e12,
+                         "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
+                         "frac": flops / world / (ms * 1e-3) / 1e12 / peaks["bf16_tflops_sustained"],
+                         "frac_of_burst_peak": flops / world / (ms * 1e-3) / 1e12 / peaks["bf16_tflops"], "traffic": None,
+                         "kernel": "whole EP step per GPU (expert kernels + exchange)",
+                         "peak_source": peaks["source"] + " (sustained; burst beside it)"},
+            "cpu_baseline": None,
+            "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
 
 
 def main():
@@ -362,9 +561,11 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--workload", default="auto")
+    ap.add_argument("--no-sweep", action="store_true", help="one GPU, default workload: leave out the other points of the metric")
     ap.add_argument("--experts", type=int, default=0, help="resident experts (smaller case for profiler captures)")
     ap.add_argument("--ep-chunks", type=int, default=0, help="expert-parallel runs: chunks of source ranks (0 = default)")
-    ap.add_argument("--token-tile", type=int, default=0, help="force a kernel: 16/32/64/128, 8 = single-launch kernel")
+    ap.add_argument("--token-tile", type=int, default=0, help="force a kernel: 16/32/64/128, 8 = the mma.sync single-launch kernel")
+    ap.add_argument("--decode-path", type=int, default=0, help="few tokens: 0 one launch, 1 chain of launches, 2 three launches")
     ap.add_argument("--profile-only", action="store_true", help="run warmup+steps eager steps and exit (for ncu)")
     args = ap.parse_args()
     spec = workload_spec(args.workload, args.gpus)

@@ -55,9 +55,15 @@ typedef struct MskMoeCfg {
   int32_t routing_mode;  /* MSK_ROUTE_* */
   float route_scale;     /* sigmoid mode: logit multiplier (reference: 1/sqrt(32)) */
   float post_norm_eps;   /* eps of the post-expert RMS norm (reference: 1e-8) */
-  int32_t num_ctas;      /* persistent grid size; 0 = one CTA per SM of the current device */
-  int32_t split_k13;     /* K splits of the gate/up GEMM; 0 = chosen from n_tokens */
-  int32_t split_k2;      /* K splits of the down GEMM;    0 = chosen from n_tokens */
+  int32_t num_ctas;      /* persistent grid size (at most 512); 0 = 148, one CTA per SM of a B200. The shares of the
+                            weight stream, and so the order in which a cut unit's partial sums are added, follow
+                            this number and the shapes, never the device */
+  int32_t decode_path;   /* steps of few tokens (n_tokens <= 32, n_tokens * top_k <= 256, token tile <= 32):
+                            0 = one launch (routing, sort, both GEMMs and the combine in one kernel),
+                            1 = the chain of launches used for many tokens,
+                            2 = row copy, gate/up kernel that routes and sorts, down kernel that combines */
+  int32_t no_pdl;        /* non-zero: launches are not chained with programmatic dependent launch (the reference's
+                            okc_set_pdl(0), muse_moe_w4a16/cuda/moe.cu:2348,2565) */
   int32_t token_tile;    /* MMA N (tokens per tile): 16/32/64/128, or 8 = the single-launch kernel for
                             up to 8 tokens; 0 = chosen from n_tokens */
   int32_t max_tokens;    /* token capacity the workspace is sized for (msk_moe_forward rejects more) */
@@ -130,7 +136,8 @@ int msk_moe_workspace_init(const MskMoeCfg* cfg, void* workspace, size_t workspa
  * (muse_moe_w4a16/cuda/moe.cu:440-478, 2604-2766). x: bf16 [T, H]; topk_ids int32 [T, k]
  * (global ids); topk_weights fp32 [T, k]; gs13/gs2 fp32 [local_count]; post_norm_w bf16 [H]
  * or NULL; out bf16 [T, H], fully overwritten (zeros for tokens without a local route).
- * Launches: sort, gate/up GEMM, down GEMM, combine. No host sync; capturable in a CUDA graph. */
+ * Launches: sort, [row copy,] gate/up GEMM, down GEMM, combine; a single launch for a few tokens
+ * (see MskMoeCfg.decode_path). No host sync; capturable in a CUDA graph. */
 int msk_moe_forward(const MskMoeCfg* cfg, const void* packed13, const void* packed2, const float* gs13,
                     const float* gs2, const void* post_norm_w, const void* x, const int32_t* topk_ids,
                     const float* topk_weights, void* out, void* workspace, size_t workspace_bytes, int n_tokens,
@@ -158,9 +165,10 @@ int msk_moe_forward_prenorm(const MskMoeCfg* cfg, const void* packed13, const vo
                             float* topk_weights, void* out, void* workspace, size_t workspace_bytes, int n_tokens,
                             void* stream);
 
-/* msk_moe_forward with a CUDA event before and after each of its four launches. Waits for the
- * last one and returns the elapsed milliseconds host_ms[4] = sort, gate/up GEMM, down GEMM,
- * combine. A measuring entry point: it synchronises and creates its events on first use; the
+/* msk_moe_forward with a CUDA event before and after each of its launches. Waits for the last one
+ * and returns the elapsed milliseconds host_ms[5] = routing + sort, row copy, gate/up GEMM, down
+ * GEMM, combine (a stage that a path does not launch reads 0; the one-launch path reports the whole
+ * step under gate/up). A measuring entry point: it synchronises and creates its events on first use; the
  * counterpart of the reference's in-kernel %globaltimer trace (muse_moe_w4a16/cuda/moe.cu:279-284). */
 int msk_moe_forward_timed(const MskMoeCfg* cfg, const void* packed13, const void* packed2, const float* gs13,
                           const float* gs2, const void* post_norm_w, const void* x, const int32_t* topk_ids,
@@ -186,10 +194,20 @@ int msk_moe_forward_static(const MskMoeCfg* cfg, const void* packed13, const voi
  * Allocates nothing; not for the timed path. No counterpart in the reference. */
 int msk_moe_static_status(int* host_status, void* stream);
 
-/* The launch plan msk_moe_forward uses for n_tokens: host_out[4] = token tile N, K splits of the
- * gate/up GEMM, K splits of the down GEMM, persistent grid size. The reference picks its build by
+/* The launch plan msk_moe_forward uses for n_tokens: host_out[4] = token tile N, path (as
+ * MskMoeCfg.decode_path; always 1 beyond a few tokens), 1 when the weight stream is cut into equal
+ * shares (else whole units), persistent grid size. The reference picks its build by
  * token count the same way (muse_moe_w4a16/py/03_kernel_fn.py:33-40). */
 int msk_moe_plan(const MskMoeCfg* cfg, int n_tokens, int* host_out);
+
+/* How the GEMM kernels deal their work (host-side twin of the device code, a test hook): the pieces
+ * that CTA `cta` of `shares` gets from n_base base units of n_stages K stages each. mode 0: whole
+ * units round-robin (token tile 128), 1: whole units in contiguous ranges, 2: equal shares of the
+ * flat (unit, stage) list. host_out receives six ints per piece: base unit, first stage, end stage,
+ * slot of the partial buffer (-1 for a whole unit), first and last CTA holding a piece of the unit.
+ * The reference's counterpart is its cost-weighted range scheduler (muse_moe_w4a16/cuda/moe.cu:2245-2289). */
+int msk_moe_share_pieces(int n_base, int n_stages, int shares, int mode, int cta, int* host_out, int capacity,
+                         int* host_count);
 
 /* Views into the workspace after msk_moe_forward (device pointers, for parity tests):
  * which: 0 cnt, 1 off, 2 perm, 3 inv, 4 inter (fp16 [R, I], holding bf16-rounded values), 5 y (fp32 [R, H]; bf16 [R, H] when the plan's

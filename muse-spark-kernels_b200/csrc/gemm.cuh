@@ -17,18 +17,36 @@
 // Measured on B200: tcgen05.mma M=128 N=16 K=16 with A in TMEM retires every ~9 cycles, with
 // A in shared memory every ~39; the decode ALU work (~2 instructions per weight) is what has
 // to be spread over all four schedulers, hence sixteen dequant warps.
-// A pair is (gate tile j, up tile j) for PHASE 0, so SwiGLU pairs sit in the same TMEM lane,
-// and (row tile 2j, row tile 2j+1) for PHASE 1. Both tiles of a pair share the B operand.
+// A pair is (gate tile j, up tile j) for the gate/up GEMM (phase 0), so SwiGLU pairs sit in the same
+// TMEM lane, and (row tile 2j, row tile 2j+1) for the down GEMM (phase 1). Both tiles of a pair
+// share the B operand.
 //
-// A work unit is (token tile, pair, K split), dealt round-robin to CTAs. Accumulators are
-// double-buffered in TMEM (N <= 64) so the epilogue of a unit overlaps the main loop of the
-// next. With more than one K split every unit stores raw FP32 accumulators to a partial
-// buffer and takes a ticket; the unit that draws the last ticket sums the partials in
-// split order 0..S-1 (the order never depends on arrival) and runs the epilogue.
+// One kernel template, three modes: MODE 0 runs phase 0, MODE 1 phase 1 (two launches chained by
+// programmatic dependent launch, any token count), MODE 2 both phases in one launch for a few tokens:
+// the weight stream, the dequant ring and the MMA pipeline run on from the last gate/up stage into
+// the first down stage without draining; only the activation gather of phase 1 waits, on a grid-wide
+// counter, until every CTA has written its rows of `inter` (the reference's single persistent kernel
+// hands over the same way, muse_moe_w4a16/cuda/moe.cu:2340-2768). MODE 2 also routes, sorts and
+// converts the token rows itself and ends with the folded combine: the step is one launch.
+//
+// Work. A base unit is (token tile, pair); its reduction runs over K / 256 stages. The base units
+// are laid out as one flat list ordered (token tile, pair) and dealt to the CTAs in one of three ways
+// (PieceIter below):
+//   flat   (few routed rows, token tiles up to 64): the list of (base unit, K stage) items is cut into
+//          gridDim.x equal contiguous shares, so every SM streams the same number of weight bytes
+//          whatever the number of units. A unit cut between CTAs is accumulated as "pieces": every
+//          piece stores its raw FP32 accumulators to a slot of the partial buffer and takes a ticket,
+//          the piece that draws the last ticket sums the pieces in ascending K order (the order never
+//          depends on arrival) and runs the epilogue. Cut points depend on the shapes, the number of
+//          token tiles and the grid size given by the host, not on the device;
+//   contiguous whole units (token tiles up to 64, many units): CTA c owns units [n c / G, n (c+1) / G);
+//   round-robin whole units (token tile 128).
+// Accumulators are double-buffered in TMEM (N <= 64) so the epilogue of a piece overlaps the main
+// loop of the next.
 //
 // Numerics: operands are e2m1*e4m3 (exact in F16) and the BF16 activations held as F16 (exact
-// in the F16 range), FP32 accumulation, accumulator * gs in the epilogue; PHASE 0 writes
-// bf16(silu(g) * u) (stored as F16), PHASE 1 writes FP32 rows times (1 + post_norm_w) when
+// in the F16 range), FP32 accumulation, accumulator * gs in the epilogue; phase 0 writes
+// bf16(silu(g) * u) (stored as F16), phase 1 writes FP32 rows times (1 + post_norm_w) when
 // given (muse_moe_w4a16/cuda/moe.cu:440-478).
 #pragma once
 #include <cstdint>
@@ -38,6 +56,7 @@
 
 #include "layout.cuh"
 #include "ptx.cuh"
+#include "route_sort.cuh"
 
 namespace msk {
 
@@ -74,34 +93,61 @@ struct GemmCfg {
   static_assert(NDBUF * 2 * N <= A_BASE && A_BASE + 2 * A_GROUP_COLS <= TMEM_COLS, "TMEM budget");
 };
 
-struct GemmParams {
-  CUtensorMap tmap_act;      // TMA_B only: [rows, K] bf16, box 64 x N, 128-byte swizzle (64-byte aligned: first member)
+struct PhaseParams {
   const uint8_t* w;          // packed tiles of this GEMM
   const float* gs;           // [local_count] global scales
-  const void* act;           // PHASE 0: x as f16 [T, H] (or sorted rows [R, H] with TMA_B); PHASE 1: inter f16 [R, I]
-  void* outp;                // PHASE 0: inter f16 [R, I]; PHASE 1: y fp32 [R, H]
-  const __nv_bfloat16* post_norm_w;  // PHASE 1 only, nullable
-  const int32_t* cnt;        // [local_count]
-  const int32_t* off;        // [local_count + 1]
-  const int32_t* perm;       // [R]
-  float* partial;            // split-K partials
-  int32_t* tickets;          // one per (token tile, pair)
+  const void* act;           // phase 0: x as f16 [T, H] (or sorted rows [R, H] with TMA_B); phase 1: inter f16 [R, I]
+  void* outp;                // phase 0: inter f16 [R, I]; phase 1: y fp32 [R, H]
+  float* partial;            // pieces of cut units: 2 * gridDim.x slots of 2 * 128 * N floats
+  int32_t* tickets;          // one per base unit, zero between launches
+  int K;                     // reduction length (H for phase 0, I for phase 1)
+  int out_ld;                // I for phase 0, H for phase 1
+  int n_pairs;               // pairs per expert
+  int pad_;
+};
+
+struct GemmParams {
+  CUtensorMap tmap_act[2];   // TMA_B only, per phase: [rows, K] f16, box 64 x N, 128-byte swizzle (64-byte aligned: first member)
+  PhaseParams ph[2];         // [0] gate/up, [1] down; a single-phase launch uses its own entry only
+  const __nv_bfloat16* post_norm_w;  // phase 1, nullable
+  int32_t* cnt;              // [local_count]      sort tables in global memory: read here, or written by CTA 0
+  int32_t* off;              // [local_count + 1]  when this kernel routes and sorts itself (route != 0)
+  int32_t* perm;             // [R]
+  int32_t* inv;              // [T * top_k]
   int32_t* status;           // workspace word 0
   unsigned long long* trace; // nullable: 16 %globaltimer stamps per CTA (see TR_* below)
-  int K;                     // reduction length (H for PHASE 0, I for PHASE 1)
-  int out_ld;                // I for PHASE 0, H for PHASE 1
-  int n_pairs;               // pairs per expert
   int nloc;
   int top_k;
-  int splits;
+  int flat;                  // 1: equal shares of the flat (base unit, K stage) list; 0: whole units
   int evict_first;
-  int y_bf16;                // PHASE 1 without K splits: y rows as BF16 instead of FP32
+  int y_bf16;                // phase 1, token tile 128: y rows as BF16 instead of FP32
+  // Phase 0 with route != 0 (at most 256 entries): every CTA derives the sort tables in its prologue.
+  // route 1: top-k of `logits` first (CTA 0 writes ids_out / tw_out); route 2: ids_in given.
+  int route;
+  const float* logits;       // [T, E]
+  const float* bias;         // [E], nullable
+  const int32_t* ids_in;     // [T, top_k]
+  int32_t* ids_out;
+  float* tw_out;
+  int T, E, lo, mode;
+  float route_scale;
+  // Phase 1 with fold != 0 (at most 32 tokens): the CTA that completes the last base unit of a token
+  // also does the token's weighted slot-order sum (the combine), so no combine launch follows.
+  int fold;
+  const float* tw;           // [T, top_k] routing weights
+  __nv_bfloat16* out;        // [T, H]
+  int32_t* tok_tickets;      // [T], zero between launches
+  float eps;                 // post-expert norm
+  // MODE 2: the token rows as given (BF16), converted to F16 into ph[0].act by all CTAs together, and
+  // the grid-wide counters: grid_bar[0] arrivals (one per CTA and stage), grid_bar[1] exits.
+  const __nv_bfloat16* x_bf16;
+  unsigned int* grid_bar;
 };
 
 // Trace slots (per CTA, nanoseconds): the counterpart of the reference's DBG(k) stamps
 // (muse_moe_w4a16/cuda/moe.cu:279-284).
 enum : int { TR_START = 0, TR_SETUP, TR_FIRST_BULK, TR_FIRST_RAW, TR_FIRST_AFULL, TR_FIRST_MMA, TR_FIRST_DFULL,
-              TR_FIRST_EPI_DONE, TR_LAST_DFULL, TR_END, TR_UNITS, TR_STAGES };
+              TR_FIRST_EPI_DONE, TR_LAST_DFULL, TR_END, TR_ROUTED, TR_FOLD_END };
 #define MSK_TR(slot) do { if (p.trace != nullptr) p.trace[blockIdx.x * 16 + (slot)] = globaltimer_ns(); } while (0)
 // Detailed event list of CTA 0: role r (0 first dequant thread, 1 MMA issuer, 2 weight producer)
 // appends up to 256 stamps, each tagged with a small code in the low 8 bits, after the
@@ -113,34 +159,38 @@ enum : int { TR_START = 0, TR_SETUP, TR_FIRST_BULK, TR_FIRST_RAW, TR_FIRST_AFULL
 #define MSK_TRD(role, idx, code) do { (void)(idx); } while (0)
 #endif
 
+constexpr int FOLD_MAX_TOKENS = 32;
+
 struct GemmCtrl {
   uint64_t raw_full[6], raw_empty[6], b_full[6], b_empty[6];
   uint64_t a_full[2][6], a_empty[2][6];
   uint64_t d_full[2], d_empty[2];
-  uint64_t epi_bar;  // the 128 epilogue threads, for the split-K ticket
+  uint64_t epi_bar;  // the 128 epilogue threads, for the tickets
   uint32_t tmem_base;
   int abort_word;
   int n_tiles;
   int last_flag;
+  int fin_n;                           // fold: tokens this CTA has to combine when its units are done
+  uint8_t fin_tok[FOLD_MAX_TOKENS];
+  uint8_t klocal[FOLD_MAX_TOKENS];     // fold: local routes of each token
+  uint8_t perm8[SMALL_SORT_MAX_ENTRIES];  // route / fold: entry index of each sorted row
 };
 static_assert(sizeof(GemmCtrl) <= 1024, "control block too large");
 
 struct UnitInfo {
-  int expert, row0, rows, pair, split, tile;
+  int expert, row0, rows, pair, tile;
 };
 
-// unit index -> (token tile, pair, split); the token tile is located in the per-expert
-// exclusive prefix of tile counts by binary search.
-__device__ __forceinline__ UnitInfo decode_unit(int u, const int* tile_start, const GemmParams& p, int N) {
+// base unit index -> (token tile, pair); the token tile is located in the per-expert exclusive
+// prefix of tile counts by binary search.
+__device__ __forceinline__ UnitInfo decode_unit(int base, const int* tile_start, int n_pairs, int nloc, int N) {
   // tile_start is followed in shared memory by copies of cnt[] and off[] (GemmCfg::TABLE_INTS apart)
   const int* cnt_s = tile_start + (MAX_LOCAL_EXPERTS + 4);
   const int* off_s = cnt_s + (MAX_LOCAL_EXPERTS + 4);
   UnitInfo ui;
-  ui.split = u % p.splits;
-  const int v = u / p.splits;
-  ui.pair = v % p.n_pairs;
-  ui.tile = v / p.n_pairs;
-  int lo = 0, hi = p.nloc;  // largest e with tile_start[e] <= tile
+  ui.pair = base % n_pairs;
+  ui.tile = base / n_pairs;
+  int lo = 0, hi = nloc;  // largest e with tile_start[e] <= tile
   while (hi - lo > 1) {
     const int mid = (lo + hi) >> 1;
     if (tile_start[mid] <= ui.tile) lo = mid; else hi = mid;
@@ -153,6 +203,61 @@ __device__ __forceinline__ UnitInfo decode_unit(int u, const int* tile_start, co
   return ui;
 }
 
+// ---- work distribution (see the header comment). Positions are indices into the flat list of
+// (base unit, K stage) items: pos = base * nst + ks.
+__host__ __device__ inline long long share_begin(long long items, int shares, int c) {
+  return items * c / shares;
+}
+// The share that holds item x: the largest c with share_begin(c) <= x.
+__host__ __device__ inline int share_owner(long long items, int shares, long long x) {
+  return static_cast<int>(((x + 1) * shares - 1) / items);
+}
+// Slot of the partial buffer for the piece of a cut unit that share c holds: a share holds at most
+// one piece that starts inside a unit (at the head of its range, slot 2c) and at most one that starts
+// a unit but does not finish it (at the tail of its range, slot 2c + 1).
+__host__ __device__ inline int piece_slot(int c, bool starts_unit) { return 2 * c + (starts_unit ? 1 : 0); }
+
+struct PieceIter {
+  long long pos, end;
+  int nst;
+  int rr_step;  // > 0: whole units, round-robin with this stride
+  __host__ __device__ bool next(int& base, int& ks0, int& ks1) {
+    if (pos >= end) return false;
+    base = static_cast<int>(pos / nst);
+    ks0 = static_cast<int>(pos - static_cast<long long>(base) * nst);
+    if (rr_step > 0) {
+      ks1 = nst;
+      pos += static_cast<long long>(rr_step) * nst;
+      return true;
+    }
+    const long long left = end - pos;
+    const int len = left < static_cast<long long>(nst - ks0) ? static_cast<int>(left) : nst - ks0;
+    ks1 = ks0 + len;
+    pos += len;
+    return true;
+  }
+};
+
+// mode 0: round-robin whole units; 1: contiguous whole units; 2: flat equal shares
+__host__ __device__ inline PieceIter make_piece_iter(int mode, int n_base, int nst, int c, int shares) {
+  PieceIter it;
+  it.nst = nst;
+  it.rr_step = 0;
+  if (mode == 0) {
+    it.pos = static_cast<long long>(c) * nst;
+    it.end = static_cast<long long>(n_base) * nst;
+    it.rr_step = shares;
+  } else if (mode == 1) {
+    it.pos = share_begin(n_base, shares, c) * nst;
+    it.end = share_begin(n_base, shares, c + 1) * nst;
+  } else {
+    const long long items = static_cast<long long>(n_base) * nst;
+    it.pos = share_begin(items, shares, c);
+    it.end = share_begin(items, shares, c + 1);
+  }
+  return it;
+}
+
 __device__ __forceinline__ float silu_f(float g) { return g / (1.0f + __expf(-g)); }
 
 // The SwiGLU value as the down GEMM reads it: rounded to BF16 (the reference's one rounding of
@@ -162,16 +267,17 @@ __device__ __forceinline__ __half inter_value(float v) {
   return __float2half_rn(fminf(fmaxf(r, -65504.f), 65504.f));
 }
 
-// Epilogue of a unit without K splits for the thread that owns TMEM lane `row`: columns
-// [c_beg, c_end) of the accumulators at d_tmem (lane base included). PHASE 0 reads gate (tile 0)
-// and up (tile 1) and writes bf16(silu(g) * u) into inter; PHASE 1 writes the rows of `tile`
-// scaled by gs (and 1 + post_norm_w) into y.
-template <int N, int PHASE>
-__device__ __forceinline__ void epilogue_columns(const GemmParams& p, const UnitInfo& ui, uint32_t d_tmem, int row,
-                                                 int c_beg, int c_end, int tile) {
-  const float gsc = p.gs[ui.expert];
-  if (PHASE == 0) {
-    __half* outp = static_cast<__half*>(p.outp) + static_cast<size_t>(ui.row0) * p.out_ld + ui.pair * 128 + row;
+// Epilogue of a whole unit for the thread that owns TMEM lane `row`: columns [c_beg, c_end) of the
+// accumulators at d_tmem (lane base included). Phase 0 reads gate (tile 0) and up (tile 1) and
+// writes bf16(silu(g) * u) into inter; phase 1 writes the rows of `tile` scaled by gs (and
+// 1 + post_norm_w) into y. (Used by the wide token tile, whose dequant warps share the epilogue.)
+template <int N>
+__device__ __forceinline__ void epilogue_columns(const GemmParams& p, const PhaseParams& pp, int phase,
+                                                 const UnitInfo& ui, uint32_t d_tmem, int row, int c_beg, int c_end,
+                                                 int tile) {
+  const float gsc = pp.gs[ui.expert];
+  if (phase == 0) {
+    __half* outp = static_cast<__half*>(pp.outp) + static_cast<size_t>(ui.row0) * pp.out_ld + ui.pair * 128 + row;
     for (int c0 = c_beg; c0 < c_end; c0 += 16) {
       if (c0 >= ui.rows) break;
       uint32_t r0[16], r1[16];
@@ -182,7 +288,7 @@ __device__ __forceinline__ void epilogue_columns(const GemmParams& p, const Unit
       for (int j = 0; j < 16; ++j) {
         if (c0 + j < ui.rows) {
           const float v = silu_f(__uint_as_float(r0[j]) * gsc) * (__uint_as_float(r1[j]) * gsc);
-          outp[static_cast<size_t>(c0 + j) * p.out_ld] = inter_value(v);
+          outp[static_cast<size_t>(c0 + j) * pp.out_ld] = inter_value(v);
         }
       }
     }
@@ -190,8 +296,8 @@ __device__ __forceinline__ void epilogue_columns(const GemmParams& p, const Unit
     const int col = (2 * ui.pair + tile) * 128 + row;
     float osc = gsc;
     if (p.post_norm_w != nullptr) osc *= 1.0f + __bfloat162float(p.post_norm_w[col]);
-    float* outp = static_cast<float*>(p.outp) + static_cast<size_t>(ui.row0) * p.out_ld + col;
-    __nv_bfloat16* outb = static_cast<__nv_bfloat16*>(p.outp) + static_cast<size_t>(ui.row0) * p.out_ld + col;
+    float* outp = static_cast<float*>(pp.outp) + static_cast<size_t>(ui.row0) * pp.out_ld + col;
+    __nv_bfloat16* outb = static_cast<__nv_bfloat16*>(pp.outp) + static_cast<size_t>(ui.row0) * pp.out_ld + col;
     for (int c0 = c_beg; c0 < c_end; c0 += 32) {
       if (c0 >= ui.rows) break;
       uint32_t r[32];
@@ -200,30 +306,130 @@ __device__ __forceinline__ void epilogue_columns(const GemmParams& p, const Unit
       if (p.y_bf16) {   // wide token tiles: y rows in BF16, as the reference's wide-tile build keeps them
 #pragma unroll
         for (int j = 0; j < 32; ++j)
-          if (c0 + j < ui.rows) outb[static_cast<size_t>(c0 + j) * p.out_ld] = __float2bfloat16_rn(__uint_as_float(r[j]) * osc);
+          if (c0 + j < ui.rows) outb[static_cast<size_t>(c0 + j) * pp.out_ld] = __float2bfloat16_rn(__uint_as_float(r[j]) * osc);
       } else {
 #pragma unroll
         for (int j = 0; j < 32; ++j)
-          if (c0 + j < ui.rows) outp[static_cast<size_t>(c0 + j) * p.out_ld] = __uint_as_float(r[j]) * osc;
+          if (c0 + j < ui.rows) outp[static_cast<size_t>(c0 + j) * pp.out_ld] = __uint_as_float(r[j]) * osc;
       }
     }
   }
 }
 
-template <int N, int PHASE>
+// Folded combine (phase 1, fold): out[t] = bf16( sum over the token's local slots, in slot order, of
+// w[t,s] * norm_s * y[inv[t,s]] ), norm_s = rsqrt(mean(y^2) + eps) with the post-expert norm, else 1
+// (muse_moe_w4a16/cuda/moe.cu:2604-2766). Run by all threads of the CTA that retired the token's
+// last base unit, after its own units are done. The rows come from other CTAs: they are read with
+// L2 loads after the ticket that ordered them. Sums of squares: per-thread partials in a fixed column
+// order, a fixed shuffle tree, then the warp partials in warp order.
+__device__ __noinline__ void fold_combine_token(const GemmParams& p, int t, float* red /* [GEMM_THREADS / 32][MAX_TOP_K] */) {
+  constexpr int NW = GEMM_THREADS / 32;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int H = p.ph[1].out_ld, k = p.top_k, n4 = H / 4;
+  const float* y = static_cast<const float*>(p.ph[1].outp);
+  int q[MAX_TOP_K];
+  float wgt[MAX_TOP_K];
+  int nv = 0;
+#pragma unroll
+  for (int s = 0; s < MAX_TOP_K; ++s) {   // squeeze out the slots without a local expert, keeping their order
+    q[s] = 0;
+    wgt[s] = 0.f;
+  }
+#pragma unroll
+  for (int s = 0; s < MAX_TOP_K; ++s) {
+    if (s < k) {
+      const int qq = __ldcg(p.inv + t * k + s);
+      if (qq >= 0) {
+        const float w = __ldcg(p.tw + t * k + s);
+#pragma unroll
+        for (int j = 0; j < MAX_TOP_K; ++j)
+          if (j == nv) { q[j] = qq; wgt[j] = w; }
+        ++nv;
+      }
+    }
+  }
+  if (p.post_norm_w != nullptr) {
+#pragma unroll
+    for (int s = 0; s < MAX_TOP_K; ++s) {
+      if (s < nv) {
+        const float4* row = reinterpret_cast<const float4*>(y + static_cast<size_t>(q[s]) * H);
+        float ss = 0.f;
+        for (int i = tid; i < n4; i += GEMM_THREADS) {
+          const float4 f = __ldcg(row + i);
+          ss += f.x * f.x + f.y * f.y + f.z * f.z + f.w * f.w;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (lane == 0) red[warp * MAX_TOP_K + s] = ss;
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int s = 0; s < MAX_TOP_K; ++s) {
+      if (s < nv) {
+        float tot = 0.f;
+        for (int w = 0; w < NW; ++w) tot += red[w * MAX_TOP_K + s];  // fixed order
+        wgt[s] *= rsqrtf(tot / static_cast<float>(H) + p.eps);
+      }
+    }
+    __syncthreads();  // red is reused by the next token
+  }
+  for (int i = tid; i < n4; i += GEMM_THREADS) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int s = 0; s < MAX_TOP_K; ++s) {  // slot order
+      if (s < nv) {
+        const float4 f = __ldcg(reinterpret_cast<const float4*>(y + static_cast<size_t>(q[s]) * H) + i);
+        acc.x += f.x * wgt[s]; acc.y += f.y * wgt[s]; acc.z += f.z * wgt[s]; acc.w += f.w * wgt[s];
+      }
+    }
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
+    uint2 pk;
+    pk.x = *reinterpret_cast<const uint32_t*>(&lo);
+    pk.y = *reinterpret_cast<const uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(p.out + static_cast<size_t>(t) * H + static_cast<size_t>(i) * 4) = pk;
+  }
+}
+
+// Bounded wait until a grid-wide counter has reached `target` (MODE 2). Called by one lane.
+__device__ __forceinline__ bool grid_counter_wait(const unsigned int* ctr, unsigned int target, volatile int* abort_word) {
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t polls = 0;
+  while (true) {
+    unsigned int v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(ctr) : "memory");
+    if (v >= target) return true;
+    __nanosleep(64);
+    if ((++polls & 15u) == 0u) {
+      if (*abort_word != 0) return false;
+      if (globaltimer_ns() - t0 > MSK_WAIT_LIMIT_NS) {
+        *abort_word = 1;
+        return false;
+      }
+    }
+  }
+}
+
+template <int N, int MODE>
 __global__ void __launch_bounds__(GEMM_THREADS, 1) moe_gemm_kernel(const __grid_constant__ GemmParams p) {
   using C = GemmCfg<N>;
   constexpr int NST = C::NST;
   constexpr int NSLOT = C::NSLOT;
   constexpr int NDBUF = C::NDBUF;
+  constexpr int PH_FIRST = MODE == 1 ? 1 : 0, PH_LAST = MODE == 0 ? 0 : 1;
+  constexpr bool FUSED = MODE == 2;
+  static_assert(!(FUSED && (C::TMA_B || NDBUF == 1)), "the one-launch mode is built for the narrow token tiles");
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* ring = smem;                                        // NST x [tile g0 | tile g1 | B]
   GemmCtrl& ctl = *reinterpret_cast<GemmCtrl*>(smem + NST * C::STAGE_BYTES + C::LUT_BYTES);
   int* tile_start = reinterpret_cast<int*>(smem + NST * C::STAGE_BYTES + C::LUT_BYTES + C::CTRL_BYTES);
+  int* cnt_s = tile_start + C::TABLE_INTS;
+  int* off_s = cnt_s + C::TABLE_INTS;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int nst_total = p.K / KS;                      // K stages of the whole reduction
-  const int per_split = (nst_total + p.splits - 1) / p.splits;
+  const bool routed_here = PH_FIRST == 0 && p.route != 0;
+  const bool fold = PH_LAST == 1 && p.fold != 0;
+  const unsigned int n_ctas = gridDim.x;
 
   // ---------------------------------------------------------------- set-up
   if (tid == 0) {
@@ -247,6 +453,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) moe_gemm_kernel(const __grid_
     mbar_init(&ctl.epi_bar, 128);
     ctl.abort_word = 0;
     ctl.last_flag = 0;
+    ctl.fin_n = 0;
     fence_mbar_init();
   }
   if (warp == 1) {
@@ -254,18 +461,66 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) moe_gemm_kernel(const __grid_
     tmem_relinquish();
   }
   // Programmatic dependent launch: everything above ran while the previous kernel was still
-  // draining. PHASE 0 reads the sort tables next, so it waits here. PHASE 1 is launched behind
-  // PHASE 0, which itself only passed this point after the sort had completed, so the tables
-  // are already final: only the activation gather (inter rows) waits, and the weight stream,
-  // dequant and TMEM ring of the down GEMM fill up during the tail of the gate/up GEMM.
-  if (PHASE == 0) pdl_wait();
+  // draining. What a launch may read before the previous grid has completed:
+  //  * MODE 0 behind a sort kernel (route == 0) reads that kernel's tables next, so it waits here.
+  //  * MODE 0 that routes itself (route != 0) is launched behind the kernel that makes the F16 copy
+  //    of the token rows. That kernel triggers its dependents only after its own wait, so whatever
+  //    precedes it (the producer of logits / ids) has completed: routing starts at once, and only
+  //    the activation gather waits (for the F16 rows).
+  //  * MODE 1 is launched behind MODE 0, which triggers its dependents only once the tables are
+  //    final (written by its CTA 0, or by the sort kernel it waited for): only the activation gather
+  //    (inter rows) and the epilogue wait, and the weight stream, dequant and TMEM ring of the down
+  //    GEMM fill up during the tail of the gate/up GEMM.
+  //  * MODE 2 is the whole step: it reads its inputs next, so it waits here.
+  if ((MODE == 0 && p.route == 0) || FUSED) pdl_wait();
+  if (FUSED) {
+    // F16 copy of the token rows, a slice per CTA; the gather warps wait for all slices (stage 1 of
+    // the grid counter) before their first read
+    const int n8 = p.T * (p.ph[0].K / 8);
+    const uint4* src = reinterpret_cast<const uint4*>(p.x_bf16);
+    uint4* dst = reinterpret_cast<uint4*>(const_cast<void*>(p.ph[0].act));
+    for (int i = static_cast<int>(blockIdx.x) * GEMM_THREADS + tid; i < n8; i += static_cast<int>(n_ctas) * GEMM_THREADS) {
+      const uint4 v = src[i];
+      dst[i] = make_uint4(bf16x2_to_f16x2(v.x), bf16x2_to_f16x2(v.y), bf16x2_to_f16x2(v.z), bf16x2_to_f16x2(v.w));
+    }
+    __threadfence();
+  }
+  if (routed_here) {
+    // top-k (route 1) or the given ids (route 2), then the stable sort, redundantly in every CTA; the
+    // scratch lives in the ring, which nothing has written yet
+    SmallSortScratch& sc = *reinterpret_cast<SmallSortScratch*>(ring);
+    const int n_entries = p.T * p.top_k;
+    if (p.route == 1) {
+      for (int t = warp; t < p.T; t += GEMM_THREADS / 32)
+        route_token_dispatch(p.logits + static_cast<size_t>(t) * p.E, p.bias, sc.ids + t * p.top_k,
+                             sc.tw + t * p.top_k, p.E, p.top_k, p.mode, p.route_scale, lane);
+    } else {
+      for (int i = tid; i < n_entries; i += GEMM_THREADS) sc.ids[i] = p.ids_in[i];
+    }
+    __syncthreads();
+    const bool writer = blockIdx.x == 0;
+    if (writer && p.route == 1) {
+      for (int i = tid; i < n_entries; i += GEMM_THREADS) {
+        p.ids_out[i] = sc.ids[i];
+        p.tw_out[i] = sc.tw[i];
+      }
+    }
+    sort_small_cta(sc, n_entries, p.lo, p.nloc, cnt_s, off_s, ctl.perm8, writer || FUSED, p.cnt, p.off, p.perm, p.inv);
+    if (writer) __threadfence();  // the tables are in global memory before the dependent grid is let go
+    fence_proxy_async_smem();     // the ring is handed to the bulk copies
+    __syncthreads();
+    if (tid == 0) MSK_TR(TR_ROUTED);
+  }
   pdl_launch_dependents();
   if (warp == 2) {  // exclusive prefix of per-expert tile counts
     int carry = 0;
     for (int base = 0; base < p.nloc; base += 32) {
       const int e = base + lane;
-      const int cn = e < p.nloc ? p.cnt[e] : 0;
-      if (e < p.nloc) tile_start[C::TABLE_INTS + e] = cn;
+      int cn = 0;
+      if (e < p.nloc) {
+        cn = routed_here ? cnt_s[e] : __ldcg(p.cnt + e);
+        if (!routed_here) cnt_s[e] = cn;
+      }
       const int c = (cn + N - 1) / N;
       int incl = c;
 #pragma unroll
@@ -281,17 +536,46 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) moe_gemm_kernel(const __grid_
       ctl.n_tiles = carry;
     }
   }
-  if (warp == 3) {  // off[] copy, in parallel with the scan above
-    for (int e = lane; e <= p.nloc; e += 32) tile_start[2 * C::TABLE_INTS + e] = p.off[e];
+  if (warp == 3 && !routed_here) {  // off[] copy, in parallel with the scan above
+    for (int e = lane; e <= p.nloc; e += 32) off_s[e] = __ldcg(p.off + e);
+  }
+  if (fold && warp >= 4 && warp < 4 + SMALL_SORT_WARPS) {
+    // the entry index of every sorted row and each token's number of local routes. In MODE 2 this CTA
+    // has just sorted: inv is its own write to global memory; in MODE 1 it is the previous grid's.
+    const int i = (warp - 4) * 32 + lane;
+    const int n_entries = p.T * p.top_k;
+    if (!FUSED) {
+      const int qq = i < n_entries ? __ldcg(p.inv + i) : -1;
+      if (qq >= 0) ctl.perm8[qq] = static_cast<uint8_t>(i);
+    }
+    if (i < p.T) {
+      int kl = 0;
+      for (int s = 0; s < p.top_k; ++s) kl += __ldcg(p.inv + i * p.top_k + s) >= 0 ? 1 : 0;
+      ctl.klocal[i] = static_cast<uint8_t>(kl);
+      // a token without any local route is nobody's to finish: its output row is zero
+      if (kl == 0 && static_cast<int>(blockIdx.x) == i % static_cast<int>(n_ctas)) {
+        uint4* orow = reinterpret_cast<uint4*>(p.out + static_cast<size_t>(i) * p.ph[1].out_ld);
+        for (int j = 0; j < p.ph[1].out_ld / 8; ++j) orow[j] = make_uint4(0u, 0u, 0u, 0u);
+      }
+    }
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  if (FUSED && tid == 0) atomicAdd(p.grid_bar, 1u);  // stage 1: this CTA's slice of the F16 rows is in memory
 
   const uint32_t tmem = ctl.tmem_base;
   if (tid == 0) MSK_TR(TR_SETUP);
-  const int n_units = ctl.n_tiles * p.n_pairs * p.splits;
+  const int iter_mode = N >= 128 ? 0 : (p.flat ? 2 : 1);
   volatile int* abortw = &ctl.abort_word;
+#define MSK_PHASES for (int phase = PH_FIRST; phase <= PH_LAST; ++phase)
+#define MSK_PHASE_SETUP                                                                                           \
+  const PhaseParams& pp = p.ph[phase];                                                                            \
+  const int nst_total = pp.K / KS;                                                                                \
+  const int n_base = ctl.n_tiles * pp.n_pairs;                                                                    \
+  PieceIter pieces = make_piece_iter(iter_mode, n_base, nst_total, static_cast<int>(blockIdx.x), static_cast<int>(n_ctas)); \
+  int base, ks0, ks1;                                                                                             \
+  (void)n_base
 
   if (warp == 0) {
 #include "gemm_producer.inl"
@@ -304,12 +588,29 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) moe_gemm_kernel(const __grid_
   } else {
 #include "gemm_epilogue.inl"
   }
+#undef MSK_PHASES
+#undef MSK_PHASE_SETUP
 
   // -------------------------------------------------------------- teardown
   __syncwarp();
   tc_fence_before();
   __syncthreads();
+  if (fold && ctl.abort_word == 0) {
+    // the tokens whose last base unit this CTA retired (the ring is free by now: scratch for the sums)
+    float* red = reinterpret_cast<float*>(ring);
+    const int nf = ctl.fin_n;
+    for (int j = 0; j < nf; ++j) fold_combine_token(p, ctl.fin_tok[j], red);
+    if (tid == 0) MSK_TR(TR_FOLD_END);
+  }
   if (tid == 0) MSK_TR(TR_END);
+  if (FUSED && tid == 0 && ctl.abort_word == 0) {
+    // the last CTA to leave puts the grid counters back to zero for the next launch
+    const unsigned int old = atomicAdd(p.grid_bar + 1, 1u);
+    if (old == n_ctas - 1u) {
+      atomicExch(p.grid_bar, 0u);
+      atomicExch(p.grid_bar + 1, 0u);
+    }
+  }
   if (ctl.abort_word != 0) {
     // give copies still in flight time to land before shared memory and TMEM are released
     const uint64_t t0 = globaltimer_ns();

@@ -24,69 +24,72 @@
       pending = false;
     };
     uint32_t unit_i = 0;
-    for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x, ++unit_i) {
-      const UnitInfo ui = decode_unit(u, tile_start, p, N);
-      const int ks0 = ui.split * per_split, ks1 = min(nst_total, ks0 + per_split);
-      for (int ks = ks0; ks < ks1 && ok; ++ks, ++it) {
-        const uint32_t slot = it % NST, par = (it / NST) & 1u;
-        if (!mbar_wait(&ctl.raw_full[slot], par, abortw)) { ok = false; break; }
-        if (it == 0 && tid == 256) MSK_TR(TR_FIRST_RAW);
-        if (tid == 256) MSK_TRD(0, tri, 1);
-        const uint32_t tile = smem_u32(ring + slot * C::STAGE_BYTES + g * TILE_BYTES);
-        const uint32_t tile_row = tile + row * 16;
-        uint32_t sfa[4];
-        asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
-                     : "=r"(sfa[0]), "=r"(sfa[1]), "=r"(sfa[2]), "=r"(sfa[3])
-                     : "r"(tile + TILE_CODE_BYTES + row * 16));
-        {
-          // this warp's slot of the stage: K half kh = chunks 4*kh .. 4*kh+3
+    MSK_PHASES {
+      MSK_PHASE_SETUP;
+      for (; ok && pieces.next(base, ks0, ks1); ++unit_i) {
+        const UnitInfo ui = decode_unit(base, tile_start, pp.n_pairs, p.nloc, N);
+        for (int ks = ks0; ks < ks1 && ok; ++ks, ++it) {
+          const uint32_t slot = it % NST, par = (it / NST) & 1u;
+          if (!mbar_wait(&ctl.raw_full[slot], par, abortw)) { ok = false; break; }
+          if (it == 0 && tid == 256) MSK_TR(TR_FIRST_RAW);
+          if (tid == 256) MSK_TRD(0, tri, 1);
+          const uint32_t tile = smem_u32(ring + slot * C::STAGE_BYTES + g * TILE_BYTES);
+          const uint32_t tile_row = tile + row * 16;
+          uint32_t sfa[4];
+          asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                       : "=r"(sfa[0]), "=r"(sfa[1]), "=r"(sfa[2]), "=r"(sfa[3])
+                       : "r"(tile + TILE_CODE_BYTES + row * 16));
+          {
+            // this warp's slot of the stage: K half kh = chunks 4*kh .. 4*kh+3
 #pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            const int chunk = kh * 4 + c;
-            uint32_t q[4];
-            asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
-                         : "=r"(q[0]), "=r"(q[1]), "=r"(q[2]), "=r"(q[3])
-                         : "r"(tile_row + chunk * 2048));
-            const uint32_t sfw = kh ? (c < 2 ? sfa[2] : sfa[3]) : (c < 2 ? sfa[0] : sfa[1]);
-            uint32_t o[16];
-            decode_chunk(q, (c & 1) ? (sfw >> 16) : sfw, o);
-            if (c == 0) {
-              // hand over the previous slot (its stores had the decode above to land), claim this one
-              if (pending) retire();
-              if (!mbar_wait(&ctl.a_empty[g][as], apar ^ 1u, abortw)) { ok = false; break; }
-              tc_fence_after();
+            for (int c = 0; c < 4; ++c) {
+              const int chunk = kh * 4 + c;
+              uint32_t q[4];
+              asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                           : "=r"(q[0]), "=r"(q[1]), "=r"(q[2]), "=r"(q[3])
+                           : "r"(tile_row + chunk * 2048));
+              const uint32_t sfw = kh ? (c < 2 ? sfa[2] : sfa[3]) : (c < 2 ? sfa[0] : sfa[1]);
+              uint32_t o[16];
+              decode_chunk(q, (c & 1) ? (sfw >> 16) : sfw, o);
+              if (c == 0) {
+                // hand over the previous slot (its stores had the decode above to land), claim this one
+                if (pending) retire();
+                if (!mbar_wait(&ctl.a_empty[g][as], apar ^ 1u, abortw)) { ok = false; break; }
+                tc_fence_after();
+              }
+              tmem_st16(a_tmem + as * C::SLOT_COLS + c * 16, o);
             }
-            tmem_st16(a_tmem + as * C::SLOT_COLS + c * 16, o);
+            if (!ok) break;
+            pending = true;
+            pending_slot = as;
+            if (it == 0 && tid == 256) MSK_TR(TR_FIRST_AFULL);
+            // the other K half takes the next ring slot; this warp's next one is two further
+            as += 2;
+            if (as >= NSLOT) { as -= NSLOT; apar ^= 1u; }
           }
           if (!ok) break;
-          pending = true;
-          pending_slot = as;
-          if (it == 0 && tid == 256) MSK_TR(TR_FIRST_AFULL);
-          // the other K half takes the next ring slot; this warp's next one is two further
-          as += 2;
-          if (as >= NSLOT) { as -= NSLOT; apar ^= 1u; }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&ctl.raw_empty[slot]);
         }
         if (!ok) break;
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&ctl.raw_empty[slot]);
+        if (pending) retire();  // the accumulators need every slot of the piece
+        if (NDBUF == 1) {
+          // single accumulator buffer: the main loop cannot go on until it is drained, so all sixteen
+          // dequant warps drain it together. The four warps of a lane quarter split the columns.
+          if (!mbar_wait(&ctl.d_full[0], unit_i & 1u, abortw)) { ok = false; break; }
+          tc_fence_after();
+          if (tid == 256) { if (unit_i == 0) MSK_TR(TR_FIRST_DFULL); MSK_TR(TR_LAST_DFULL); }
+          if (phase == 0) {
+            const int part = kh * 2 + g;  // 0..3: a quarter of the token columns, gate and up of this lane
+            epilogue_columns<N>(p, pp, phase, ui, tmem + lane_base, row, part * (N / 4), (part + 1) * (N / 4), 0);
+          } else {
+            epilogue_columns<N>(p, pp, phase, ui, tmem + lane_base, row, kh * (N / 2), (kh + 1) * (N / 2), g);
+          }
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&ctl.d_empty[0]);
+          if (tid == 256 && unit_i == 0) MSK_TR(TR_FIRST_EPI_DONE);
+        }
       }
       if (!ok) break;
-      if (pending) retire();  // the accumulators need every slot of the unit
-      if (NDBUF == 1) {
-        // single accumulator buffer: the main loop cannot go on until it is drained, so all sixteen
-        // dequant warps drain it together. The four warps of a lane quarter split the columns.
-        if (!mbar_wait(&ctl.d_full[0], unit_i & 1u, abortw)) { ok = false; break; }
-        tc_fence_after();
-        if (tid == 256) { if (unit_i == 0) MSK_TR(TR_FIRST_DFULL); MSK_TR(TR_LAST_DFULL); }
-        if (PHASE == 0) {
-          const int part = kh * 2 + g;  // 0..3: a quarter of the token columns, gate and up of this lane
-          epilogue_columns<N, PHASE>(p, ui, tmem + lane_base, row, part * (N / 4), (part + 1) * (N / 4), 0);
-        } else {
-          epilogue_columns<N, PHASE>(p, ui, tmem + lane_base, row, kh * (N / 2), (kh + 1) * (N / 2), g);
-        }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&ctl.d_empty[0]);
-        if (tid == 256 && unit_i == 0) MSK_TR(TR_FIRST_EPI_DONE);
-      }
     }

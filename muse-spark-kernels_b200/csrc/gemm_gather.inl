@@ -1,6 +1,6 @@
 // Role body of moe_gemm_kernel (included inside the kernel): activation gather, warp 2.
-// Copies the token rows of the unit (x rows through the permutation for PHASE 0, sorted inter
-// rows for PHASE 1) with 16-byte cp.async into the K-major core-matrix layout of the B operand:
+// Copies the token rows of the piece (x rows through the permutation for phase 0, sorted inter
+// rows for phase 1) with 16-byte cp.async into the K-major core-matrix layout of the B operand:
 // element (n, k) at (n/8)*B_SBO + (k/8)*B_LBO + (n%8)*16 + (k%8)*2. Eight lanes write one
 // 128-byte core matrix, so shared-memory writes are conflict free. A stage is published a few
 // stages late, once its copies have landed and a proxy fence has ordered them before the
@@ -12,53 +12,73 @@
     constexpr int GLAG = NST >= 5 ? 3 : (NST >= 4 ? 2 : 1);
     uint32_t it = 0, signalled = 0;
     const uint64_t keep = policy_evict_last();  // token rows are re-read by every pair of the expert
-    if (PHASE == 1) pdl_wait();  // inter is written by the gate/up GEMM
     bool ok = true;
-    const size_t act_ld = static_cast<size_t>(p.K);
-    for (int u = blockIdx.x; u < n_units && ok; u += gridDim.x) {
-      const UnitInfo ui = decode_unit(u, tile_start, p, N);
-      const int ks0 = ui.split * per_split, ks1 = min(nst_total, ks0 + per_split);
-      // source row of token n = ng*8 + n_sub, for every 8-group ng
-      const __half* src[N / 8];
-#pragma unroll
-      for (int ng = 0; ng < N / 8; ++ng) {
-        const int n = ng * 8 + n_sub;
-        src[ng] = nullptr;
-        if (n < ui.rows) {
-          const int r = ui.row0 + n;
-          const size_t row = PHASE == 0 ? static_cast<size_t>(p.perm[r] / p.top_k) : static_cast<size_t>(r);
-          src[ng] = static_cast<const __half*>(p.act) + row * act_ld;
-        }
+    // everything issued so far has landed: publish it
+    auto drain = [&]() {
+      if (signalled < it) {
+        cp_async_wait<0>();
+        fence_proxy_async_smem();
+        __syncwarp();
+        for (; signalled < it; ++signalled)
+          if (lane == 0) mbar_arrive(&ctl.b_full[signalled % NST]);
       }
-      for (int ks = ks0; ks < ks1; ++ks, ++it) {
-        const uint32_t slot = it % NST, par = (it / NST) & 1u;
-        if (!mbar_wait(&ctl.b_empty[slot], par ^ 1u, abortw)) { ok = false; break; }
-        uint8_t* dstB = ring + slot * C::STAGE_BYTES + 2 * TILE_BYTES;
+    };
+    MSK_PHASES {
+      MSK_PHASE_SETUP;
+      // What the rows of this phase wait for. Two launches: inter is written by the gate/up GEMM, and the
+      // F16 token rows, when the gate/up kernel routes itself, by the row-copy kernel launched in front
+      // of it. One launch: every CTA's slice of the F16 rows (stage 1 of the grid counter), then every
+      // CTA's rows of inter (stage 2).
+      if (FUSED) {
+        drain();
+        int go = 1;
+        if (lane == 0) go = grid_counter_wait(p.grid_bar, (phase + 1) * n_ctas, abortw) ? 1 : 0;
+        go = __shfl_sync(0xffffffffu, go, 0);
+        if (!go) { ok = false; break; }
+      } else if (MODE == 1 || routed_here) {
+        pdl_wait();
+      }
+      const size_t act_ld = static_cast<size_t>(pp.K);
+      while (ok && pieces.next(base, ks0, ks1)) {
+        const UnitInfo ui = decode_unit(base, tile_start, pp.n_pairs, p.nloc, N);
+        // source row of token n = ng*8 + n_sub, for every 8-group ng
+        const __half* src[N / 8];
 #pragma unroll
         for (int ng = 0; ng < N / 8; ++ng) {
-          const bool valid = src[ng] != nullptr;
-          const __half* s = valid ? src[ng] + static_cast<size_t>(ks) * KS : static_cast<const __half*>(p.act);
-#pragma unroll
-          for (int cg = 0; cg < 8; ++cg) {
-            const int chunk = cg * 4 + c_sub;
-            cp_async16_hint(dstB + ng * B_SBO + chunk * B_LBO + n_sub * 16, s + chunk * 8, valid, keep);
+          const int n = ng * 8 + n_sub;
+          src[ng] = nullptr;
+          if (n < ui.rows) {
+            const int r = ui.row0 + n;
+            size_t row = static_cast<size_t>(r);
+            if (phase == 0) row = static_cast<size_t>((routed_here ? static_cast<int>(ctl.perm8[r]) : p.perm[r]) / p.top_k);
+            src[ng] = static_cast<const __half*>(pp.act) + row * act_ld;
           }
         }
-        cp_async_commit();
-        if (it + 1 - signalled > GLAG) {
-          cp_async_wait<GLAG>();
-          fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&ctl.b_full[signalled % NST]);
-          ++signalled;
+        for (int ks = ks0; ks < ks1; ++ks, ++it) {
+          const uint32_t slot = it % NST, par = (it / NST) & 1u;
+          if (!mbar_wait(&ctl.b_empty[slot], par ^ 1u, abortw)) { ok = false; break; }
+          uint8_t* dstB = ring + slot * C::STAGE_BYTES + 2 * TILE_BYTES;
+#pragma unroll
+          for (int ng = 0; ng < N / 8; ++ng) {
+            const bool valid = src[ng] != nullptr;
+            const __half* s = valid ? src[ng] + static_cast<size_t>(ks) * KS : static_cast<const __half*>(pp.act);
+#pragma unroll
+            for (int cg = 0; cg < 8; ++cg) {
+              const int chunk = cg * 4 + c_sub;
+              cp_async16_hint(dstB + ng * B_SBO + chunk * B_LBO + n_sub * 16, s + chunk * 8, valid, keep);
+            }
+          }
+          cp_async_commit();
+          if (it + 1 - signalled > GLAG) {
+            cp_async_wait<GLAG>();
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&ctl.b_full[signalled % NST]);
+            ++signalled;
+          }
         }
       }
+      if (!ok) break;
     }
-    if (signalled < it) {
-      cp_async_wait<0>();
-      fence_proxy_async_smem();
-      __syncwarp();
-      for (; signalled < it; ++signalled)
-        if (lane == 0) mbar_arrive(&ctl.b_full[signalled % NST]);
-    }
+    drain();
     }

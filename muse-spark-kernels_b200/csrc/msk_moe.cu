@@ -170,6 +170,21 @@ __global__ void __launch_bounds__(256) gather_rows_kernel(const __nv_bfloat16* _
   }
 }
 
+// xh = f16(x), one 16-byte chunk per thread, in small blocks: the row copy in front of a gate/up
+// kernel that routes itself (few tokens). It waits for whatever precedes the step, then lets its
+// dependents start: the gate/up kernel's prologue (routing, sort) overlaps this copy and only its
+// activation gather waits for it.
+__global__ void __launch_bounds__(64) convert_rows_kernel(const __nv_bfloat16* __restrict__ x, __half* __restrict__ xh,
+                                                          int n_chunks) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int i = blockIdx.x * 64 + threadIdx.x;
+  if (i >= n_chunks) return;
+  const uint4 v = reinterpret_cast<const uint4*>(x)[i];
+  reinterpret_cast<uint4*>(xh)[i] =
+      make_uint4(bf16x2_to_f16x2(v.x), bf16x2_to_f16x2(v.y), bf16x2_to_f16x2(v.z), bf16x2_to_f16x2(v.w));
+}
+
 // ---------------------------------------------------------------- combine
 // One block per token: out[t] = bf16( sum over slots in index order of
 // w[t,s] * norm_s * y[inv[t,s]] ), norm_s = rsqrt(mean(y^2) + eps) when the post-expert
@@ -447,31 +462,19 @@ static int sm_count() {
   return cached[dev];
 }
 
+// Persistent grid when the caller names none: the SM count of a B200. A constant, so that the
+// shares of the weight stream (and with them the order in which a cut unit's pieces are summed)
+// depend on the configuration, not on the device the library happens to run on.
+constexpr int DEFAULT_CTAS = 148;
+constexpr int MAX_CTAS = 512;
+constexpr int FLAT_MAX_ROWS = SMALL_SORT_MAX_ENTRIES;  // up to here the weight stream is cut into equal shares
+
 struct Plan {
   int N;         // token tile
-  int s13, s2;   // K splits
+  int path;      // 0 one launch, 1 chain of launches, 2 row copy + routing gate/up kernel + combining down kernel
+  int flat;      // equal shares of the flat (base unit, K stage) list
   int grid;
 };
-
-// Expected number of token tiles for T tokens spread uniformly over the local experts.
-static double expected_tiles(const MskMoeCfg* c, int T, int N) {
-  const double routes = static_cast<double>(T) * c->top_k * c->local_count / c->n_experts;
-  const double active = c->local_count * (1.0 - std::pow(1.0 - 1.0 / c->local_count, routes));
-  return std::max(active, routes / N);
-}
-
-static int pick_split(double units, int n_stages, int grid) {
-  int best = 1;
-  double best_cost = 1e30;
-  for (int s = 1; s <= std::min(n_stages, 8); ++s) {
-    const double waves = std::ceil(units * s / grid);
-    // per wave: the K stages of one unit plus a switch cost (the epilogue overlaps the next unit), in
-    // stage times; splitting adds the partial stores per unit and one ticket round trip at the end
-    const double cost = waves * (std::ceil(static_cast<double>(n_stages) / s) + 0.5 + (s > 1 ? 0.3 : 0.0)) + (s > 1 ? 2.0 : 0.0);
-    if (cost < best_cost - 1e-9) { best_cost = cost; best = s; }
-  }
-  return best;
-}
 
 // Few-token kernel: piece slots per output element. A share of the flat stage-tile list holds at
 // least `per` stage tiles, so a tile of nst stages meets at most ceil(nst / per) + 1 shares,
@@ -520,11 +523,12 @@ static bool small_fits(const MskMoeCfg* c, int T, int grid) {
 
 static Plan make_plan(const MskMoeCfg* c, int T) {
   Plan p;
-  p.grid = c->num_ctas > 0 ? c->num_ctas : sm_count();
-  // on request only: at 1 to 8 tokens the chain of launches below is still the faster one
+  p.grid = c->num_ctas > 0 ? std::min(c->num_ctas, MAX_CTAS) : DEFAULT_CTAS;
+  p.path = 1;
+  p.flat = 0;
+  // on request only: the mma.sync single-launch kernel for up to 8 tokens
   if (c->token_tile == 8 && small_fits(c, T, p.grid)) {
-    p.N = 8;  // the few-token kernel
-    p.s13 = p.s2 = 1;
+    p.N = 8;
     return p;
   }
   if (c->token_tile > 0) {
@@ -536,43 +540,39 @@ static Plan make_plan(const MskMoeCfg* c, int T) {
     // same up to 64 tokens (the weight decode bounds it), so past a few rows per expert wider is better
     p.N = rpe <= 8 ? 16 : rpe <= 12 ? 32 : rpe <= 32 ? 64 : 128;
   }
-  const double tiles = expected_tiles(c, T, p.N);
-  p.s13 = c->split_k13 > 0 ? c->split_k13 : pick_split(tiles * (c->inter / 128), c->hidden / KS, p.grid);
-  p.s2 = c->split_k2 > 0 ? c->split_k2 : pick_split(tiles * (c->hidden / 256), c->inter / KS, p.grid);
-  p.s13 = std::min(p.s13, c->hidden / KS);
-  p.s2 = std::min(p.s2, c->inter / KS);
-  if (p.N >= 128) p.s13 = p.s2 = 1;  // the single-buffered wide tile has no split-K epilogue (and no use for one)
+  const long long rows = static_cast<long long>(T) * c->top_k;
+  p.flat = (rows <= FLAT_MAX_ROWS && p.N <= 64) ? 1 : 0;
+  // few tokens: the kernels route, sort and combine themselves
+  const bool few = rows <= SMALL_SORT_MAX_ENTRIES && T <= FOLD_MAX_TOKENS && p.N <= 32 && c->stop_after == 0;
+  if (few) {
+    p.path = c->decode_path == 1 ? 1 : (c->decode_path == 2 ? 2 : 0);
+    if (p.path == 0 && p.grid > sm_count()) p.path = 2;  // the one-launch kernel needs every CTA resident
+  }
   return p;
 }
 
 // Workspace carving. Everything is sized for max_tokens with the worst plan.
 struct Carve {
-  size_t status, trace, cnt, off, perm, inv, tickets, small_ctl, sort_blk, inter, y, partial, xs, small_part, total;
+  size_t status, trace, cnt, off, perm, inv, tickets, small_ctl, few_ctl, sort_blk, inter, y, partial, xs, small_part, total;
 };
-constexpr size_t MAX_SPLIT = 8;
 constexpr size_t TRACE_CTAS = 256;
 constexpr size_t TRACE_WORDS = TRACE_CTAS * 16 + 3 * 256;
 
 static size_t max_tiles(const MskMoeCfg* c, int T) {
-  // ceil(cnt/16) summed over experts <= R/16 + local_count
+  // ceil(cnt/16) summed over experts <= R/16 + (experts that can hold a row)
   const size_t R = static_cast<size_t>(T) * c->top_k;
-  return R / 16 + c->local_count;
+  return R / 16 + std::min(static_cast<size_t>(c->local_count), R);
 }
 
-static size_t partial_floats(const MskMoeCfg* c, int T) {
-  // split-K is only planned while it pays: bounded by the units of a 4-wave launch; beyond
-  // that make_plan picks 1. Size for the largest product (base units * splits * 2 * 128 * N)
-  // any plan can ask for.
-  size_t worst = 0;
-  const int Ns[4] = {16, 32, 64, 128};
-  for (int N : Ns) {
-    const size_t tiles = static_cast<size_t>(T) * c->top_k / N + c->local_count;
-    const size_t pairs = std::max(c->inter / 128, c->hidden / 256);
-    worst = std::max(worst, tiles * pairs * MAX_SPLIT * 2 * 128 * static_cast<size_t>(N));
-  }
-  // cap: a launch with that many units never splits (pick_split sees many waves)
-  const size_t cap = static_cast<size_t>(64) << 20;  // 64 Mi floats = 256 MiB
-  return std::min(worst, cap);
+// Pieces of cut units (flat shares): two slots per CTA of the largest grid, each the two accumulator
+// tiles of the widest token tile that is ever cut (64).
+static size_t partial_floats(const MskMoeCfg* c) {
+  const size_t grid = c->num_ctas > 0 ? static_cast<size_t>(std::min(c->num_ctas, MAX_CTAS)) : DEFAULT_CTAS;
+  return 2 * grid * 2 * 128 * 64;
+}
+
+static size_t ticket_ints(const MskMoeCfg* c, int T) {
+  return max_tiles(c, T) * static_cast<size_t>(std::max(c->inter / 128, c->hidden / 256));
 }
 
 static Carve carve(const MskMoeCfg* c, int T) {
@@ -585,15 +585,16 @@ static Carve carve(const MskMoeCfg* c, int T) {
   k.off = o; o += round_up(static_cast<size_t>(c->local_count + 1) * 4, 256);
   k.perm = o; o += round_up(R * 4, 256);
   k.inv = o; o += round_up(R * 4, 256);
-  const size_t pairs = std::max(c->inter / 128, c->hidden / 256);
-  k.tickets = o; o += 2 * round_up(max_tiles(c, T) * pairs * 4, 256);  // one region per GEMM
-  k.small_ctl = o; o += 1024;  // few-token kernel: grid barrier (2 words), per-token tickets at +64, row weights at +256
+  k.tickets = o; o += 2 * round_up(ticket_ints(c, T) * 4, 256);  // one region per GEMM
+  k.small_ctl = o; o += 1024;  // mma.sync few-token kernel: grid barrier (2 words), per-token tickets at +64, row weights at +256
+  k.few_ctl = o; o += 256;     // few-token paths of the GEMM kernel: token tickets [32] at +0, grid counters [2] at +128
   k.sort_blk = o; o += static_cast<size_t>(SORT_MULTI_BLOCKS) * MAX_LOCAL_EXPERTS * 4;  // per-CTA counts of the multi-CTA sort
+  // everything above is control state: msk_moe_workspace_init zeroes [0, inter)
   k.inter = o; o += round_up(R * c->inter * 2, 256);
   k.y = o; o += round_up(R * c->hidden * 4, 256);
-  k.partial = o; o += 2 * round_up(partial_floats(c, T) * 4, 256);  // one region per GEMM
-  k.xs = o; o += round_up(R * c->hidden * 2, 256);  // sorted copy of the token rows (wide token tiles only)
-  k.small_part = o; o += round_up(small_part_floats(c) * 4, 256);  // pieces of the few-token kernel
+  k.partial = o; o += 2 * round_up(partial_floats(c) * 4, 256);  // one region per GEMM
+  k.xs = o; o += round_up(R * c->hidden * 2, 256);  // F16 copy of the token rows ([T, H], or sorted [R, H] for wide token tiles)
+  k.small_part = o; o += round_up(small_part_floats(c) * 4, 256);  // pieces of the mma.sync few-token kernel
   k.total = o;
   return k;
 }
@@ -623,13 +624,16 @@ static int encode_act_map(CUtensorMap* map, const void* base, size_t rows, int K
   return r == CUDA_SUCCESS ? 0 : static_cast<int>(cudaErrorInvalidValue);
 }
 
-template <int N, int PHASE>
-static int launch_gemm(const GemmParams& p, int grid, cudaStream_t st) {
+// MODE 2 (one launch for the step) waits on a grid-wide counter, so it is launched cooperatively:
+// either every CTA is resident or the launch fails. The other modes are chained with programmatic
+// dependent launch (unless pdl == 0).
+template <int N, int MODE>
+static int launch_gemm(const GemmParams& p, int grid, cudaStream_t st, int pdl) {
   static bool attr_set[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(moe_gemm_kernel<N, PHASE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(moe_gemm_kernel<N, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          GemmCfg<N>::SMEM_BYTES);
     if (e != cudaSuccess) return static_cast<int>(e);
     attr_set[dev] = true;
@@ -640,20 +644,33 @@ static int launch_gemm(const GemmParams& p, int grid, cudaStream_t st) {
   lc.dynamicSmemBytes = GemmCfg<N>::SMEM_BYTES;
   lc.stream = st;
   cudaLaunchAttribute at[1];
-  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;  // may start while its predecessor drains
-  at[0].val.programmaticStreamSerializationAllowed = 1;
+  if (MODE == 2) {
+    at[0].id = cudaLaunchAttributeCooperative;
+    at[0].val.cooperative = 1;
+  } else {
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;  // may start while its predecessor drains
+    at[0].val.programmaticStreamSerializationAllowed = pdl ? 1 : 0;
+  }
   lc.attrs = at;
   lc.numAttrs = 1;
-  return static_cast<int>(cudaLaunchKernelEx(&lc, moe_gemm_kernel<N, PHASE>, p));
+  return static_cast<int>(cudaLaunchKernelEx(&lc, moe_gemm_kernel<N, MODE>, p));
 }
 
-template <int PHASE>
-static int launch_gemm_n(int N, const GemmParams& p, int grid, cudaStream_t st) {
+template <int MODE>
+static int launch_gemm_n(int N, const GemmParams& p, int grid, cudaStream_t st, int pdl) {
   switch (N) {
-    case 16: return launch_gemm<16, PHASE>(p, grid, st);
-    case 32: return launch_gemm<32, PHASE>(p, grid, st);
-    case 64: return launch_gemm<64, PHASE>(p, grid, st);
-    case 128: return launch_gemm<128, PHASE>(p, grid, st);
+    case 16: return launch_gemm<16, MODE>(p, grid, st, pdl);
+    case 32: return launch_gemm<32, MODE>(p, grid, st, pdl);
+    case 64: return launch_gemm<64, MODE>(p, grid, st, pdl);
+    case 128: return launch_gemm<128, MODE>(p, grid, st, pdl);
+    default: return MSK_ERR_SHAPE;
+  }
+}
+
+static int launch_gemm_fused(int N, const GemmParams& p, int grid, cudaStream_t st) {
+  switch (N) {
+    case 16: return launch_gemm<16, 2>(p, grid, st, 0);
+    case 32: return launch_gemm<32, 2>(p, grid, st, 0);
     default: return MSK_ERR_SHAPE;
   }
 }
@@ -885,7 +902,8 @@ int msk_moe_workspace_view(const MskMoeCfg* cfg, void* workspace, int which, voi
   return MSK_OK;
 }
 
-// ev, when given, holds 5 events: recorded before sort, gate/up GEMM, down GEMM, combine and after it.
+// ev, when given, holds 6 events: [0] before the step, [1] after routing + sort, [5] after the row copy,
+// [2] after the gate/up GEMM, [3] after the down GEMM, [4] after the combine.
 static int forward_impl(const MskMoeCfg* cfg, const void* packed13, const void* packed2, const float* gs13,
                         const float* gs2, const void* post_norm_w, const void* x, const int32_t* topk_ids,
                         const float* topk_weights, void* out, void* workspace, size_t workspace_bytes, int n_tokens,
@@ -958,7 +976,7 @@ static int forward_impl(const MskMoeCfg* cfg, const void* packed13, const void* 
       if (ae != cudaSuccess) return static_cast<int>(ae);
       attr_set[dev] = true;
     }
-    if (ev) { cudaEventRecord(ev[0], st); cudaEventRecord(ev[1], st); }
+    if (ev) { cudaEventRecord(ev[0], st); cudaEventRecord(ev[1], st); cudaEventRecord(ev[5], st); }
     cudaLaunchConfig_t lc{};
     lc.gridDim = dim3(static_cast<unsigned>(plan.grid));
     lc.blockDim = dim3(ST_THREADS_ALL);
@@ -974,18 +992,88 @@ static int forward_impl(const MskMoeCfg* cfg, const void* packed13, const void* 
     return le;
   }
   if (plan.N != 16 && plan.N != 32 && plan.N != 64 && plan.N != 128) return MSK_ERR_SHAPE;
-  if (plan.s13 < 1 || plan.s2 < 1 || plan.s13 > static_cast<int>(MAX_SPLIT) || plan.s2 > static_cast<int>(MAX_SPLIT))
-    return MSK_ERR_SHAPE;
-  // the partial buffer bounds what a split plan may use; fall back to one split beyond it
-  {
-    const size_t tiles = max_tiles(cfg, n_tokens);
-    const size_t need13 = tiles * (cfg->inter / 128) * plan.s13 * 2 * 128 * static_cast<size_t>(plan.N);
-    const size_t need2 = tiles * (cfg->hidden / 256) * plan.s2 * 2 * 128 * static_cast<size_t>(plan.N);
-    const size_t have = partial_floats(cfg, n_tokens);
-    if (plan.s13 > 1 && need13 > have) plan.s13 = 1;
-    if (plan.s2 > 1 && need2 > have) plan.s2 = 1;
+  if (plan.grid < 1 || plan.grid > MAX_CTAS) return MSK_ERR_SHAPE;
+  const int pdl = cfg->no_pdl ? 0 : 1;
+  const size_t r_max = static_cast<size_t>(cfg->max_tokens) * cfg->top_k;
+  unsigned long long* trace = (cfg->trace != 0 && plan.grid <= static_cast<int>(TRACE_CTAS))
+                                  ? reinterpret_cast<unsigned long long*>(b + k.trace) : nullptr;
+
+  // what every launch of the two GEMMs shares
+  GemmParams p{};
+  p.cnt = cnt; p.off = off; p.perm = perm; p.inv = inv; p.status = status; p.trace = trace;
+  p.nloc = cfg->local_count; p.top_k = cfg->top_k; p.flat = plan.flat;
+  // weights stream through L2 once per token tile; the activation rows are what many CTAs re-read,
+  // so the weights must not be the ones L2 keeps
+  p.evict_first = 1;
+  p.post_norm_w = static_cast<const __nv_bfloat16*>(post_norm_w);
+  p.eps = cfg->post_norm_eps;
+  PhaseParams& g13 = p.ph[0];
+  PhaseParams& g2 = p.ph[1];
+  g13.w = static_cast<const uint8_t*>(packed13); g13.gs = gs13; g13.act = xs; g13.outp = inter;
+  g13.partial = partial; g13.tickets = tickets;
+  g13.K = cfg->hidden; g13.out_ld = cfg->inter; g13.n_pairs = cfg->inter / 128;
+  g2.w = static_cast<const uint8_t*>(packed2); g2.gs = gs2; g2.act = inter; g2.outp = y;
+  g2.partial = partial + round_up(partial_floats(cfg) * 4, 256) / 4;
+  g2.tickets = tickets + round_up(ticket_ints(cfg, cfg->max_tokens) * 4, 256) / 4;
+  g2.K = cfg->inter; g2.out_ld = cfg->hidden; g2.n_pairs = cfg->hidden / 256;
+
+  if (plan.path != 1) {
+    // ---- few tokens: the GEMM kernels route, sort and combine themselves
+    p.route = logits != nullptr ? 1 : 2;
+    p.logits = logits; p.bias = bias; p.ids_in = topk_ids; p.ids_out = ids_out; p.tw_out = tw_out;
+    p.T = n_tokens; p.E = cfg->n_experts; p.lo = cfg->local_start; p.mode = cfg->routing_mode;
+    p.route_scale = cfg->route_scale;
+    p.fold = 1; p.tw = topk_weights; p.out = static_cast<__nv_bfloat16*>(out);
+    p.tok_tickets = reinterpret_cast<int32_t*>(b + k.few_ctl);
+    p.grid_bar = reinterpret_cast<unsigned int*>(b + k.few_ctl + 128);
+    p.x_bf16 = static_cast<const __nv_bfloat16*>(x);
+    if (ev) { cudaEventRecord(ev[0], st); cudaEventRecord(ev[1], st); }
+    if (plan.path == 0 && pre_norm_w == nullptr) {
+      if (ev) cudaEventRecord(ev[5], st);
+      const int e1 = launch_gemm_fused(plan.N, p, plan.grid, st);
+      if (ev) { cudaEventRecord(ev[2], st); cudaEventRecord(ev[3], st); cudaEventRecord(ev[4], st); }
+      return e1;
+    }
+    // F16 copy of the token rows (with the pre-expert norm when asked for), small blocks so that the
+    // gate/up kernel's CTAs fit beside them; it waits for what precedes the step and lets go of its
+    // dependents after that wait
+    int e = 0;
+    {
+      const bool pre = pre_norm_w != nullptr;
+      cudaLaunchConfig_t lc{};
+      lc.stream = st;
+      cudaLaunchAttribute at[1];
+      at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      at[0].val.programmaticStreamSerializationAllowed = pdl;
+      lc.attrs = at;
+      lc.numAttrs = 1;
+      if (pre) {
+        lc.gridDim = dim3(static_cast<unsigned>(n_tokens));
+        lc.blockDim = dim3(256);
+        e = static_cast<int>(cudaLaunchKernelEx(&lc, gather_rows_kernel, static_cast<const __nv_bfloat16*>(x),
+                                                static_cast<const int32_t*>(perm), static_cast<const int32_t*>(off),
+                                                static_cast<int>(cfg->local_count), static_cast<int>(cfg->top_k),
+                                                static_cast<int>(cfg->hidden), 0, xs,
+                                                static_cast<const __nv_bfloat16*>(pre_norm_w), pre_norm_eps));
+      } else {
+        const int n8 = n_tokens * (cfg->hidden / 8);
+        lc.gridDim = dim3(static_cast<unsigned>((n8 + 63) / 64));
+        lc.blockDim = dim3(64);
+        e = static_cast<int>(cudaLaunchKernelEx(&lc, convert_rows_kernel, static_cast<const __nv_bfloat16*>(x), xs, n8));
+      }
+      if (e != 0) return e;
+    }
+    if (ev) cudaEventRecord(ev[5], st);
+    e = launch_gemm_n<0>(plan.N, p, plan.grid, st, pdl);
+    if (e != 0) return e;
+    if (ev) cudaEventRecord(ev[2], st);
+    if (trace) p.trace = trace + TRACE_WORDS;
+    e = launch_gemm_n<1>(plan.N, p, plan.grid, st, pdl);
+    if (ev) { cudaEventRecord(ev[3], st); cudaEventRecord(ev[4], st); }
+    return e;
   }
 
+  // ---- chain of launches: [top-k +] sort, [row copy,] gate/up GEMM, down GEMM, combine
   if (ev) cudaEventRecord(ev[0], st);
   int e = 0;
   // narrow token tiles read an F16 copy of x; for few tokens the sorting CTA makes it
@@ -1010,20 +1098,6 @@ static int forward_impl(const MskMoeCfg* cfg, const void* packed13, const void* 
   if (ev) cudaEventRecord(ev[1], st);
   if (cfg->stop_after == 1) return MSK_OK;
 
-  GemmParams p{};
-  p.cnt = cnt; p.off = off; p.perm = perm; p.partial = partial; p.tickets = tickets; p.status = status;
-  p.nloc = cfg->local_count; p.top_k = cfg->top_k;
-  unsigned long long* trace = (cfg->trace != 0 && plan.grid <= static_cast<int>(TRACE_CTAS))
-                                  ? reinterpret_cast<unsigned long long*>(b + k.trace) : nullptr;
-  p.trace = trace;
-  // weights stream through L2 once per token tile; the activation rows are what many CTAs re-read,
-  // so the weights must not be the ones L2 keeps
-  p.evict_first = 1;
-
-  const size_t r_max = static_cast<size_t>(cfg->max_tokens) * cfg->top_k;
-  p.w = static_cast<const uint8_t*>(packed13); p.gs = gs13; p.act = x; p.outp = inter; p.post_norm_w = nullptr;
-  p.K = cfg->hidden; p.out_ld = cfg->inter; p.n_pairs = cfg->inter / 128; p.splits = plan.s13;
-  p.act = xs;
   if (!convert_in_sort) {
     // F16 copy of the token rows: sorted (expert-major) for the TMA tiles, plain [T, H] otherwise
     cudaLaunchConfig_t lc{};
@@ -1032,7 +1106,7 @@ static int forward_impl(const MskMoeCfg* cfg, const void* packed13, const void* 
     lc.stream = st;
     cudaLaunchAttribute at[1];
     at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    at[0].val.programmaticStreamSerializationAllowed = 1;
+    at[0].val.programmaticStreamSerializationAllowed = pdl;
     lc.attrs = at;
     lc.numAttrs = 1;
     e = static_cast<int>(cudaLaunchKernelEx(&lc, gather_rows_kernel, static_cast<const __nv_bfloat16*>(x),
@@ -1041,29 +1115,22 @@ static int forward_impl(const MskMoeCfg* cfg, const void* packed13, const void* 
                                             static_cast<int>(cfg->hidden), tma_b ? 1 : 0, xs,
                                             static_cast<const __nv_bfloat16*>(pre_norm_w), pre_norm_eps));
     if (e != 0) return e;
-    p.act = xs;
     if (tma_b) {
-      e = encode_act_map(&p.tmap_act, xs, r_max, cfg->hidden, plan.N);
+      e = encode_act_map(&p.tmap_act[0], xs, r_max, cfg->hidden, plan.N);
+      if (e != 0) return e;
+      e = encode_act_map(&p.tmap_act[1], inter, r_max, cfg->inter, plan.N);
       if (e != 0) return e;
     }
   }
-  e = launch_gemm_n<0>(plan.N, p, plan.grid, st);
+  if (ev) cudaEventRecord(ev[5], st);
+  p.y_bf16 = plan.N == 128 ? 1 : 0;  // the wide tile: half the y bytes written and read back
+  e = launch_gemm_n<0>(plan.N, p, plan.grid, st, pdl);
   if (e != 0) return e;
   if (ev) cudaEventRecord(ev[2], st);
   if (cfg->stop_after == 2) return MSK_OK;
 
-  p.w = static_cast<const uint8_t*>(packed2); p.gs = gs2; p.act = inter; p.outp = y;
-  p.partial = partial + round_up(partial_floats(cfg, cfg->max_tokens) * 4, 256) / 4;
-  p.tickets = tickets + round_up(max_tiles(cfg, cfg->max_tokens) * std::max(cfg->inter / 128, cfg->hidden / 256) * 4, 256) / 4;
   if (trace) p.trace = trace + TRACE_WORDS;
-  p.post_norm_w = static_cast<const __nv_bfloat16*>(post_norm_w);
-  p.K = cfg->inter; p.out_ld = cfg->hidden; p.n_pairs = cfg->hidden / 256; p.splits = plan.s2;
-  p.y_bf16 = (plan.N == 128 && plan.s2 == 1) ? 1 : 0;  // the wide tile: half the y bytes written and read back
-  if (tma_b) {
-    e = encode_act_map(&p.tmap_act, inter, r_max, cfg->inter, plan.N);
-    if (e != 0) return e;
-  }
-  e = launch_gemm_n<1>(plan.N, p, plan.grid, st);
+  e = launch_gemm_n<1>(plan.N, p, plan.grid, st, pdl);
   if (e != 0) return e;
   if (ev) cudaEventRecord(ev[3], st);
   if (cfg->stop_after == 3) return MSK_OK;
@@ -1075,7 +1142,7 @@ static int forward_impl(const MskMoeCfg* cfg, const void* packed13, const void* 
     lc.stream = st;
     cudaLaunchAttribute at[1];
     at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    at[0].val.programmaticStreamSerializationAllowed = 1;
+    at[0].val.programmaticStreamSerializationAllowed = pdl;
     lc.attrs = at;
     lc.numAttrs = 1;
     const bool wide = n_tokens >= COMBINE_WIDE_TOKENS;
@@ -1133,12 +1200,12 @@ int msk_moe_forward_timed(const MskMoeCfg* cfg, const void* packed13, const void
                           const float* topk_weights, void* out, void* workspace, size_t workspace_bytes,
                           int n_tokens, void* stream, float* host_ms) {
   if (!host_ms) return MSK_ERR_NULL;
-  static cudaEvent_t ev[64][5];
+  static cudaEvent_t ev[64][6];
   static bool made[64] = {false};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return MSK_ERR_RANGE;
   if (!made[dev]) {
-    for (int i = 0; i < 5; ++i) {
+    for (int i = 0; i < 6; ++i) {
       cudaError_t ce = cudaEventCreate(&ev[dev][i]);
       if (ce != cudaSuccess) return static_cast<int>(ce);
     }
@@ -1149,8 +1216,9 @@ int msk_moe_forward_timed(const MskMoeCfg* cfg, const void* packed13, const void
   if (rc != 0) return rc;
   cudaError_t ce = cudaEventSynchronize(ev[dev][4]);
   if (ce != cudaSuccess) return static_cast<int>(ce);
-  for (int i = 0; i < 4; ++i) {
-    ce = cudaEventElapsedTime(&host_ms[i], ev[dev][i], ev[dev][i + 1]);
+  const int from[5] = {0, 1, 5, 2, 3}, to[5] = {1, 5, 2, 3, 4};  // sort, row copy, gate/up, down, combine
+  for (int i = 0; i < 5; ++i) {
+    ce = cudaEventElapsedTime(&host_ms[i], ev[dev][from[i]], ev[dev][to[i]]);
     if (ce != cudaSuccess) return static_cast<int>(ce);
   }
   return MSK_OK;
@@ -1167,7 +1235,7 @@ int msk_moe_forward_timed(const MskMoeCfg* cfg, const void* packed13, const void
 // array instead. The array is part of the loaded library image: every GPU that loads the
 // library holds MSK_STATIC_WS_BYTES of it until the process exits.
 //  * Limits: n_tokens * top_k <= 128 routed rows, hidden <= 8192, inter <= 4096; anything
-//    larger is refused with MSK_ERR_TOO_LARGE. The GEMMs run without K splits here.
+//    larger is refused with MSK_ERR_TOO_LARGE. The GEMMs run on whole units here (no cut units, no pieces).
 //  * The first call on each device looks up the array's device address (cudaGetSymbolAddress,
 //    with that device current). Make that first call outside stream capture.
 //  * All calls on a device share the one array and it keeps what the last call left; the status
@@ -1250,23 +1318,48 @@ int msk_moe_forward_static(const MskMoeCfg* cfg, const void* packed13, const voi
   e = static_cast<int>(cudaGetLastError());
   if (e != 0) return e;
   GemmParams p{};
-  p.cnt = cnt; p.off = off; p.perm = perm; p.partial = nullptr; p.tickets = nullptr;
+  p.cnt = cnt; p.off = off; p.perm = perm; p.inv = inv;
   p.status = reinterpret_cast<int32_t*>(b); p.trace = nullptr;
-  p.nloc = cfg->local_count; p.top_k = cfg->top_k; p.evict_first = 1; p.splits = 1;
-  const int grid = cfg->num_ctas > 0 ? cfg->num_ctas : sm_count();
-  p.w = static_cast<const uint8_t*>(packed13); p.gs = gs13; p.act = xh; p.outp = inter; p.post_norm_w = nullptr;
-  p.K = cfg->hidden; p.out_ld = cfg->inter; p.n_pairs = cfg->inter / 128;
-  e = launch_gemm_n<0>(16, p, grid, st);
-  if (e != 0) return e;
-  p.w = static_cast<const uint8_t*>(packed2); p.gs = gs2; p.act = inter; p.outp = y;
+  p.nloc = cfg->local_count; p.top_k = cfg->top_k; p.evict_first = 1;
+  p.flat = 0;  // whole units only: no pieces, so no partial buffer and no tickets
   p.post_norm_w = static_cast<const __nv_bfloat16*>(post_norm_w);
-  p.K = cfg->inter; p.out_ld = cfg->hidden; p.n_pairs = cfg->hidden / 256;
-  e = launch_gemm_n<1>(16, p, grid, st);
+  const int grid = cfg->num_ctas > 0 ? std::min(cfg->num_ctas, MAX_CTAS) : DEFAULT_CTAS;
+  p.ph[0].w = static_cast<const uint8_t*>(packed13); p.ph[0].gs = gs13; p.ph[0].act = xh; p.ph[0].outp = inter;
+  p.ph[0].K = cfg->hidden; p.ph[0].out_ld = cfg->inter; p.ph[0].n_pairs = cfg->inter / 128;
+  p.ph[1].w = static_cast<const uint8_t*>(packed2); p.ph[1].gs = gs2; p.ph[1].act = inter; p.ph[1].outp = y;
+  p.ph[1].K = cfg->inter; p.ph[1].out_ld = cfg->hidden; p.ph[1].n_pairs = cfg->hidden / 256;
+  e = launch_gemm_n<0>(16, p, grid, st, 1);
+  if (e != 0) return e;
+  e = launch_gemm_n<1>(16, p, grid, st, 1);
   if (e != 0) return e;
   combine_kernel<4, false, 1><<<static_cast<unsigned>(n_tokens), COMBINE_THREADS, 0, st>>>(
       y, inv, topk_weights, static_cast<__nv_bfloat16*>(out), cfg->hidden, cfg->top_k, post_norm_w != nullptr ? 1 : 0,
       cfg->post_norm_eps);
   return static_cast<int>(cudaGetLastError());
+}
+
+int msk_moe_share_pieces(int n_base, int n_stages, int shares, int mode, int cta, int* host_out, int capacity,
+                         int* host_count) {
+  if (!host_out || !host_count) return MSK_ERR_NULL;
+  if (n_base < 0 || n_stages < 1 || shares < 1 || cta < 0 || cta >= shares || mode < 0 || mode > 2 || capacity < 0)
+    return MSK_ERR_SHAPE;
+  PieceIter it = make_piece_iter(mode, n_base, n_stages, cta, shares);
+  const long long items = static_cast<long long>(n_base) * n_stages;
+  int n = 0, base, ks0, ks1;
+  while (it.next(base, ks0, ks1)) {
+    if (n < capacity) {
+      int* o = host_out + 6 * n;
+      const bool whole = ks0 == 0 && ks1 == n_stages;
+      const long long b0 = static_cast<long long>(base) * n_stages;
+      o[0] = base; o[1] = ks0; o[2] = ks1;
+      o[3] = whole ? -1 : piece_slot(cta, ks0 == 0);
+      o[4] = whole ? cta : share_owner(items, shares, b0);
+      o[5] = whole ? cta : share_owner(items, shares, b0 + n_stages - 1);
+    }
+    ++n;
+  }
+  *host_count = n;
+  return n <= capacity ? MSK_OK : MSK_ERR_TOO_LARGE;
 }
 
 #ifndef MSK_BUILD_ID
@@ -1280,7 +1373,7 @@ int msk_moe_plan(const MskMoeCfg* cfg, int n_tokens, int* host_out) {
   if (!host_out) return MSK_ERR_NULL;
   if (n_tokens < 1) return MSK_ERR_SHAPE;
   const Plan plan = make_plan(cfg, n_tokens);
-  host_out[0] = plan.N; host_out[1] = plan.s13; host_out[2] = plan.s2; host_out[3] = plan.grid;
+  host_out[0] = plan.N; host_out[1] = plan.path; host_out[2] = plan.flat; host_out[3] = plan.grid;
   return MSK_OK;
 }
 

@@ -431,4 +431,82 @@ __global__ void __launch_bounds__(SORT_THREADS) route_sort_kernel(const float* _
   sort_entries_block(sm, ids, T * k, lo, nloc, cnt, off, perm, inv);
 }
 
+// ---- routing + stable sort of a few entries inside another kernel's prologue
+// For up to 256 (token, slot) entries every CTA of the gate/up GEMM kernel derives the tables itself,
+// as every CTA of the reference kernel does (muse_moe_w4a16/cuda/moe.cu:313-433), so the step needs no
+// separate routing / sorting launch. Same algorithm as sort_entries_block with one 32-entry step per
+// warp: warps 0-7 own entries [32 w, 32 w + 32), equal experts keep ascending entry order.
+constexpr int SMALL_SORT_MAX_ENTRIES = 256;
+constexpr int SMALL_SORT_WARPS = SMALL_SORT_MAX_ENTRIES / 32;
+
+struct SmallSortScratch {
+  int wcnt[SMALL_SORT_WARPS][MAX_LOCAL_EXPERTS];
+  int wsum[SMALL_SORT_WARPS];
+  int32_t ids[SMALL_SORT_MAX_ENTRIES];
+  float tw[SMALL_SORT_MAX_ENTRIES];
+};
+
+// Called by every thread of the CTA (block size a multiple of 32, at least 256). ids_s: the entries
+// in shared memory. Results: cnt_s[nloc], off_s[nloc + 1], perm8_s[q] = entry index (fits a byte) in
+// shared memory; when `global` the calling CTA also writes cnt, off, perm, inv to global memory.
+__device__ __forceinline__ void sort_small_cta(SmallSortScratch& sc, int n, int lo, int nloc, int* cnt_s, int* off_s,
+                                               uint8_t* perm8_s, bool global, int32_t* cnt_g, int32_t* off_g,
+                                               int32_t* perm_g, int32_t* inv_g) {
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, nthreads = blockDim.x;
+  for (int i = tid; i < SMALL_SORT_WARPS * MAX_LOCAL_EXPERTS; i += nthreads) (&sc.wcnt[0][0])[i] = 0;
+  __syncthreads();
+  int l = -1, rank = 0;
+  if (warp < SMALL_SORT_WARPS) {
+    const int i = warp * 32 + lane;
+    l = i < n ? local_expert(sc.ids[i], lo, nloc) : -1;
+    const unsigned peers = __match_any_sync(0xffffffffu, l);
+    rank = __popc(peers & ((1u << lane) - 1u));
+    if (l >= 0 && rank == 0) sc.wcnt[warp][l] = __popc(peers);
+  }
+  __syncthreads();
+  int tot = 0, excl = 0;
+  if (tid < MAX_LOCAL_EXPERTS) {   // thread e: exclusive scan of expert e over the warps, then over the experts
+    if (tid < nloc) {
+#pragma unroll
+      for (int w = 0; w < SMALL_SORT_WARPS; ++w) {
+        const int c = sc.wcnt[w][tid];
+        sc.wcnt[w][tid] = tot;
+        tot += c;
+      }
+      cnt_s[tid] = tot;
+    }
+    int incl = tot;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += v;
+    }
+    if (lane == 31) sc.wsum[warp] = incl;
+    excl = incl - tot;
+  }
+  __syncthreads();
+  if (tid < MAX_LOCAL_EXPERTS) {
+    for (int w = 0; w < warp; ++w) excl += sc.wsum[w];
+    if (tid < nloc) off_s[tid] = excl;
+    if (tid == nloc - 1) off_s[nloc] = excl + tot;
+  }
+  __syncthreads();
+  if (warp < SMALL_SORT_WARPS) {
+    const int i = warp * 32 + lane;
+    if (i < n) {
+      const int q = l >= 0 ? off_s[l] + sc.wcnt[warp][l] + rank : -1;
+      if (q >= 0) perm8_s[q] = static_cast<uint8_t>(i);
+      if (global) {
+        inv_g[i] = q;
+        if (q >= 0) perm_g[q] = i;
+      }
+    }
+  }
+  if (global) {
+    if (tid < nloc) cnt_g[tid] = cnt_s[tid];
+    if (tid <= nloc) off_g[tid] = off_s[tid];
+  }
+  __syncthreads();
+}
+
 }  // namespace msk

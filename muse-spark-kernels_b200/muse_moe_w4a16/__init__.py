@@ -36,7 +36,7 @@ def _stream():
 
 
 def prepare(weights, *, local_start=0, n_experts=None, top_k=8, max_tokens=8192, routing_mode="softmax_topk",
-            route_scale=0.1767766952966369, post_norm_eps=1e-8, num_ctas=0, split_k13=0, split_k2=0, token_tile=0,
+            route_scale=0.1767766952966369, post_norm_eps=1e-8, num_ctas=0, decode_path=0, no_pdl=0, token_tile=0,
             trace=0, stop_after=0, pre_norm_eps=1e-5):
     """Repack the NVFP4 weights into the tile layout the GEMM kernel streams (bit and byte
     permutations only, never requantised) and allocate the workspace. Returns `state`."""
@@ -55,7 +55,7 @@ def prepare(weights, *, local_start=0, n_experts=None, top_k=8, max_tokens=8192,
         raise RuntimeError("muse_moe_w4a16.prepare: global scales must be float32")
     cfg = MskMoeCfg(hidden=H, inter=I, n_experts=n_experts or n_local, local_start=local_start,
                     local_count=n_local, top_k=top_k, routing_mode=_MODES[routing_mode], route_scale=route_scale,
-                    post_norm_eps=post_norm_eps, num_ctas=num_ctas, split_k13=split_k13, split_k2=split_k2,
+                    post_norm_eps=post_norm_eps, num_ctas=num_ctas, decode_path=decode_path, no_pdl=no_pdl,
                     token_tile=token_tile, max_tokens=max_tokens, trace=trace, stop_after=stop_after)
     b13, b2 = ctypes.c_size_t(), ctypes.c_size_t()
     _lib.check(lib.msk_moe_packed_bytes(ctypes.byref(cfg), ctypes.byref(b13), ctypes.byref(b2)), "msk_moe_packed_bytes")
@@ -233,13 +233,14 @@ class GraphedStep:
 
 def kernel_fn_timed(data, state):
     """kernel_fn with CUDA events around each launch of the expert step; synchronises.
-    Returns (out, [ms sort, ms gate/up GEMM, ms down GEMM, ms combine]). Measuring only."""
+    Returns (out, [ms routing + sort, ms row copy, ms gate/up GEMM, ms down GEMM, ms combine]); the
+    one-launch path for a few tokens reports the whole step under gate/up. Measuring only."""
     cfg, lib = state["cfg"], state["lib"].lib
     x = data["hidden_states"].contiguous()
     T = x.shape[0]
     ids, tw = _route(data, state, x, T)
     out = torch.empty((T, cfg.hidden), dtype=torch.bfloat16, device=x.device)
-    ms = (ctypes.c_float * 4)()
+    ms = (ctypes.c_float * 5)()
     _lib.check(lib.msk_moe_forward_timed(ctypes.byref(cfg), _lib.ptr(state["packed13"]), _lib.ptr(state["packed2"]),
                                          _lib.ptr(state["gs13"]), _lib.ptr(state["gs2"]),
                                          _lib.ptr(state["post_norm_w"]), _lib.ptr(x), _lib.ptr(ids), _lib.ptr(tw),
@@ -249,7 +250,7 @@ def kernel_fn_timed(data, state):
 
 
 def plan(state, T):
-    """(token tile N, K splits gate/up, K splits down, grid) that kernel_fn uses for T tokens."""
+    """(token tile N, path, flat shares, grid) that kernel_fn uses for T tokens (see msk_moe_plan)."""
     out = (ctypes.c_int * 4)()
     _lib.check(state["lib"].lib.msk_moe_plan(ctypes.byref(state["cfg"]), T, out), "msk_moe_plan")
     return tuple(out)
@@ -309,8 +310,8 @@ def workspace_views(state, T):
     perm = view(2, T * k * 4, torch.int32)
     inv = view(3, T * k * 4, torch.int32)
     inter = view(4, R * cfg.inter * 2, torch.float16).view(R, cfg.inter)
-    n_tile, _, s2, _ = plan(state, T)
-    if n_tile == 128 and s2 == 1:      # the wide token tile keeps y in BF16
+    n_tile = plan(state, T)[0]
+    if n_tile == 128:      # the wide token tile keeps y in BF16
         y = view(5, R * cfg.hidden * 2, torch.bfloat16).view(R, cfg.hidden)
     else:
         y = view(5, R * cfg.hidden * 4, torch.float32).view(R, cfg.hidden)

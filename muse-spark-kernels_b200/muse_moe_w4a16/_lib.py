@@ -37,8 +37,8 @@ class MskMoeCfg(ctypes.Structure):
         ("route_scale", ctypes.c_float),
         ("post_norm_eps", ctypes.c_float),
         ("num_ctas", ctypes.c_int32),
-        ("split_k13", ctypes.c_int32),
-        ("split_k2", ctypes.c_int32),
+        ("decode_path", ctypes.c_int32),
+        ("no_pdl", ctypes.c_int32),
         ("token_tile", ctypes.c_int32),
         ("max_tokens", ctypes.c_int32),
         ("trace", ctypes.c_int32),
@@ -77,6 +77,7 @@ SIGNATURES = {
     "msk_moe_forward_static": [_CFG, _P, _P, _P, _P, _P, _P, _P, _P, _P, ctypes.c_int, _P],
     "msk_moe_static_status": [_INTP, _P],
     "msk_moe_plan": [_CFG, ctypes.c_int, _INTP],
+    "msk_moe_share_pieces": [ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, _INTP, ctypes.c_int, _INTP],
     "msk_moe_workspace_view": [_CFG, _P, ctypes.c_int, ctypes.POINTER(_P)],
     "msk_moe_read_status": [_P, _INTP, _P],
     "msk_moe_attrs": [ctypes.c_int, ctypes.c_int, _INTP],

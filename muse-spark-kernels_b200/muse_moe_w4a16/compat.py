@@ -24,8 +24,10 @@ class OkcExt:
         return self
 
     def okc_set_pdl(self, on):
-        """Accepted and ignored: the launches of a step are always chained with programmatic
-        dependent launch here."""
+        """The reference's process-wide switch (muse_moe_w4a16/cuda/moe.cu:2348,2565) as a field of this
+        state's configuration: with 0 the launches of a step are plain stream-ordered launches, with 1
+        they are chained with programmatic dependent launch (the default)."""
+        self.state["cfg"].no_pdl = 0 if on else 1
         return None
 
     def okc_attrs(self):
@@ -36,10 +38,14 @@ class OkcExt:
 
     def okc_run(self, w, scratch, x, ids, tw, out, lo, nloc, grid):
         """`w` and `scratch` are the reference's tensor lists; the prepared state owns their
-        counterparts, so they are ignored. `lo` / `nloc` must be the prepared local range; `grid`
-        (CTAs) is fixed at prepare time."""
+        counterparts, so they are not read. `lo` / `nloc` must be the prepared local range and `grid`
+        the persistent grid the state was prepared for (num_ctas, 148 by default): a call that asks for
+        another one is refused rather than silently run on a different grid."""
         st = self.state
         if int(lo) != st["lo"] or int(nloc) != st["cnt"]:
             raise RuntimeError("okc_run: local range differs from the prepared state")
+        want = st["cfg"].num_ctas or 148
+        if int(grid) != want:
+            raise RuntimeError(f"okc_run: grid {int(grid)} differs from the prepared state's {want}")
         kernel_fn({"hidden_states": x, "topk_ids": ids, "topk_weights": tw}, st, out=out)
         return None

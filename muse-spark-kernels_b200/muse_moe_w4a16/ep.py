@@ -251,87 +251,3 @@ class EPModule:
         if self.exchange is not None:
             return self.exchange.step(x, ids, tw, self._experts, self.per_rank)
         return ep_step(x, ids, tw, self._experts, self.per_rank, self.group)
-
-
-def bench_ep(args, spec, dev, rank, world, metric, unit, clock_sampler_cls, load_peaks):
-    """The --gpus N > 1 arm of bench.py: config 4 (H7168 I2048 E256 top-8, T = 4096 per GPU)."""
-    import json
-
-    from . import inputs
-
-    s = inputs.SHAPES[spec["shape"]]
-    H, I, E, k, T = s["H"], s["I"], s["E"], s["k"], spec["T"]
-    per = E // world
-    weights = inputs.make_weights_random_bytes(H, I, per, 1000 + rank, dev)
-    mod = EPModule(weights, rank, world, E, k, T, chunks=(getattr(args, "ep_chunks", 0) or None))
-    del weights
-    torch.cuda.empty_cache()
-    pool = [inputs.make_inputs(spec["shape"], T, 17 * rank + i, dev)[0] for i in range(4)]
-    host_pool = [{"hidden_states": d["hidden_states"].cpu().pin_memory(),
-                  "router_logits": d["router_logits"].cpu().pin_memory()} for d in pool]
-    sampler = clock_sampler_cls(dev.index)
-    sampler.start()
-
-    def run(n, e2e):
-        xd = torch.empty((T, H), dtype=torch.bfloat16, device=dev)
-        ld = torch.empty((T, E), dtype=torch.float32, device=dev)
-        out_h = torch.empty((T, H), dtype=torch.bfloat16).pin_memory()
-        dist.barrier()
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for i in range(n):
-            if e2e:
-                hp = host_pool[i % len(pool)]
-                xd.copy_(hp["hidden_states"], non_blocking=True)
-                ld.copy_(hp["router_logits"], non_blocking=True)
-                o = mod.kernel_fn({"hidden_states": xd, "router_logits": ld})
-                out_h.copy_(o, non_blocking=True)
-            else:
-                mod.kernel_fn(pool[i % len(pool)])
-        e1.record()
-        torch.cuda.synchronize()
-        dist.barrier()
-        t = torch.tensor([e0.elapsed_time(e1)], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
-
-    run(max(args.warmup, 3), False)
-    ms = run(args.steps, False)
-    run(max(args.warmup, 3), True)
-    ms_e2e = run(args.steps, True)
-    clocks = sampler.stop()
-    from . import read_status
-
-    status = torch.tensor([read_status(mod.state)], device=dev)
-    dist.all_reduce(status, op=dist.ReduceOp.MAX)
-    if int(status.item()) != 0:
-        raise RuntimeError("device status word is non-zero on some rank")
-    if rank == 0:
-        peaks = load_peaks()
-        flops = inputs.algorithmic_flops(H, I, T * k * world) * args.steps
-        line = {
-            "metric": metric, "value": T * world * args.steps / (ms * 1e-3), "unit": unit, "n_gpus": world,
-            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16 x nvfp4 -> fp32 acc",
-            "data": "synthetic",
-            "config": {"workload": spec["name"], "tokens_per_gpu": T, "hidden": H, "inter": I, "experts": E,
-                       "top_k": k, "parallelism": f"ep{world}", "l2": "inputs and weights exceed L2 (792 MB of weights per rank at 8 ranks)",
-                       "dispatch": f"{mod.transport}, {mod.chunks} chunk(s) of source ranks"},
-            "e2e": {"value": T * world * args.steps / (ms_e2e * 1e-3), "unit": unit,
-                    "h2d_bytes_per_step": (T * H * 2 + T * E * 4) * world, "d2h_bytes_per_step": T * H * 2 * world,
-                    "ms_per_step": ms_e2e / args.steps},
-            # per rank and step: top-k, the final rank-order sum, and per chunk the sort (three launches from
-            # 16384 entries on), the F16 row copy, two GEMMs and the combine
-            "gpu_launches": (2 + (7 if (world // mod.chunks) * T * k >= 16384 else 5) * mod.chunks) * args.steps * world,
-            "roofline": {"bound": "tensor", "achieved": flops / world / (ms * 1e-3) / 1e12,
-                         "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
-                         "frac": flops / world / (ms * 1e-3) / 1e12 / peaks["bf16_tflops_sustained"], "traffic": None,
-                         "kernel": "whole EP step per GPU (expert kernels + exchange)",
-                         "peak_source": peaks["source"] + " (sustained)"},
-            "cpu_baseline": None,
-            "clocks": clocks,
-        }
-        print(json.dumps(line), flush=True)
-    dist.barrier()
-    dist.destroy_process_group()

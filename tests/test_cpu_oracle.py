@@ -185,6 +185,85 @@ def test_host_side_validation_rejects_bad_arguments():
     assert lib.msk_moe_plan(ctypes.byref(cfg), 4, plan) == 0 and plan[0] in (8, 16, 32, 64, 128)
 
 
+def _pieces(lib, n_base, nst, shares, mode, cta):
+    cap = 4096
+    buf = (ctypes.c_int * (6 * cap))()
+    n = ctypes.c_int()
+    assert lib.msk_moe_share_pieces(n_base, nst, shares, mode, cta, buf, cap, ctypes.byref(n)) == 0
+    return [tuple(buf[6 * i:6 * i + 6]) for i in range(n.value)]
+
+
+@pytest.mark.parametrize("n_base,nst,shares", [(96, 16, 148), (128, 6, 148), (600, 16, 148), (3, 28, 148), (1, 1, 7),
+                                               (0, 16, 148), (37, 5, 5), (224, 8, 148), (50, 2, 1)])
+def test_flat_shares_cover_every_stage_once_and_name_their_pieces(n_base, nst, shares):
+    """The work distribution of the GEMM kernels (host twin of the device code): with flat shares
+    every (unit, stage) item belongs to exactly one CTA, shares differ by at most one item, a cut unit's
+    pieces sit in consecutive CTAs in ascending K order, each in a slot of its own, and the first / last
+    owner every piece computes is the CTA that really holds the unit's first / last stage."""
+    from muse_moe_w4a16 import _lib
+
+    lib = _lib.load()
+    seen = {}
+    sizes = []
+    slots = set()
+    for c in range(shares):
+        pcs = _pieces(lib, n_base, nst, shares, 2, c)
+        sizes.append(sum(k1 - k0 for _, k0, k1, *_ in pcs))
+        for base, k0, k1, slot, first, last in pcs:
+            assert 0 <= k0 < k1 <= nst
+            for ks in range(k0, k1):
+                assert (base, ks) not in seen
+                seen[(base, ks)] = c
+            if slot >= 0:
+                assert slot not in slots and slot // 2 == c
+                slots.add(slot)
+            else:
+                assert (k0, k1) == (0, nst)
+    assert len(seen) == n_base * nst
+    assert max(sizes) - min(sizes) <= 1
+    for c in range(shares):
+        for base, k0, k1, slot, first, last in _pieces(lib, n_base, nst, shares, 2, c):
+            assert first == seen[(base, 0)] and last == seen[(base, nst - 1)]
+            owners = [seen[(base, ks)] for ks in range(nst)]
+            assert owners == sorted(owners) and first <= min(owners) and max(owners) <= last
+            # every share between the first and the last owner either holds a piece of the unit or is empty
+            assert all(c in owners or sizes[c] == 0 for c in range(first, last + 1))
+
+
+@pytest.mark.parametrize("mode", [0, 1])
+def test_whole_unit_modes_give_every_unit_to_one_cta(mode):
+    from muse_moe_w4a16 import _lib
+
+    lib = _lib.load()
+    n_base, nst, shares = 301, 16, 148
+    got = []
+    for c in range(shares):
+        for base, k0, k1, slot, first, last in _pieces(lib, n_base, nst, shares, mode, c):
+            assert (k0, k1, slot) == (0, nst, -1)
+            got.append(base)
+    assert sorted(got) == list(range(n_base))
+
+
+def test_plan_is_a_function_of_the_configuration_only():
+    """Token tile, path and grid follow from the shapes and the token count (never from the device:
+    the default grid is a constant), few tokens take the one-launch path with flat shares."""
+    from muse_moe_w4a16 import _lib
+
+    lib = _lib.load()
+    plan = (ctypes.c_int * 4)()
+    cfg = _lib.MskMoeCfg(hidden=4096, inter=1536, n_experts=128, local_start=0, local_count=128, top_k=8, max_tokens=8192)
+    want = {1: (16, 0, 1, 148), 8: (16, 0, 1, 148), 32: (16, 0, 1, 148), 64: (16, 1, 0, 148), 256: (64, 1, 0, 148),
+            8192: (128, 1, 0, 148)}
+    for T, w in want.items():
+        assert lib.msk_moe_plan(ctypes.byref(cfg), T, plan) == 0
+        assert tuple(plan) == w, (T, tuple(plan))
+    cfg.decode_path = 2
+    assert lib.msk_moe_plan(ctypes.byref(cfg), 8, plan) == 0 and tuple(plan) == (16, 2, 1, 148)
+    cfg.decode_path = 1
+    cfg.num_ctas = 37
+    assert lib.msk_moe_plan(ctypes.byref(cfg), 8, plan) == 0 and tuple(plan) == (16, 1, 1, 37)
+
+
 def test_module_refuses_cpu_tensors():
     import muse_moe_w4a16 as moe
     from muse_moe_w4a16 import inputs

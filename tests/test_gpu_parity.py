@@ -199,22 +199,53 @@ def test_forward_tiny_config0(cuda_dev):
     _check_forward(out, ref, parts, m.workspace_views(st, T))
 
 
-@pytest.mark.parametrize("T,tile,s13,s2,post", [(1, 0, 0, 0, False), (5, 16, 1, 1, True), (5, 16, 2, 2, False),
-                                                (40, 32, 1, 1, False), (70, 64, 1, 1, True),
-                                                (300, 128, 1, 1, False), (9, 16, 2, 1, True),
-                                                (600, 0, 0, 0, True), (300, 128, 1, 1, True)])
-def test_forward_small_shapes(cuda_dev, T, tile, s13, s2, post):
+@pytest.mark.parametrize("T,tile,path,post", [(1, 0, 0, False), (5, 16, 0, True), (5, 16, 1, False), (5, 16, 2, True),
+                                              (40, 32, 1, False), (70, 64, 1, True), (300, 128, 1, False),
+                                              (9, 16, 0, True), (9, 16, 1, True), (600, 0, 1, True), (300, 128, 1, True),
+                                              (32, 16, 0, False), (32, 32, 2, True), (17, 32, 0, True), (32, 16, 1, True)])
+def test_forward_small_shapes(cuda_dev, T, tile, path, post):
+    """Every token tile and, for a few tokens, every path (0 one launch, 1 chain of launches, 2 row
+    copy + routing gate/up kernel + combining down kernel)."""
     m, inputs, _lib, orc = _mods()
     out, ref, parts, views, st, _ = _run_forward(m, inputs, orc, cuda_dev, 512, 256, 8, 2, T, seed=T, post_norm=post,
-                                                 token_tile=tile, split_k13=s13, split_k2=s2)
+                                                 token_tile=tile, decode_path=path)
+    if T <= 32:
+        assert m.plan(st, T)[1] == path
     _check_forward(out, ref, parts, views)
+
+
+@pytest.mark.parametrize("T,path,ctas,post", [(1, 0, 0, False), (1, 0, 37, True), (1, 2, 0, True), (1, 1, 0, False),
+                                              (3, 0, 5, True), (3, 2, 148, False), (8, 0, 0, True), (8, 2, 37, False),
+                                              (8, 1, 100, True), (32, 0, 0, True), (32, 0, 111, False), (32, 2, 0, True),
+                                              (20, 0, 1, False), (2, 0, 148, True)])
+def test_forward_few_token_paths_and_grids(cuda_dev, T, path, ctas, post):
+    """Few tokens: the weight stream is cut into equal shares per CTA, so units are summed from pieces
+    whose cut points move with the grid size; the kernels route, sort and combine themselves (paths 0
+    and 2). Every combination must match the oracle, give the same bits with the routing passed in
+    instead of the logits, and stay within rounding of the chain of launches."""
+    m, inputs, _lib, orc = _mods()
+    H, I, E, k = 1024, 512, 16, 4
+    out, ref, parts, views, st, (x, ids, tw, w) = _run_forward(m, inputs, orc, cuda_dev, H, I, E, k, T, seed=60 + T,
+                                                               post_norm=post, decode_path=path, num_ctas=ctas)
+    plan = m.plan(st, T)
+    assert plan[1] == path and plan[2] == 1 and plan[3] == (ctas or 148)
+    _check_forward(out, ref, parts, views)
+    again = m.kernel_fn({"hidden_states": x, "topk_ids": ids, "topk_weights": tw}, st)
+    assert torch.equal(again, out)
+    chain = m.prepare(w, n_experts=E, top_k=k, max_tokens=T, decode_path=1, token_tile=16, num_ctas=3)
+    other = m.kernel_fn({"hidden_states": x, "topk_ids": ids, "topk_weights": tw}, chain)
+    assert _rel(out, other) <= 8e-3   # same products, other cut points: a bf16 ulp or two of the output
+    torch.cuda.synchronize()
+    assert m.read_status(st) == 0 and m.read_status(chain) == 0
 
 
 def test_forward_decode_shape_T1_and_T8(cuda_dev):
     """Config 1/2 shape with fewer experts resident (E=16 of the 4096 x 1536 experts)."""
     m, inputs, _lib, orc = _mods()
-    for T in (1, 8):
-        out, ref, parts, views, st, _ = _run_forward(m, inputs, orc, cuda_dev, 4096, 1536, 16, 8, T, seed=10 + T)
+    for T, path in ((1, 0), (8, 0), (1, 2), (8, 2), (8, 1)):
+        out, ref, parts, views, st, _ = _run_forward(m, inputs, orc, cuda_dev, 4096, 1536, 16, 8, T, seed=10 + T,
+                                                     decode_path=path)
+        assert m.plan(st, T)[:3] == (16, path, 1)
         _check_forward(out, ref, parts, views)
 
 
@@ -253,20 +284,20 @@ def test_forward_few_token_kernel(cuda_dev, T, post, ctas):
     # given routing instead of logits, and the chain of launches on the same inputs
     again = m.kernel_fn({"hidden_states": x, "topk_ids": ids, "topk_weights": tw}, st)
     assert torch.equal(again, out)
-    chain = m.prepare(w, n_experts=16, top_k=4, max_tokens=T, token_tile=16)
+    chain = m.prepare(w, n_experts=16, top_k=4, max_tokens=T, token_tile=16, decode_path=1)
     other = m.kernel_fn({"hidden_states": x, "topk_ids": ids, "topk_weights": tw}, chain)
     assert _rel(out, other) <= 8e-3   # same products, different summation order: a bf16 ulp or two of the output
     assert m.read_status(st) == 0 and m.read_status(chain) == 0
 
 
-@pytest.mark.parametrize("tile", [8, 16])
-def test_forward_local_range_negative_ids_and_empty_tokens(cuda_dev, tile):
+@pytest.mark.parametrize("tile,path", [(8, 0), (16, 0), (16, 1), (16, 2)])
+def test_forward_local_range_negative_ids_and_empty_tokens(cuda_dev, tile, path):
     """Experts [4, 12) of 16 resident: routes outside the range and negative ids are dropped (the
     reference's filter, muse_moe_w4a16/cuda/moe.cu:347-350); a token left without any route is zero."""
     m, inputs, _lib, orc = _mods()
     H, I, E, k, T, lo, nloc = 512, 256, 16, 4, 6, 4, 8
     w = inputs.make_weights(H, I, nloc, 31, cuda_dev, post_norm=True)
-    st = m.prepare(w, local_start=lo, n_experts=E, top_k=k, max_tokens=T, token_tile=tile)
+    st = m.prepare(w, local_start=lo, n_experts=E, top_k=k, max_tokens=T, token_tile=tile, decode_path=path)
     g = torch.Generator(device=cuda_dev).manual_seed(5)
     x = torch.randn((T, H), generator=g, device=cuda_dev).to(torch.bfloat16)
     ids = torch.stack([torch.randperm(E, generator=g, device=cuda_dev)[:k] for _ in range(T)]).to(torch.int32)
@@ -386,6 +417,16 @@ def test_okc_ext_runs_the_decode_layer_call_site(cuda_dev):
     assert len(ext.okc_attrs()) == 6
     with pytest.raises(RuntimeError):
         ext.okc_run(None, None, x[:1], lids[:1], wts[:1], out[:1], 1, nloc, 148)
+    with pytest.raises(RuntimeError):
+        ext.okc_run(None, None, x[:1], lids[:1], wts[:1], out[:1], 0, nloc, 132)   # a grid it was not prepared for
+    # without programmatic dependent launch the chain of launches gives the same bits
+    ext.okc_set_pdl(0)
+    out2 = torch.empty_like(out)
+    for m0 in range(0, T, 8):
+        m1 = min(T, m0 + 8)
+        ext.okc_run(None, None, x[m0:m1], lids[m0:m1], wts[m0:m1], out2[m0:m1], 0, nloc, 148)
+    torch.cuda.synchronize()
+    assert torch.equal(out2, out)
 
 
 @pytest.mark.parametrize("T,given_ids", [(3, False), (7, True), (40, True), (300, False), (600, True)])
@@ -543,7 +584,7 @@ def test_forward_reference_skewed_counts(cuda_dev, tile):
     _check_forward(out, ref, parts, m.workspace_views(st, T))
 
 
-SENTINEL = 0x5EADBEEF - (1 << 32)   # as int32
+SENTINEL = 0x5EADBEEF
 GUARD_WORDS = 65536
 
 
