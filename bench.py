@@ -18,8 +18,10 @@ SwiGLU, down GEMM, combine) over one batch of seeded synthetic input.
              D2H of `out`; event-timed, with the host wall-clock time per step beside it
   roofline   dominant kernel: algorithmic bytes or flops / its mean event-timed duration
   cpu_baseline  the CPU oracle (PyTorch eager on the host cores) on a bounded sample of the same inputs
-L2 is flushed (a 256 MiB write) before every timed step, outside the timed interval, and the
-steps cycle through a pool of different routings.
+L2 is flushed before every timed step, outside the timed interval, by reading a 256 MiB buffer
+(`--flush write` zeroes it instead: that leaves L2 full of dirty lines whose write-back competes
+with the step; the reference sweeps by reading for that reason), and the steps cycle through a
+pool of different routings.
 """
 import argparse
 import json
@@ -186,7 +188,7 @@ def run_reference(args, spec):
 
 
 # ------------------------------------------------------------ one GPU, one workload
-def measure(moe, inputs, state, spec, steps, warmup, peaks, dev, flush, with_e2e=True):
+def measure(moe, inputs, state, spec, steps, warmup, peaks, dev, flush_fn, with_e2e=True):
     """Times one workload on a prepared state. Returns the dict that goes into the JSON line."""
     import torch
 
@@ -227,7 +229,7 @@ def measure(moe, inputs, state, spec, steps, warmup, peaks, dev, flush, with_e2e
     def timed_graph_steps(n):
         evs = []
         for i in range(n):
-            flush.zero_()
+            flush_fn()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
             graphs[i % POOL].replay()
@@ -250,7 +252,7 @@ def measure(moe, inputs, state, spec, steps, warmup, peaks, dev, flush, with_e2e
         def e2e_steps(n):
             evs = []
             for i in range(n):
-                flush.zero_()
+                flush_fn()
                 hp = host_pool[i % POOL]
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 e0.record()
@@ -266,7 +268,7 @@ def measure(moe, inputs, state, spec, steps, warmup, peaks, dev, flush, with_e2e
             # what a caller that needs the result on the host feels: Python, staging copy, launch, D2H, sync
             ts = []
             for i in range(n):
-                flush.zero_()
+                flush_fn()
                 torch.cuda.synchronize()
                 hp = host_pool[i % POOL]
                 t0 = time.perf_counter()
@@ -286,7 +288,7 @@ def measure(moe, inputs, state, spec, steps, warmup, peaks, dev, flush, with_e2e
     n_prof = max(3, min(steps, 200))
     k_ms = [0.0] * 5
     for i in range(n_prof + 3):
-        flush.zero_()
+        flush_fn()
         _, ms = moe.kernel_fn_timed(pool[i % POOL], state)
         if i >= 3:
             k_ms = [a + b for a, b in zip(k_ms, ms)]
@@ -380,21 +382,22 @@ def run_gpu(args, spec):
                         decode_path=args.decode_path)
     del weights
     torch.cuda.empty_cache()
-    flush = torch.empty(64 * 1024 * 1024, dtype=torch.int32, device=dev)  # 256 MiB > 126 MB of L2
+    sweeper = moe.L2Sweep(dev)    # 256 MiB > 126 MB of L2
+    flush_fn = sweeper.buf.zero_ if args.flush == "write" else sweeper.sweep
     if args.profile_only:
         for i in range(max(args.warmup, 1) + args.steps):
             data, _ = inputs.make_inputs(spec["shape"], T, i % POOL, dev)
-            flush.zero_()
+            flush_fn()
             moe.kernel_fn(data, state)
         torch.cuda.synchronize()
         print(json.dumps({"profile_only": spec["name"], "plan": moe.plan(state, T), "status": moe.read_status(state)}))
         return
 
-    head = measure(moe, inputs, state, spec, args.steps, args.warmup, peaks, dev, flush)
+    head = measure(moe, inputs, state, spec, args.steps, args.warmup, peaks, dev, flush_fn)
     sweep = []
     for w in sweep_specs:
         n = max(5, min(args.steps, 20 if w["T"] > 1024 else 100))
-        sweep.append(measure(moe, inputs, state, w, n, min(args.warmup, 5), peaks, dev, flush))
+        sweep.append(measure(moe, inputs, state, w, n, min(args.warmup, 5), peaks, dev, flush_fn))
     cpu_base, _ = cpu_oracle_run(spec, 2, cpu_sample_tokens(spec))
 
     line = {
@@ -402,7 +405,8 @@ def run_gpu(args, spec):
         "warmup": max(args.warmup, 3), "ms_per_step": head["ms_per_step"], "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": DTYPE, "data": "synthetic",
         "config": {"workload": spec["name"], "tokens": T, "hidden": H, "inter": I, "experts": E, "top_k": k,
-                   "l2": "flushed by a 256 MiB write before every timed step; CUDA-graph replays"},
+                   "l2": ("flushed before every timed step by " + ("zeroing" if args.flush == "write" else "reading")
+                          + " a 256 MiB buffer; CUDA-graph replays")},
         "plan": dict(head["plan"], workspace_bytes=state["workspace_bytes"], build_id=_lib.build_id()),
         "e2e": head["e2e"],
         "gpu_launches": head["gpu_launches_per_step"] * args.steps,
@@ -566,6 +570,7 @@ def main():
     ap.add_argument("--ep-chunks", type=int, default=0, help="expert-parallel runs: chunks of source ranks (0 = default)")
     ap.add_argument("--token-tile", type=int, default=0, help="force a kernel: 16/32/64/128, 8 = the mma.sync single-launch kernel")
     ap.add_argument("--decode-path", type=int, default=0, help="few tokens: 0 one launch, 1 chain of launches, 2 three launches")
+    ap.add_argument("--flush", default="read", choices=["read", "write"], help="how L2 is flushed before a timed step")
     ap.add_argument("--profile-only", action="store_true", help="run warmup+steps eager steps and exit (for ncu)")
     args = ap.parse_args()
     spec = workload_spec(args.workload, args.gpus)

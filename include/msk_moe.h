@@ -59,9 +59,10 @@ typedef struct MskMoeCfg {
                             weight stream, and so the order in which a cut unit's partial sums are added, follow
                             this number and the shapes, never the device */
   int32_t decode_path;   /* steps of few tokens (n_tokens <= 32, n_tokens * top_k <= 256, token tile <= 32):
-                            0 = one launch (routing, sort, both GEMMs and the combine in one kernel),
+                            0 = chosen by token count (one launch up to 8 tokens, the chain beyond),
                             1 = the chain of launches used for many tokens,
-                            2 = row copy, gate/up kernel that routes and sorts, down kernel that combines */
+                            2 = row copy, gate/up kernel that routes and sorts, down kernel that combines,
+                            3 = one launch (routing, sort, both GEMMs and the combine in one kernel) */
   int32_t no_pdl;        /* non-zero: launches are not chained with programmatic dependent launch (the reference's
                             okc_set_pdl(0), muse_moe_w4a16/cuda/moe.cu:2348,2565) */
   int32_t token_tile;    /* MMA N (tokens per tile): 16/32/64/128, or 8 = the single-launch kernel for
@@ -69,6 +70,8 @@ typedef struct MskMoeCfg {
   int32_t max_tokens;    /* token capacity the workspace is sized for (msk_moe_forward rejects more) */
   int32_t trace;         /* non-zero: the GEMM kernels stamp %globaltimer per CTA into the workspace (view 6) */
   int32_t stop_after;    /* measuring aid: 0 = whole step; 1/2/3 = return after sort / gate-up GEMM / down GEMM */
+  int32_t flat_shares;   /* non-zero (with n_tokens * top_k <= 256 and paths 1, 2): the last rounds of the weight stream
+                            are cut into equal shares per CTA instead of whole units (see msk_moe_share_pieces) */
 } MskMoeCfg;
 
 /* ---- prepare-time repack (lossless; replaces the four layouts built by
@@ -201,18 +204,20 @@ int msk_moe_static_status(int* host_status, void* stream);
 int msk_moe_plan(const MskMoeCfg* cfg, int n_tokens, int* host_out);
 
 /* How the GEMM kernels deal their work (host-side twin of the device code, a test hook): the pieces
- * that CTA `cta` of `shares` gets from n_base base units of n_stages K stages each. mode 0: whole
- * units round-robin (token tile 128), 1: whole units in contiguous ranges, 2: equal shares of the
- * flat (unit, stage) list. host_out receives six ints per piece: base unit, first stage, end stage,
- * slot of the partial buffer (-1 for a whole unit), first and last CTA holding a piece of the unit.
- * The reference's counterpart is its cost-weighted range scheduler (muse_moe_w4a16/cuda/moe.cu:2245-2289). */
-int msk_moe_share_pieces(int n_base, int n_stages, int shares, int mode, int cta, int* host_out, int capacity,
-                         int* host_count);
+ * that CTA `cta` of `shares` gets from n_base base units of n_stages K stages each. flat == 0: whole
+ * units, round-robin; flat != 0: equal shares of the flat (unit, stage) list. host_out receives six
+ * ints per piece: base unit, first stage, end stage, slot of the partial buffer (-1 for a whole
+ * unit), first and last CTA that can hold a piece of the unit. heavy / skip (whole units only): the
+ * first `heavy` CTAs are left out of the first `skip` rounds, which is how the one-launch kernel deals
+ * its down-GEMM units when those CTAs hold one more gate/up unit. The reference's counterpart is its
+ * cost-weighted range scheduler (muse_moe_w4a16/cuda/moe.cu:2245-2289). */
+int msk_moe_share_pieces(int n_base, int n_stages, int shares, int flat, int cta, int heavy, int skip, int* host_out,
+                         int capacity, int* host_count);
 
 /* Views into the workspace after msk_moe_forward (device pointers, for parity tests):
  * which: 0 cnt, 1 off, 2 perm, 3 inv, 4 inter (fp16 [R, I], holding bf16-rounded values), 5 y (fp32 [R, H]; bf16 [R, H] when the plan's
  * token tile is 128),
- * 6 trace (uint64 [2 GEMMs][256 CTAs][16 stamps], ns; written when cfg->trace != 0). */
+ * 6 trace (uint64 [2 launches][256 CTAs x 16 stamps, then 6 x 128 event words], ns; written when cfg->trace != 0). */
 int msk_moe_workspace_view(const MskMoeCfg* cfg, void* workspace, int which, void** host_ptr);
 
 /* Copies workspace word 0 to *host_status after synchronising `stream`. 0 = no device-side
@@ -241,6 +246,11 @@ int msk_ep_combine(const void* back, const void* self_rows, int self_rank, const
  * peer is certain to issue, and run under a host-side time-out. No counterpart in the reference. */
 int msk_ep_flag_write(void* addr, uint32_t value, void* stream);
 int msk_ep_flag_wait(void* addr, uint32_t value, void* stream);
+
+/* Cold-cache timing aid: reads `bytes` of `buf` (more than the L2 capacity) with ordinary loads so that
+ * L2 ends up holding clean lines of the buffer and nothing of the step to be timed; the reference's
+ * read sweep (muse_decode_layer/py/05_tune.py:74-94, muse_moe_w4a16/py/04_diag.py:24-49). */
+int msk_l2_sweep(const void* buf, size_t bytes, uint32_t* sink, void* stream);
 
 /* Hash of the source files this library was built from (set by the build script); the Python
  * binding compares it with the sources beside it and refuses a stale binary. */

@@ -24,23 +24,25 @@
 // One kernel template, three modes: MODE 0 runs phase 0, MODE 1 phase 1 (two launches chained by
 // programmatic dependent launch, any token count), MODE 2 both phases in one launch for a few tokens:
 // the weight stream, the dequant ring and the MMA pipeline run on from the last gate/up stage into
-// the first down stage without draining; only the activation gather of phase 1 waits, on a grid-wide
-// counter, until every CTA has written its rows of `inter` (the reference's single persistent kernel
-// hands over the same way, muse_moe_w4a16/cuda/moe.cu:2340-2768). MODE 2 also routes, sorts and
+// the first down stage without draining; only the activation gather of phase 1 waits, per token tile,
+// until the gate/up units of that tile have all written their columns of `inter` (the reference's single
+// persistent kernel hands over per job in the same way, with no barrier between its phases:
+// muse_moe_w4a16/cuda/moe.cu:690,1895,2020). MODE 2 also routes, sorts and
 // converts the token rows itself and ends with the folded combine: the step is one launch.
 //
 // Work. A base unit is (token tile, pair); its reduction runs over K / 256 stages. The base units
-// are laid out as one flat list ordered (token tile, pair) and dealt to the CTAs in one of three ways
+// are laid out as one flat list ordered (token tile, pair) and dealt to the CTAs in one of two ways
 // (PieceIter below):
-//   flat   (few routed rows, token tiles up to 64): the list of (base unit, K stage) items is cut into
-//          gridDim.x equal contiguous shares, so every SM streams the same number of weight bytes
-//          whatever the number of units. A unit cut between CTAs is accumulated as "pieces": every
-//          piece stores its raw FP32 accumulators to a slot of the partial buffer and takes a ticket,
-//          the piece that draws the last ticket sums the pieces in ascending K order (the order never
-//          depends on arrival) and runs the epilogue. Cut points depend on the shapes, the number of
-//          token tiles and the grid size given by the host, not on the device;
-//   contiguous whole units (token tiles up to 64, many units): CTA c owns units [n c / G, n (c+1) / G);
-//   round-robin whole units (token tile 128).
+//   whole units, round-robin (unit u to CTA u % gridDim.x);
+//   flat shares (few routed rows, token tiles up to 64): full rounds of whole units as above, then
+//          the last full round together with the units left over as a list of (base unit, K stage)
+//          items cut into gridDim.x equal contiguous shares, so every SM streams the same number of
+//          weight bytes (with fewer units than CTAs nothing is cut). A unit cut between CTAs is
+//          accumulated as "pieces": every piece stores its raw FP32 accumulators to a slot of the
+//          partial buffer and takes a ticket, the piece that draws the last ticket sums the pieces in
+//          ascending K order (the order never depends on arrival) and runs the epilogue. Cut points
+//          depend on the shapes, the number of token tiles and the grid size given by the host, not
+//          on the device.
 // Accumulators are double-buffered in TMEM (N <= 64) so the epilogue of a piece overlaps the main
 // loop of the next.
 //
@@ -61,6 +63,7 @@
 namespace msk {
 
 constexpr int GEMM_THREADS = 768;
+static_assert(GEMM_THREADS / 32 == SMALL_ROUTE_WARPS, "one routing scratch row per warp");
 constexpr int TMEM_COLS = 512;
 constexpr int B_SBO = 4096;        // bytes between 8-token groups of the B tile (32 core matrices)
 constexpr int B_LBO = 128;         // bytes between K-adjacent core matrices
@@ -131,30 +134,36 @@ struct GemmParams {
   float* tw_out;
   int T, E, lo, mode;
   float route_scale;
-  // Phase 1 with fold != 0 (at most 32 tokens): the CTA that completes the last base unit of a token
-  // also does the token's weighted slot-order sum (the combine), so no combine launch follows.
+  // Phase 1 with fold != 0 (at most 32 tokens): the combine is done by the CTAs that complete a
+  // token's last contributions, so no combine launch follows. fold 1 (post-expert norm): per token, at
+  // the end of the kernel; fold 2 (no norm): per (token, pair of 256 output columns), in the epilogue.
   int fold;
   const float* tw;           // [T, top_k] routing weights
   __nv_bfloat16* out;        // [T, H]
-  int32_t* tok_tickets;      // [T], zero between launches
+  int32_t* tok_tickets;      // [T] (fold 1) or [T][pairs of phase 1] (fold 2), zero between launches
   float eps;                 // post-expert norm
-  // MODE 2: the token rows as given (BF16), converted to F16 into ph[0].act by all CTAs together, and
-  // the grid-wide counters: grid_bar[0] arrivals (one per CTA and stage), grid_bar[1] exits.
+  // MODE 2: the token rows as given (BF16), converted to F16 into ph[0].act by all CTAs together; the
+  // grid-wide counters grid_bar[0] (CTAs whose slice of the F16 rows is written) and grid_bar[1]
+  // (exits); and per token tile the number of finished gate/up units (tile_done) and of down units
+  // that have seen them all (tile_seen), which hand `inter` from phase 0 to phase 1 tile by tile.
   const __nv_bfloat16* x_bf16;
   unsigned int* grid_bar;
+  unsigned int* tile_done;
+  unsigned int* tile_seen;
 };
 
 // Trace slots (per CTA, nanoseconds): the counterpart of the reference's DBG(k) stamps
 // (muse_moe_w4a16/cuda/moe.cu:279-284).
 enum : int { TR_START = 0, TR_SETUP, TR_FIRST_BULK, TR_FIRST_RAW, TR_FIRST_AFULL, TR_FIRST_MMA, TR_FIRST_DFULL,
-              TR_FIRST_EPI_DONE, TR_LAST_DFULL, TR_END, TR_ROUTED, TR_FOLD_END };
+              TR_FIRST_EPI_DONE, TR_LAST_DFULL, TR_END, TR_ROUTED, TR_FOLD_END, TR_CONVERTED, TR_TOPK };
 #define MSK_TR(slot) do { if (p.trace != nullptr) p.trace[blockIdx.x * 16 + (slot)] = globaltimer_ns(); } while (0)
-// Detailed event list of CTA 0: role r (0 first dequant thread, 1 MMA issuer, 2 weight producer)
-// appends up to 256 stamps, each tagged with a small code in the low 8 bits, after the
+// Detailed event list of CTA 0: role r (0 first dequant thread, 1 MMA issuer, 2 weight producer, 3 first
+// epilogue thread, 4 gather warp)
+// appends up to 128 stamps, each tagged with a small code in the low 8 bits, after the
 // 256 x 16 per-CTA stamps.
 #ifdef MSK_TRACE_DETAIL
-#define MSK_TRD(role, idx, code) do { if (p.trace != nullptr && blockIdx.x == 0 && (idx) < 256) { \
-  p.trace[256 * 16 + (role) * 256 + (idx)] = (globaltimer_ns() << 8) | (code); ++(idx); } } while (0)
+#define MSK_TRD(role, idx, code) do { if (p.trace != nullptr && blockIdx.x == MSK_TRACE_DETAIL && (idx) < 128) { \
+  p.trace[256 * 16 + (role) * 128 + (idx)] = (globaltimer_ns() << 8) | (code); ++(idx); } } while (0)
 #else
 #define MSK_TRD(role, idx, code) do { (void)(idx); } while (0)
 #endif
@@ -169,7 +178,7 @@ struct GemmCtrl {
   uint32_t tmem_base;
   int abort_word;
   int n_tiles;
-  int last_flag;
+  int last_flag[2];
   int fin_n;                           // fold: tokens this CTA has to combine when its units are done
   uint8_t fin_tok[FOLD_MAX_TOKENS];
   uint8_t klocal[FOLD_MAX_TOKENS];     // fold: local routes of each token
@@ -204,58 +213,99 @@ __device__ __forceinline__ UnitInfo decode_unit(int base, const int* tile_start,
 }
 
 // ---- work distribution (see the header comment). Positions are indices into the flat list of
-// (base unit, K stage) items: pos = base * nst + ks.
-__host__ __device__ inline long long share_begin(long long items, int shares, int c) {
-  return items * c / shares;
+// (base unit, K stage) items: pos = base * nst + ks. 32-bit arithmetic throughout (the host only
+// plans flat shares while items * shares fits; a 64-bit divide is a subroutine call, and on a
+// one-token step every cold instruction line counts).
+__host__ __device__ inline int share_begin(int items, int shares, int c) {
+  return static_cast<int>(static_cast<unsigned>(items) * static_cast<unsigned>(c) / static_cast<unsigned>(shares));
 }
 // The share that holds item x: the largest c with share_begin(c) <= x.
-__host__ __device__ inline int share_owner(long long items, int shares, long long x) {
-  return static_cast<int>(((x + 1) * shares - 1) / items);
+__host__ __device__ inline int share_owner(int items, int shares, int x) {
+  return static_cast<int>((static_cast<unsigned>(x + 1) * static_cast<unsigned>(shares) - 1u) / static_cast<unsigned>(items));
 }
 // Slot of the partial buffer for the piece of a cut unit that share c holds: a share holds at most
 // one piece that starts inside a unit (at the head of its range, slot 2c) and at most one that starts
 // a unit but does not finish it (at the tail of its range, slot 2c + 1).
 __host__ __device__ inline int piece_slot(int c, bool starts_unit) { return 2 * c + (starts_unit ? 1 : 0); }
+constexpr long long FLAT_MAX_PRODUCT = 1ll << 31;   // items * shares must stay below this for flat shares
 
+// Whole units first, round-robin (unit u to CTA u % shares, the order in which the weights lie in
+// memory: at any time the CTAs stream neighbouring units), as long as full rounds can be dealt; with
+// flat shares the units that are left over (fewer than there are CTAs) are then cut into equal
+// contiguous shares of (unit, stage) items. Measured on B200: dealing all units as contiguous
+// per-CTA ranges instead streams about 6 % slower than round-robin.
 struct PieceIter {
-  long long pos, end;
-  int nst;
-  int rr_step;  // > 0: whole units, round-robin with this stride
+  int a_pos, a_end, a_step;     // whole units, first round-robin sequence (see make_piece_iter)
+  int rr_pos, rr_end, rr_step;  // whole units, round-robin over all CTAs
+  int pos, end;                 // flat positions inside the tail: (base - tail_base) * nst + ks
+  int nst, tail_base;
   __host__ __device__ bool next(int& base, int& ks0, int& ks1) {
-    if (pos >= end) return false;
-    base = static_cast<int>(pos / nst);
-    ks0 = static_cast<int>(pos - static_cast<long long>(base) * nst);
-    if (rr_step > 0) {
+    if (a_pos < a_end) {
+      base = a_pos;
+      ks0 = 0;
       ks1 = nst;
-      pos += static_cast<long long>(rr_step) * nst;
+      a_pos += a_step;
       return true;
     }
-    const long long left = end - pos;
-    const int len = left < static_cast<long long>(nst - ks0) ? static_cast<int>(left) : nst - ks0;
+    if (rr_pos < rr_end) {
+      base = rr_pos;
+      ks0 = 0;
+      ks1 = nst;
+      rr_pos += rr_step;
+      return true;
+    }
+    if (pos >= end) return false;
+    const int b = pos / nst;
+    base = tail_base + b;
+    ks0 = pos - b * nst;
+    const int left = end - pos;
+    const int len = left < nst - ks0 ? left : nst - ks0;
     ks1 = ks0 + len;
     pos += len;
     return true;
   }
 };
 
-// mode 0: round-robin whole units; 1: contiguous whole units; 2: flat equal shares
-__host__ __device__ inline PieceIter make_piece_iter(int mode, int n_base, int nst, int c, int shares) {
+// First unit of the flat tail: the units before it are dealt whole. The tail is the last full round
+// plus the left-over units, so that a share holds at least one unit's worth of stages and a unit is cut
+// into two or three pieces at most. With fewer units than CTAs nothing is cut: a cut unit pays for its
+// pieces' round trips through L2 (store, fence, ticket, reload: several microseconds, about seven K
+// stages of streaming), more than the idle CTAs of a single round cost.
+__host__ __device__ inline int tail_begin(int flat, int n_base, int shares) {
+  if (!flat || n_base < shares) return n_base;
+  return (n_base / shares - 1) * shares;
+}
+
+// heavy / skip (one launch for both phases, phase 1 only): the first `heavy` CTAs hold one more unit
+// of phase 0 than the others, so the first `skip` rounds of phase 1 are dealt to the other CTAs only;
+// skip is that extra unit's cost in units of phase 1. With heavy == 0 every unit u goes to CTA u % shares.
+__host__ __device__ inline PieceIter make_piece_iter(int flat, int n_base, int nst, int c, int shares, int heavy = 0,
+                                                     int skip = 0) {
   PieceIter it;
   it.nst = nst;
-  it.rr_step = 0;
-  if (mode == 0) {
-    it.pos = static_cast<long long>(c) * nst;
-    it.end = static_cast<long long>(n_base) * nst;
-    it.rr_step = shares;
-  } else if (mode == 1) {
-    it.pos = share_begin(n_base, shares, c) * nst;
-    it.end = share_begin(n_base, shares, c + 1) * nst;
-  } else {
-    const long long items = static_cast<long long>(n_base) * nst;
-    it.pos = share_begin(items, shares, c);
-    it.end = share_begin(items, shares, c + 1);
-  }
+  it.tail_base = tail_begin(flat, n_base, shares);
+  const int light = shares - heavy;
+  int n_a = (heavy > 0 && !flat) ? skip * light : 0;
+  if (n_a > n_base) n_a = n_base;
+  it.a_pos = c >= heavy ? c - heavy : n_a;
+  it.a_end = n_a;
+  it.a_step = light;
+  it.rr_pos = n_a + c;
+  it.rr_end = it.tail_base;
+  it.rr_step = shares;
+  const int items = (n_base - it.tail_base) * nst;
+  it.pos = share_begin(items, shares, c);
+  it.end = share_begin(items, shares, c + 1);
   return it;
+}
+
+// The (heavy, skip) pair of phase 1 in the one-launch kernel, from the unit count and stage count of phase 0.
+__host__ __device__ inline void phase1_skew(int n_base0, int nst0, int nst1, int shares, int& heavy, int& skip) {
+  // With less than one full round of phase 0 nothing is skewed: every tile then completes at the same
+  // time, the CTAs without a gate/up unit cannot start phase 1 any earlier, and plain round-robin
+  // spreads it best.
+  heavy = n_base0 >= shares ? n_base0 % shares : 0;
+  skip = heavy > 0 ? (nst0 + nst1 / 2) / nst1 : 0;
 }
 
 __device__ __forceinline__ float silu_f(float g) { return g / (1.0f + __expf(-g)); }
@@ -321,67 +371,64 @@ __device__ __forceinline__ void epilogue_columns(const GemmParams& p, const Phas
 // (muse_moe_w4a16/cuda/moe.cu:2604-2766). Run by all threads of the CTA that retired the token's
 // last base unit, after its own units are done. The rows come from other CTAs: they are read with
 // L2 loads after the ticket that ordered them. Sums of squares: per-thread partials in a fixed column
-// order, a fixed shuffle tree, then the warp partials in warp order.
-__device__ __noinline__ void fold_combine_token(const GemmParams& p, int t, float* red /* [GEMM_THREADS / 32][MAX_TOP_K] */) {
+// order, a fixed shuffle tree, then the warp partials in warp order. Plain loops on purpose (compact
+// code: this runs once, from a cold instruction cache, at the very end of a one-token step).
+struct FoldScratch {
+  float red[GEMM_THREADS / 32][MAX_TOP_K];
+  float wgt[MAX_TOP_K];
+  int q[MAX_TOP_K];
+  int nv;
+};
+
+__device__ __noinline__ void fold_combine_token(const GemmParams& p, int t, FoldScratch& fs) {
   constexpr int NW = GEMM_THREADS / 32;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int H = p.ph[1].out_ld, k = p.top_k, n4 = H / 4;
   const float* y = static_cast<const float*>(p.ph[1].outp);
-  int q[MAX_TOP_K];
-  float wgt[MAX_TOP_K];
-  int nv = 0;
-#pragma unroll
-  for (int s = 0; s < MAX_TOP_K; ++s) {   // squeeze out the slots without a local expert, keeping their order
-    q[s] = 0;
-    wgt[s] = 0.f;
-  }
-#pragma unroll
-  for (int s = 0; s < MAX_TOP_K; ++s) {
-    if (s < k) {
-      const int qq = __ldcg(p.inv + t * k + s);
-      if (qq >= 0) {
-        const float w = __ldcg(p.tw + t * k + s);
-#pragma unroll
-        for (int j = 0; j < MAX_TOP_K; ++j)
-          if (j == nv) { q[j] = qq; wgt[j] = w; }
-        ++nv;
-      }
+  if (warp == 0) {   // lane s takes slot s; a ballot squeezes out the slots without a local expert, keeping their order
+    const int qq = lane < k ? __ldcg(p.inv + t * k + lane) : -1;
+    const float w = lane < k ? __ldcg(p.tw + t * k + lane) : 0.f;
+    const unsigned have = __ballot_sync(0xffffffffu, qq >= 0);
+    if (qq >= 0) {
+      const int at = __popc(have & ((1u << lane) - 1u));
+      fs.q[at] = qq;
+      fs.wgt[at] = w;
     }
+    if (lane == 0) fs.nv = __popc(have);
   }
+  __syncthreads();
+  const int nv = fs.nv;
   if (p.post_norm_w != nullptr) {
-#pragma unroll
-    for (int s = 0; s < MAX_TOP_K; ++s) {
-      if (s < nv) {
-        const float4* row = reinterpret_cast<const float4*>(y + static_cast<size_t>(q[s]) * H);
-        float ss = 0.f;
-        for (int i = tid; i < n4; i += GEMM_THREADS) {
-          const float4 f = __ldcg(row + i);
-          ss += f.x * f.x + f.y * f.y + f.z * f.z + f.w * f.w;
-        }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-        if (lane == 0) red[warp * MAX_TOP_K + s] = ss;
+#pragma unroll 1
+    for (int s = 0; s < nv; ++s) {
+      const float4* row = reinterpret_cast<const float4*>(y + static_cast<size_t>(fs.q[s]) * H);
+      float ss = 0.f;
+#pragma unroll 1
+      for (int i = tid; i < n4; i += GEMM_THREADS) {
+        const float4 f = __ldcg(row + i);
+        ss += f.x * f.x + f.y * f.y + f.z * f.z + f.w * f.w;
       }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      if (lane == 0) fs.red[warp][s] = ss;
     }
     __syncthreads();
-#pragma unroll
-    for (int s = 0; s < MAX_TOP_K; ++s) {
-      if (s < nv) {
-        float tot = 0.f;
-        for (int w = 0; w < NW; ++w) tot += red[w * MAX_TOP_K + s];  // fixed order
-        wgt[s] *= rsqrtf(tot / static_cast<float>(H) + p.eps);
-      }
+    if (tid < nv) {
+      float tot = 0.f;
+#pragma unroll 1
+      for (int w = 0; w < NW; ++w) tot += fs.red[w][tid];  // fixed order
+      fs.wgt[tid] *= rsqrtf(tot / static_cast<float>(H) + p.eps);
     }
-    __syncthreads();  // red is reused by the next token
+    __syncthreads();
   }
+#pragma unroll 1
   for (int i = tid; i < n4; i += GEMM_THREADS) {
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-    for (int s = 0; s < MAX_TOP_K; ++s) {  // slot order
-      if (s < nv) {
-        const float4 f = __ldcg(reinterpret_cast<const float4*>(y + static_cast<size_t>(q[s]) * H) + i);
-        acc.x += f.x * wgt[s]; acc.y += f.y * wgt[s]; acc.z += f.z * wgt[s]; acc.w += f.w * wgt[s];
-      }
+#pragma unroll 4
+    for (int s = 0; s < nv; ++s) {  // slot order
+      const float4 f = __ldcg(reinterpret_cast<const float4*>(y + static_cast<size_t>(fs.q[s]) * H) + i);
+      const float w = fs.wgt[s];
+      acc.x += f.x * w; acc.y += f.y * w; acc.z += f.z * w; acc.w += f.w * w;
     }
     const __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
     uint2 pk;
@@ -389,6 +436,7 @@ __device__ __noinline__ void fold_combine_token(const GemmParams& p, int t, floa
     pk.y = *reinterpret_cast<const uint32_t*>(&hi);
     *reinterpret_cast<uint2*>(p.out + static_cast<size_t>(t) * H + static_cast<size_t>(i) * 4) = pk;
   }
+  __syncthreads();  // the scratch is reused by the next token
 }
 
 // Bounded wait until a grid-wide counter has reached `target` (MODE 2). Called by one lane.
@@ -452,7 +500,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) moe_gemm_kernel(const __grid_
     }
     mbar_init(&ctl.epi_bar, 128);
     ctl.abort_word = 0;
-    ctl.last_flag = 0;
+    ctl.last_flag[0] = ctl.last_flag[1] = 0;
     ctl.fin_n = 0;
     fence_mbar_init();
   }
@@ -484,20 +532,24 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) moe_gemm_kernel(const __grid_
       dst[i] = make_uint4(bf16x2_to_f16x2(v.x), bf16x2_to_f16x2(v.y), bf16x2_to_f16x2(v.z), bf16x2_to_f16x2(v.w));
     }
     __threadfence();
+    if (tid == 0) MSK_TR(TR_CONVERTED);
   }
   if (routed_here) {
     // top-k (route 1) or the given ids (route 2), then the stable sort, redundantly in every CTA; the
     // scratch lives in the ring, which nothing has written yet
     SmallSortScratch& sc = *reinterpret_cast<SmallSortScratch*>(ring);
     const int n_entries = p.T * p.top_k;
-    if (p.route == 1) {
+    if (p.route == 1 && p.T * p.E <= SMALL_RANK_MAX_PAIRS && p.T * p.E * p.E <= SMALL_RANK_MAX_COMPARES) {
+      route_by_rank_cta(sc, p.logits, p.bias, p.T, p.E, p.top_k, p.mode, p.route_scale);
+    } else if (p.route == 1) {
       for (int t = warp; t < p.T; t += GEMM_THREADS / 32)
-        route_token_dispatch(p.logits + static_cast<size_t>(t) * p.E, p.bias, sc.ids + t * p.top_k,
-                             sc.tw + t * p.top_k, p.E, p.top_k, p.mode, p.route_scale, lane);
+        route_token_compact(p.logits + static_cast<size_t>(t) * p.E, p.bias, sc.key[warp], sc.raw[warp],
+                            sc.ids + t * p.top_k, sc.tw + t * p.top_k, p.E, p.top_k, p.mode, p.route_scale, lane);
     } else {
       for (int i = tid; i < n_entries; i += GEMM_THREADS) sc.ids[i] = p.ids_in[i];
     }
     __syncthreads();
+    if (tid == 0) MSK_TR(TR_TOPK);
     const bool writer = blockIdx.x == 0;
     if (writer && p.route == 1) {
       for (int i = tid; i < n_entries; i += GEMM_THREADS) {
@@ -550,7 +602,12 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) moe_gemm_kernel(const __grid_
     }
     if (i < p.T) {
       int kl = 0;
-      for (int s = 0; s < p.top_k; ++s) kl += __ldcg(p.inv + i * p.top_k + s) >= 0 ? 1 : 0;
+      if (FUSED) {   // the ids this CTA has just sorted are still in the scratch (nothing has written the ring yet)
+        const SmallSortScratch& sc = *reinterpret_cast<const SmallSortScratch*>(ring);
+        for (int s = 0; s < p.top_k; ++s) kl += local_expert(sc.ids[i * p.top_k + s], p.lo, p.nloc) >= 0 ? 1 : 0;
+      } else {
+        for (int s = 0; s < p.top_k; ++s) kl += __ldcg(p.inv + i * p.top_k + s) >= 0 ? 1 : 0;
+      }
       ctl.klocal[i] = static_cast<uint8_t>(kl);
       // a token without any local route is nobody's to finish: its output row is zero
       if (kl == 0 && static_cast<int>(blockIdx.x) == i % static_cast<int>(n_ctas)) {
@@ -562,18 +619,22 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) moe_gemm_kernel(const __grid_
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  if (FUSED && tid == 0) atomicAdd(p.grid_bar, 1u);  // stage 1: this CTA's slice of the F16 rows is in memory
+  if (FUSED && tid == 0) atomicAdd(p.grid_bar, 1u);  // this CTA's slice of the F16 rows is in memory
 
   const uint32_t tmem = ctl.tmem_base;
   if (tid == 0) MSK_TR(TR_SETUP);
-  const int iter_mode = N >= 128 ? 0 : (p.flat ? 2 : 1);
+  const int iter_mode = (N < 128 && p.flat) ? 1 : 0;
   volatile int* abortw = &ctl.abort_word;
 #define MSK_PHASES for (int phase = PH_FIRST; phase <= PH_LAST; ++phase)
 #define MSK_PHASE_SETUP                                                                                           \
   const PhaseParams& pp = p.ph[phase];                                                                            \
   const int nst_total = pp.K / KS;                                                                                \
   const int n_base = ctl.n_tiles * pp.n_pairs;                                                                    \
-  PieceIter pieces = make_piece_iter(iter_mode, n_base, nst_total, static_cast<int>(blockIdx.x), static_cast<int>(n_ctas)); \
+  int heavy_ = 0, skip_ = 0;                                                                                     \
+  if (FUSED && phase == 1) phase1_skew(ctl.n_tiles * p.ph[0].n_pairs, p.ph[0].K / KS, nst_total, static_cast<int>(n_ctas), heavy_, skip_); \
+  PieceIter pieces = make_piece_iter(iter_mode, n_base, nst_total, static_cast<int>(blockIdx.x), static_cast<int>(n_ctas), heavy_, skip_); \
+  const int tail_base = pieces.tail_base;                                                                         \
+  (void)tail_base;                                                                                                \
   int base, ks0, ks1;                                                                                             \
   (void)n_base
 
@@ -595,11 +656,12 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) moe_gemm_kernel(const __grid_
   __syncwarp();
   tc_fence_before();
   __syncthreads();
-  if (fold && ctl.abort_word == 0) {
+  if (fold && p.fold == 1 && ctl.abort_word == 0) {
     // the tokens whose last base unit this CTA retired (the ring is free by now: scratch for the sums)
-    float* red = reinterpret_cast<float*>(ring);
+    FoldScratch& fs = *reinterpret_cast<FoldScratch*>(ring);
     const int nf = ctl.fin_n;
-    for (int j = 0; j < nf; ++j) fold_combine_token(p, ctl.fin_tok[j], red);
+#pragma unroll 1
+    for (int j = 0; j < nf; ++j) fold_combine_token(p, ctl.fin_tok[j], fs);
     if (tid == 0) MSK_TR(TR_FOLD_END);
   }
   if (tid == 0) MSK_TR(TR_END);

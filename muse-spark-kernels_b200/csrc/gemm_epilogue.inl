@@ -8,25 +8,27 @@
     const int row = (warp & 3) * 32 + lane;
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
     uint32_t unit_i = 0, epi_par = 0;
+    int tri = 0;
+    (void)tri;
     if (MODE == 1) pdl_wait();  // y rows and tickets must not be touched before the previous grid is done
     bool ok = true;
     // bounded barrier over the 128 epilogue threads (a plain bar.sync could not time out)
     auto epi_sync = [&]() -> bool {
       mbar_arrive(&ctl.epi_bar);
-      const bool r = mbar_wait(&ctl.epi_bar, epi_par, abortw);
+      const bool r = mbar_wait_short(&ctl.epi_bar, epi_par, abortw);
       epi_par ^= 1u;
       return r;
     };
     constexpr size_t part_stride = static_cast<size_t>(2) * 128 * N;  // floats per piece
     MSK_PHASES {
       MSK_PHASE_SETUP;
-      const long long items = static_cast<long long>(n_base) * nst_total;
+      const int items = (n_base - tail_base) * nst_total;   // the flat tail, where units are cut
       for (; ok && pieces.next(base, ks0, ks1); ++unit_i) {
         const UnitInfo ui = decode_unit(base, tile_start, pp.n_pairs, p.nloc, N);
         const uint32_t db = unit_i % NDBUF, duse = unit_i / NDBUF;
         if (!mbar_wait(&ctl.d_full[db], duse & 1u, abortw)) { ok = false; break; }
         tc_fence_after();
-        if (tid == 128) { if (unit_i == 0) MSK_TR(TR_FIRST_DFULL); MSK_TR(TR_LAST_DFULL); }
+        if (tid == 128) { if (unit_i == 0) MSK_TR(TR_FIRST_DFULL); MSK_TR(TR_LAST_DFULL); MSK_TRD(3, tri, 1); }
         const uint32_t d_tmem = tmem + lane_base + db * (2 * N);
         const float gsc = pp.gs[ui.expert];
         const bool whole = ks0 == 0 && ks1 == nst_total;
@@ -52,9 +54,10 @@
           __syncwarp();
           if (lane == 0) mbar_arrive(&ctl.d_empty[db]);
           __threadfence();
+          if (tid == 128) MSK_TRD(3, tri, 2);
           if (!epi_sync()) { ok = false; break; }
           // the shares that hold a piece of this unit: first and last owner of its K stages
-          const long long b0 = static_cast<long long>(base) * nst_total;
+          const int b0 = (base - tail_base) * nst_total;
           c_first = share_owner(items, static_cast<int>(n_ctas), b0);
           c_last = share_owner(items, static_cast<int>(n_ctas), b0 + nst_total - 1);
           if (tid == 128) {
@@ -67,88 +70,70 @@
             const int last = (old == n_pieces - 1) ? 1 : 0;
             if (last) pp.tickets[base] = 0;  // leave the workspace launch-ready
             __threadfence();
-            ctl.last_flag = last;
+            ctl.last_flag[unit_i & 1u] = last;   // two words in turn: the next piece writes the other one
           }
+          if (tid == 128) MSK_TRD(3, tri, 3);
           if (!epi_sync()) { ok = false; break; }
-          finish = ctl.last_flag != 0;
-          if (!epi_sync()) { ok = false; break; }  // last_flag is rewritten by the next piece
+          finish = ctl.last_flag[unit_i & 1u] != 0;
+          if (tid == 128) MSK_TRD(3, tri, 4);
         }
         if (finish) {
-          const long long b0 = static_cast<long long>(base) * nst_total;
-          if (phase == 0) {
-            __half* outp = static_cast<__half*>(pp.outp);
-            const int col = ui.pair * 128 + row;
-            for (int c0 = 0; c0 < N; c0 += 8) {
-              if (c0 >= ui.rows) break;
-              float ga[8], up[8];
-              if (!whole) {
+          // (a cut unit: the pieces' partial accumulators are summed in ascending K order; plain loops on
+          // purpose: this path runs once or twice per launch from a cold instruction cache, where every
+          // extra line of code costs more than the loads it could overlap)
+          const int b0 = (base - tail_base) * nst_total;
+          const int col0 = phase == 0 ? ui.pair * 128 + row : (2 * ui.pair) * 128 + row;
+          float osc0 = gsc, osc1 = gsc;
+          if (phase == 1 && p.post_norm_w != nullptr) {
+            osc0 *= 1.0f + __bfloat162float(p.post_norm_w[col0]);
+            osc1 *= 1.0f + __bfloat162float(p.post_norm_w[col0 + 128]);
+          }
+          for (int c0 = 0; c0 < N; c0 += 8) {
+            if (c0 >= ui.rows) break;
+            float a0[8], a1[8];   // tile 0 (gate, or the even row tile) and tile 1 (up, or the odd one)
+            if (!whole) {
 #pragma unroll
-                for (int j = 0; j < 8; ++j) { ga[j] = 0.f; up[j] = 0.f; }
-                for (int c = c_first; c <= c_last; ++c) {   // ascending K
-                  const long long sb = share_begin(items, static_cast<int>(n_ctas), c);
-                  if (share_begin(items, static_cast<int>(n_ctas), c + 1) <= sb) continue;  // an empty share
-                  const float* ps = pp.partial + static_cast<size_t>(piece_slot(c, sb <= b0)) * part_stride;
-                  const float4* pg = reinterpret_cast<const float4*>(ps + static_cast<size_t>(row) * N + c0);
-                  const float4* pu = reinterpret_cast<const float4*>(ps + (128 + static_cast<size_t>(row)) * N + c0);
-#pragma unroll
-                  for (int j = 0; j < 2; ++j) {
-                    const float4 a = __ldcg(pg + j), b = __ldcg(pu + j);
-                    ga[4 * j] += a.x; ga[4 * j + 1] += a.y; ga[4 * j + 2] += a.z; ga[4 * j + 3] += a.w;
-                    up[4 * j] += b.x; up[4 * j + 1] += b.y; up[4 * j + 2] += b.z; up[4 * j + 3] += b.w;
-                  }
-                }
-              } else {
-                uint32_t r0[8], r1[8];
-                tmem_ld8(d_tmem + c0, r0);
-                tmem_ld8(d_tmem + N + c0, r1);
-                tmem_wait_ld();
-#pragma unroll
-                for (int j = 0; j < 8; ++j) { ga[j] = __uint_as_float(r0[j]); up[j] = __uint_as_float(r1[j]); }
+              for (int j = 0; j < 8; ++j) { a0[j] = 0.f; a1[j] = 0.f; }
+#pragma unroll 1
+              for (int c = c_first; c <= c_last; ++c) {
+                const int sb = share_begin(items, static_cast<int>(n_ctas), c);
+                if (share_begin(items, static_cast<int>(n_ctas), c + 1) <= sb) continue;  // an empty share
+                const float* ps = pp.partial + static_cast<size_t>(piece_slot(c, sb <= b0)) * part_stride;
+                const float4* q0 = reinterpret_cast<const float4*>(ps + static_cast<size_t>(row) * N + c0);
+                const float4* q1 = reinterpret_cast<const float4*>(ps + (128 + static_cast<size_t>(row)) * N + c0);
+                const float4 x0 = __ldcg(q0), x1 = __ldcg(q0 + 1), y0 = __ldcg(q1), y1 = __ldcg(q1 + 1);
+                a0[0] += x0.x; a0[1] += x0.y; a0[2] += x0.z; a0[3] += x0.w;
+                a0[4] += x1.x; a0[5] += x1.y; a0[6] += x1.z; a0[7] += x1.w;
+                a1[0] += y0.x; a1[1] += y0.y; a1[2] += y0.z; a1[3] += y0.w;
+                a1[4] += y1.x; a1[5] += y1.y; a1[6] += y1.z; a1[7] += y1.w;
               }
+            } else {
+              uint32_t r0[8], r1[8];
+              tmem_ld8(d_tmem + c0, r0);
+              tmem_ld8(d_tmem + N + c0, r1);
+              tmem_wait_ld();
+#pragma unroll
+              for (int j = 0; j < 8; ++j) { a0[j] = __uint_as_float(r0[j]); a1[j] = __uint_as_float(r1[j]); }
+            }
+            if (phase == 0) {
+              __half* outp = static_cast<__half*>(pp.outp);
 #pragma unroll
               for (int j = 0; j < 8; ++j) {
                 const int n = c0 + j;
                 if (n < ui.rows) {
-                  const float v = silu_f(ga[j] * gsc) * (up[j] * gsc);
-                  outp[static_cast<size_t>(ui.row0 + n) * pp.out_ld + col] = inter_value(v);
+                  const float v = silu_f(a0[j] * gsc) * (a1[j] * gsc);
+                  outp[static_cast<size_t>(ui.row0 + n) * pp.out_ld + col0] = inter_value(v);
                 }
               }
-            }
-          } else {
-            float* outp = static_cast<float*>(pp.outp);
+            } else {
+              float* outp = static_cast<float*>(pp.outp);
 #pragma unroll
-            for (int t2 = 0; t2 < 2; ++t2) {
-              const int col = (2 * ui.pair + t2) * 128 + row;
-              float osc = gsc;
-              if (p.post_norm_w != nullptr) osc *= 1.0f + __bfloat162float(p.post_norm_w[col]);
-              for (int c0 = 0; c0 < N; c0 += 8) {
-                if (c0 >= ui.rows) break;
-                float acc[8];
-                if (!whole) {
-#pragma unroll
-                  for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-                  for (int c = c_first; c <= c_last; ++c) {   // ascending K
-                    const long long sb = share_begin(items, static_cast<int>(n_ctas), c);
-                    if (share_begin(items, static_cast<int>(n_ctas), c + 1) <= sb) continue;  // an empty share
-                    const float* ps = pp.partial + static_cast<size_t>(piece_slot(c, sb <= b0)) * part_stride;
-                    const float4* pq = reinterpret_cast<const float4*>(ps + (static_cast<size_t>(t2) * 128 + row) * N + c0);
-#pragma unroll
-                    for (int j = 0; j < 2; ++j) {
-                      const float4 a = __ldcg(pq + j);
-                      acc[4 * j] += a.x; acc[4 * j + 1] += a.y; acc[4 * j + 2] += a.z; acc[4 * j + 3] += a.w;
-                    }
-                  }
-                } else {
-                  uint32_t r[8];
-                  tmem_ld8(d_tmem + t2 * N + c0, r);
-                  tmem_wait_ld();
-#pragma unroll
-                  for (int j = 0; j < 8; ++j) acc[j] = __uint_as_float(r[j]);
-                }
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                  const int n = c0 + j;
-                  if (n < ui.rows) outp[static_cast<size_t>(ui.row0 + n) * pp.out_ld + col] = acc[j] * osc;
+              for (int j = 0; j < 8; ++j) {
+                const int n = c0 + j;
+                if (n < ui.rows) {
+                  float* orow = outp + static_cast<size_t>(ui.row0 + n) * pp.out_ld + col0;
+                  orow[0] = a0[j] * osc0;
+                  orow[128] = a1[j] * osc1;
                 }
               }
             }
@@ -159,33 +144,72 @@
           __syncwarp();
           if (lane == 0) mbar_arrive(&ctl.d_empty[db]);
         }
+        if (tid == 128) MSK_TRD(3, tri, 5);
+        if (FUSED && phase == 0) {
+          // one launch: this unit's columns of inter are complete; count it for its token tile, whose down
+          // units wait for the count to reach the number of gate/up pairs
+          __threadfence();
+          if (!epi_sync()) { ok = false; break; }
+          if (finish && tid == 128) { atomicAdd(p.tile_done + ui.tile, 1u); MSK_TRD(3, tri, 7); }
+        }
         if (fold && phase == 1) {
-          // Token tickets: a base unit that has just been finished counts once for every token that has a
-          // row in it. The CTA that brings a token's ticket to (its local routes) x (pairs) has seen the
-          // token's last unit and puts it on its list for the folded combine.
+          // Tickets: a base unit that has just been finished counts once for every token that has a row in
+          // it. With the post-expert norm a token can only be combined when all of its rows are complete
+          // (the norm needs whole rows): one ticket per token, target (local routes) x (pairs); the CTA
+          // that draws the last one puts the token on its list for the folded combine at the end of the
+          // kernel. Without the norm the 256 output columns of this pair only need the same columns of the
+          // token's other rows: one ticket per (token, pair), target (local routes), and the epilogue
+          // threads of the CTA that draws the last one combine those columns right here.
           __threadfence();
           if (!epi_sync()) { ok = false; break; }
           const int j = tid - 128;
+          const bool by_column = p.fold == 2;
           if (finish && j < ui.rows) {
             const int t = static_cast<int>(ctl.perm8[ui.row0 + j]) / p.top_k;
-            const int want = static_cast<int>(ctl.klocal[t]) * pp.n_pairs;
-            const int old = atomicAdd(&p.tok_tickets[t], 1);
+            const int want = by_column ? static_cast<int>(ctl.klocal[t]) : static_cast<int>(ctl.klocal[t]) * pp.n_pairs;
+            int32_t* ticket = p.tok_tickets + (by_column ? t * pp.n_pairs + ui.pair : t);
+            const int old = atomicAdd(ticket, 1);
             if (old == want - 1) {
-              p.tok_tickets[t] = 0;  // launch-ready again
+              *ticket = 0;  // launch-ready again
               __threadfence();
               const int at = atomicAdd(&ctl.fin_n, 1);
               if (at < FOLD_MAX_TOKENS) ctl.fin_tok[at] = static_cast<uint8_t>(t);
             }
           }
+          if (tid == 128) MSK_TRD(3, tri, 6);
+          if (by_column) {
+            if (!epi_sync()) { ok = false; break; }
+            const int nf = finish ? ctl.fin_n : 0;
+            const int H = pp.out_ld, col0 = (2 * ui.pair) * 128 + row;
+            const float* yb = static_cast<const float*>(pp.outp);
+#pragma unroll 1
+            for (int f = 0; f < nf; ++f) {
+              const int t = ctl.fin_tok[f];
+              // lane s fetches slot s of the token; the sums below run in slot order
+              const int qv = lane < p.top_k ? __ldcg(p.inv + t * p.top_k + lane) : -1;
+              const float wv = lane < p.top_k ? __ldcg(p.tw + t * p.top_k + lane) : 0.f;
+              float a0 = 0.f, a1 = 0.f;
+#pragma unroll 8
+              for (int sl = 0; sl < p.top_k; ++sl) {
+                const int q = __shfl_sync(0xffffffffu, qv, sl);
+                const float w = __shfl_sync(0xffffffffu, wv, sl);
+                if (q >= 0) {
+                  const float* yr = yb + static_cast<size_t>(q) * H + col0;
+                  a0 += __ldcg(yr) * w;
+                  a1 += __ldcg(yr + 128) * w;
+                }
+              }
+              __nv_bfloat16* orow = p.out + static_cast<size_t>(t) * H + col0;
+              orow[0] = __float2bfloat16_rn(a0);
+              orow[128] = __float2bfloat16_rn(a1);
+            }
+            if (!epi_sync()) { ok = false; break; }   // the list is read by all before it is emptied
+            if (tid == 128) ctl.fin_n = 0;
+            if (tid == 128) MSK_TRD(3, tri, 8);
+          }
         }
         if (tid == 128 && unit_i == 0) MSK_TR(TR_FIRST_EPI_DONE);
       }
       if (!ok) break;
-      if (FUSED && phase == 0) {
-        // stage 2 of the grid counter: every row of inter this CTA had to write is in memory
-        __threadfence();
-        if (!epi_sync()) { ok = false; break; }
-        if (tid == 128) atomicAdd(p.grid_bar, 1u);
-      }
     }
     }

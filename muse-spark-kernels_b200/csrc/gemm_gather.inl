@@ -11,6 +11,8 @@
     // copies it has just started (one stage of lag made every iteration a full memory latency).
     constexpr int GLAG = NST >= 5 ? 3 : (NST >= 4 ? 2 : 1);
     uint32_t it = 0, signalled = 0;
+    int tri = 0;
+    (void)tri;
     const uint64_t keep = policy_evict_last();  // token rows are re-read by every pair of the expert
     bool ok = true;
     // everything issued so far has landed: publish it
@@ -21,6 +23,7 @@
         __syncwarp();
         for (; signalled < it; ++signalled)
           if (lane == 0) mbar_arrive(&ctl.b_full[signalled % NST]);
+        if (lane == 0) MSK_TRD(4, tri, 5);
       }
     };
     MSK_PHASES {
@@ -29,15 +32,11 @@
       // F16 token rows, when the gate/up kernel routes itself, by the row-copy kernel launched in front
       // of it. One launch: every CTA's slice of the F16 rows (stage 1 of the grid counter), then every
       // CTA's rows of inter (stage 2).
-      if (FUSED) {
-        drain();
-        int go = 1;
-        if (lane == 0) go = grid_counter_wait(p.grid_bar, (phase + 1) * n_ctas, abortw) ? 1 : 0;
-        go = __shfl_sync(0xffffffffu, go, 0);
-        if (!go) { ok = false; break; }
-      } else if (MODE == 1 || routed_here) {
-        pdl_wait();
-      }
+      // (the wait itself sits below, in front of the first copy of the phase, after the addresses of
+      // that copy have been worked out)
+      bool must_wait = FUSED && phase == 0;
+      int last_tile = -1;
+      if (!FUSED && (MODE == 1 || routed_here)) pdl_wait();
       const size_t act_ld = static_cast<size_t>(pp.K);
       while (ok && pieces.next(base, ks0, ks1)) {
         const UnitInfo ui = decode_unit(base, tile_start, pp.n_pairs, p.nloc, N);
@@ -52,6 +51,33 @@
             size_t row = static_cast<size_t>(r);
             if (phase == 0) row = static_cast<size_t>((routed_here ? static_cast<int>(ctl.perm8[r]) : p.perm[r]) / p.top_k);
             src[ng] = static_cast<const __half*>(pp.act) + row * act_ld;
+          }
+        }
+        bool first_piece = false;
+        if (FUSED && (must_wait || (phase == 1 && ui.tile != last_tile))) {
+          // phase 0: every CTA's slice of the F16 token rows; phase 1: the gate/up units of this token
+          // tile. Everything issued so far is handed over first, so that the MMA warps never starve on
+          // copies that have long landed.
+          drain();
+          int go = 1;
+          if (lane == 0) {
+            go = phase == 0 ? grid_counter_wait(p.grid_bar, n_ctas, abortw)
+                            : grid_counter_wait(p.tile_done + ui.tile, static_cast<unsigned>(p.ph[0].n_pairs), abortw);
+          }
+          go = __shfl_sync(0xffffffffu, go, 0);
+          if (!go) { ok = false; break; }
+          if (lane == 0) MSK_TRD(4, tri, 1 + phase);
+          first_piece = must_wait || phase == 1;
+          must_wait = false;
+          last_tile = ui.tile;
+        }
+        if (FUSED && phase == 1 && lane == 0) {
+          // every down unit of the tile reports that it has seen the count complete; the last one puts both
+          // counters back to zero for the next launch
+          const unsigned seen = atomicAdd(p.tile_seen + ui.tile, 1u);
+          if (seen == static_cast<unsigned>(pp.n_pairs) - 1u) {
+            atomicExch(p.tile_done + ui.tile, 0u);
+            atomicExch(p.tile_seen + ui.tile, 0u);
           }
         }
         for (int ks = ks0; ks < ks1; ++ks, ++it) {
@@ -69,16 +95,22 @@
             }
           }
           cp_async_commit();
+          if (lane == 0) MSK_TRD(4, tri, 3);
           if (it + 1 - signalled > GLAG) {
             cp_async_wait<GLAG>();
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) mbar_arrive(&ctl.b_full[signalled % NST]);
             ++signalled;
+            if (lane == 0) MSK_TRD(4, tri, 4);
           }
         }
+        // right behind a wait on other CTAs the MMA warps may stand idle: hand the piece over as soon as it
+        // has landed instead of a few stages late
+        if (ok && first_piece) drain();
       }
       if (!ok) break;
+      // a CTA without work in this phase still takes part in nothing it has to wait for
     }
     drain();
     }

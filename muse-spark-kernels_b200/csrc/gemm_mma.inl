@@ -8,6 +8,8 @@
     const int mg = warp == 1 ? 0 : 1;  // warp 1 issues for tile 0, warp 3 for tile 1
     uint32_t it = 0, unit_i = 0, sc = 0;
     uint32_t as = 0, apar = 0;  // A ring position and its phase parity
+    int tri = 0;
+    (void)tri;
     bool ok = true;
     MSK_PHASES {
       MSK_PHASE_SETUP;
@@ -16,6 +18,7 @@
         const uint32_t db = unit_i % NDBUF, duse = unit_i / NDBUF;
         if (!mbar_wait(&ctl.d_empty[db], (duse & 1u) ^ 1u, abortw)) { ok = false; break; }
         tc_fence_after();
+        if (mg == 0 && lane == 0) MSK_TRD(1, tri, 3);
         const uint32_t d_tmem = tmem + db * (2 * N) + mg * N;
         // a ragged last token tile of an expert only pays for the columns it has (MMA N in steps of 16):
         // at N = 128 an MMA costs 64 cycles, at N = 16 nine
@@ -24,6 +27,7 @@
         for (int ks = ks0; ks < ks1 && ok; ++ks, ++it) {
           const uint32_t slot = it % NST, par = (it / NST) & 1u;
           if (!mbar_wait(&ctl.b_full[slot], par, abortw)) { ok = false; break; }
+          if (mg == 0 && lane == 0) MSK_TRD(1, tri, 1);
           const uint32_t b_addr = smem_u32(ring + slot * C::STAGE_BYTES + 2 * TILE_BYTES);
 #pragma unroll
           for (int sl = 0; sl < 2; ++sl, ++sc) {
@@ -50,6 +54,7 @@
         }
         if (ok && elect_one()) tc_commit(&ctl.d_full[db]);
         __syncwarp();
+        if (mg == 0 && lane == 0) MSK_TRD(1, tri, 2);
       }
       if (!ok) break;
     }

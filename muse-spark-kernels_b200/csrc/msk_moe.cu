@@ -4,6 +4,7 @@
 #include <algorithm>
 #include <cmath>
 #include <cstdint>
+#include <cstdlib>
 #include <cstring>
 
 #include <cuda_bf16.h>
@@ -12,7 +13,6 @@
 #include "../../include/msk_moe.h"
 #include "route_sort.cuh"
 #include "gemm.cuh"
-#include "small_tokens.cuh"
 
 namespace msk {
 
@@ -467,7 +467,8 @@ static int sm_count() {
 // depend on the configuration, not on the device the library happens to run on.
 constexpr int DEFAULT_CTAS = 148;
 constexpr int MAX_CTAS = 512;
-constexpr int FLAT_MAX_ROWS = SMALL_SORT_MAX_ENTRIES;  // up to here the weight stream is cut into equal shares
+constexpr int FLAT_MAX_ROWS = SMALL_SORT_MAX_ENTRIES;  // up to here the weight stream may be cut into equal shares
+constexpr int ONE_LAUNCH_MAX_TOKENS = 8;               // up to here the step is one launch by default
 
 struct Plan {
   int N;         // token tile
@@ -476,61 +477,11 @@ struct Plan {
   int grid;
 };
 
-// Few-token kernel: piece slots per output element. A share of the flat stage-tile list holds at
-// least `per` stage tiles, so a tile of nst stages meets at most ceil(nst / per) + 1 shares,
-// one piece per group of consumer warps each. The fewest stage tiles there can be is one expert's.
-static int small_pieces(int tiles, int nst, int grid) {
-  const int per = std::max(1, tiles * nst / std::max(grid, 1));
-  return ST_GROUPS * ((nst + per - 1) / per + 1);
-}
-constexpr int SMALL_MAX_PIECES = 64;  // bits of the slot mask
-
-static size_t small_part_floats(const MskMoeCfg* c) {
-  // sized for any grid: per = 1, capped at what the kernel accepts
-  const int p1 = std::min(ST_GROUPS * (c->hidden / KS + 1), SMALL_MAX_PIECES);
-  const int p2 = std::min(ST_GROUPS * (c->inter / KS + 1), SMALL_MAX_PIECES);
-  return static_cast<size_t>(ST_MAX_ROWS) * (static_cast<size_t>(p1) * 2 * c->inter + static_cast<size_t>(p2) * c->hidden);
-}
-
-constexpr size_t SMALL_SMEM_LIMIT = 227 * 1024;
-
-static size_t small_fixed_smem(const MskMoeCfg* c) {
-  return ST_OFF_ACT + static_cast<size_t>(ST_MAX_TOKENS) * (static_cast<size_t>(std::max(c->hidden, c->inter)) * 2 + 32);
-}
-
-// Ring slots: as many as fit, a multiple of the consumer groups (a slot always serves the same
-// group, which therefore sees every phase of the slot's barrier), at most 8.
-static int small_slots(const MskMoeCfg* c) {
-  const size_t fixed = small_fixed_smem(c);
-  if (fixed + ST_GROUPS * ST_SLOT_BYTES > SMALL_SMEM_LIMIT) return 0;
-  const int n = std::min(ST_MAX_SLOTS, static_cast<int>((SMALL_SMEM_LIMIT - fixed) / ST_SLOT_BYTES));
-  return n / ST_GROUPS * ST_GROUPS;
-}
-
-static size_t small_smem_bytes(const MskMoeCfg* c) {
-  return small_fixed_smem(c) + static_cast<size_t>(small_slots(c)) * ST_SLOT_BYTES;
-}
-
-// The few-token kernel takes the step when it fits: at most 8 tokens and 64 routed rows, the
-// piece slots within the mask, the activation rows within shared memory, the whole grid resident.
-static bool small_fits(const MskMoeCfg* c, int T, int grid) {
-  if (T > ST_MAX_TOKENS || T * c->top_k > ST_MAX_ROWS) return false;
-  if (small_pieces(2 * c->inter / 128, c->hidden / KS, grid) > SMALL_MAX_PIECES) return false;
-  if (small_pieces(c->hidden / 128, c->inter / KS, grid) > SMALL_MAX_PIECES) return false;
-  if (small_slots(c) < ST_GROUPS) return false;
-  return grid <= sm_count();
-}
-
 static Plan make_plan(const MskMoeCfg* c, int T) {
   Plan p;
   p.grid = c->num_ctas > 0 ? std::min(c->num_ctas, MAX_CTAS) : DEFAULT_CTAS;
   p.path = 1;
   p.flat = 0;
-  // on request only: the mma.sync single-launch kernel for up to 8 tokens
-  if (c->token_tile == 8 && small_fits(c, T, p.grid)) {
-    p.N = 8;
-    return p;
-  }
   if (c->token_tile > 0) {
     p.N = c->token_tile;
   } else {
@@ -541,19 +492,35 @@ static Plan make_plan(const MskMoeCfg* c, int T) {
     p.N = rpe <= 8 ? 16 : rpe <= 12 ? 32 : rpe <= 32 ? 64 : 128;
   }
   const long long rows = static_cast<long long>(T) * c->top_k;
-  p.flat = (rows <= FLAT_MAX_ROWS && p.N <= 64) ? 1 : 0;
+  // Flat shares are an option, off by default: measured on B200 a cut unit's pieces cost about 6 us of
+  // round trips through L2 at the end of each GEMM (store, fence, ticket, reload from a cold instruction
+  // cache), as much as the idle CTAs of the last round of whole units cost at these sizes.
+  p.flat = (c->flat_shares != 0 && rows <= FLAT_MAX_ROWS && p.N <= 64) ? 1 : 0;
+  {
+    // the kernels do the share arithmetic in 32 bits: items * shares has to fit
+    const long long pairs = std::max(c->inter / 128, c->hidden / 256), nst = std::max(c->hidden, c->inter) / KS;
+    if ((rows + 1) * pairs * nst * p.grid >= FLAT_MAX_PRODUCT) p.flat = 0;
+  }
   // few tokens: the kernels route, sort and combine themselves
   const bool few = rows <= SMALL_SORT_MAX_ENTRIES && T <= FOLD_MAX_TOKENS && p.N <= 32 && c->stop_after == 0;
   if (few) {
-    p.path = c->decode_path == 1 ? 1 : (c->decode_path == 2 ? 2 : 0);
+    // measured (H4096 I1536 E128 top-8, cold L2): one launch 47 / 64 / 89 / 136 us at 1 / 2 / 4 / 8 tokens
+    // against 57 / 72 / 94 / 135 for the chain; at 16 and 32 tokens 195 / 268 against 197 / 249
+    switch (c->decode_path) {
+      case 1: p.path = 1; break;
+      case 2: p.path = 2; break;
+      case 3: p.path = 0; break;
+      default: p.path = T <= ONE_LAUNCH_MAX_TOKENS ? 0 : 1; break;
+    }
     if (p.path == 0 && p.grid > sm_count()) p.path = 2;  // the one-launch kernel needs every CTA resident
+    if (p.path == 0) p.flat = 0;  // its phases hand over per token tile, which counts whole units
   }
   return p;
 }
 
 // Workspace carving. Everything is sized for max_tokens with the worst plan.
 struct Carve {
-  size_t status, trace, cnt, off, perm, inv, tickets, small_ctl, few_ctl, sort_blk, inter, y, partial, xs, small_part, total;
+  size_t status, trace, cnt, off, perm, inv, tickets, few_ctl, sort_blk, inter, y, partial, xs, total;
 };
 constexpr size_t TRACE_CTAS = 256;
 constexpr size_t TRACE_WORDS = TRACE_CTAS * 16 + 3 * 256;
@@ -586,15 +553,14 @@ static Carve carve(const MskMoeCfg* c, int T) {
   k.perm = o; o += round_up(R * 4, 256);
   k.inv = o; o += round_up(R * 4, 256);
   k.tickets = o; o += 2 * round_up(ticket_ints(c, T) * 4, 256);  // one region per GEMM
-  k.small_ctl = o; o += 1024;  // mma.sync few-token kernel: grid barrier (2 words), per-token tickets at +64, row weights at +256
-  k.few_ctl = o; o += 256;     // few-token paths of the GEMM kernel: token tickets [32] at +0, grid counters [2] at +128
+  k.few_ctl = o; o += 8192;    // few-token paths of the GEMM kernel: tickets [32 tokens][up to 32 pairs] at +0, grid counters [2] at
+                               // +4096, per-tile counters [2][up to 384 tiles] at +4352
   k.sort_blk = o; o += static_cast<size_t>(SORT_MULTI_BLOCKS) * MAX_LOCAL_EXPERTS * 4;  // per-CTA counts of the multi-CTA sort
   // everything above is control state: msk_moe_workspace_init zeroes [0, inter)
   k.inter = o; o += round_up(R * c->inter * 2, 256);
   k.y = o; o += round_up(R * c->hidden * 4, 256);
   k.partial = o; o += 2 * round_up(partial_floats(c) * 4, 256);  // one region per GEMM
   k.xs = o; o += round_up(R * c->hidden * 2, 256);  // F16 copy of the token rows ([T, H], or sorted [R, H] for wide token tiles)
-  k.small_part = o; o += round_up(small_part_floats(c) * 4, 256);  // pieces of the mma.sync few-token kernel
   k.total = o;
   return k;
 }
@@ -624,6 +590,15 @@ static int encode_act_map(CUtensorMap* map, const void* base, size_t rows, int K
   return r == CUDA_SUCCESS ? 0 : static_cast<int>(cudaErrorInvalidValue);
 }
 
+// Experiment switch (environment variable MSK_FUSED_PLAIN): launch the one-launch kernel without the
+// cooperative attribute. Its grid never exceeds the SM count and it holds an SM per CTA, so its CTAs
+// are resident together in practice, and its waits are bounded either way.
+static bool fused_plain_launch() {
+  static int v = -1;
+  if (v < 0) v = std::getenv("MSK_FUSED_PLAIN") != nullptr ? 1 : 0;
+  return v == 1;
+}
+
 // MODE 2 (one launch for the step) waits on a grid-wide counter, so it is launched cooperatively:
 // either every CTA is resident or the launch fails. The other modes are chained with programmatic
 // dependent launch (unless pdl == 0).
@@ -644,7 +619,7 @@ static int launch_gemm(const GemmParams& p, int grid, cudaStream_t st, int pdl) 
   lc.dynamicSmemBytes = GemmCfg<N>::SMEM_BYTES;
   lc.stream = st;
   cudaLaunchAttribute at[1];
-  if (MODE == 2) {
+  if (MODE == 2 && !fused_plain_launch()) {
     at[0].id = cudaLaunchAttributeCooperative;
     at[0].val.cooperative = 1;
   } else {
@@ -942,55 +917,6 @@ static int forward_impl(const MskMoeCfg* cfg, const void* packed13, const void* 
   __half* xs = reinterpret_cast<__half*>(b + k.xs);
 
   Plan plan = make_plan(cfg, n_tokens);
-  if (plan.N == 8) {
-    if (cfg->stop_after != 0 || pre_norm_w != nullptr) return MSK_ERR_SHAPE;  // the stage hooks and the pre-expert norm belong to the chain of launches  // the stage hooks belong to the chain of launches
-    SmallParams sp{};
-    sp.w13 = static_cast<const uint8_t*>(packed13); sp.w2 = static_cast<const uint8_t*>(packed2);
-    sp.gs13 = gs13; sp.gs2 = gs2; sp.post_norm_w = static_cast<const __nv_bfloat16*>(post_norm_w);
-    sp.x = static_cast<const __nv_bfloat16*>(x);
-    sp.ids_in = logits ? nullptr : topk_ids; sp.tw_in = logits ? nullptr : topk_weights;
-    sp.logits = logits; sp.bias = bias; sp.ids_out = ids_out; sp.tw_out = tw_out;
-    sp.out = static_cast<__nv_bfloat16*>(out);
-    sp.cnt = cnt; sp.off = off; sp.perm = perm; sp.inv = inv; sp.inter = inter; sp.y = y;
-    sp.P1 = small_pieces(2 * cfg->inter / 128, cfg->hidden / KS, plan.grid);
-    sp.P2 = small_pieces(cfg->hidden / 128, cfg->inter / KS, plan.grid);
-    sp.part1 = reinterpret_cast<float*>(b + k.small_part);
-    sp.part2 = sp.part1 + static_cast<size_t>(ST_MAX_ROWS) * sp.P1 * 2 * cfg->inter;
-    sp.bar = reinterpret_cast<unsigned int*>(b + k.small_ctl);
-    sp.tickets = reinterpret_cast<int32_t*>(b + k.small_ctl + 64);
-    sp.row_w = reinterpret_cast<float*>(b + k.small_ctl + 256);
-    sp.status = status;
-    sp.trace = (cfg->trace != 0 && plan.grid <= static_cast<int>(TRACE_CTAS))
-                   ? reinterpret_cast<unsigned long long*>(b + k.trace) : nullptr;
-    sp.H = cfg->hidden; sp.I = cfg->inter; sp.E = cfg->n_experts; sp.lo = cfg->local_start; sp.nloc = cfg->local_count;
-    sp.k = cfg->top_k; sp.T = n_tokens; sp.mode = cfg->routing_mode;
-    sp.route_scale = cfg->route_scale; sp.eps = cfg->post_norm_eps;
-    sp.slots = small_slots(cfg);
-    const size_t smem = small_smem_bytes(cfg);
-    static bool attr_set[64] = {false};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-      const cudaError_t ae = cudaFuncSetAttribute(moe_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                  static_cast<int>(SMALL_SMEM_LIMIT));
-      if (ae != cudaSuccess) return static_cast<int>(ae);
-      attr_set[dev] = true;
-    }
-    if (ev) { cudaEventRecord(ev[0], st); cudaEventRecord(ev[1], st); cudaEventRecord(ev[5], st); }
-    cudaLaunchConfig_t lc{};
-    lc.gridDim = dim3(static_cast<unsigned>(plan.grid));
-    lc.blockDim = dim3(ST_THREADS_ALL);
-    lc.dynamicSmemBytes = smem;
-    lc.stream = st;
-    cudaLaunchAttribute at[1];
-    at[0].id = cudaLaunchAttributeCooperative;   // every CTA resident: the grid barriers rely on it
-    at[0].val.cooperative = 1;
-    lc.attrs = at;
-    lc.numAttrs = 1;
-    const int le = static_cast<int>(cudaLaunchKernelEx(&lc, moe_small_kernel, sp));
-    if (ev) { cudaEventRecord(ev[2], st); cudaEventRecord(ev[3], st); cudaEventRecord(ev[4], st); }
-    return le;
-  }
   if (plan.N != 16 && plan.N != 32 && plan.N != 64 && plan.N != 128) return MSK_ERR_SHAPE;
   if (plan.grid < 1 || plan.grid > MAX_CTAS) return MSK_ERR_SHAPE;
   const int pdl = cfg->no_pdl ? 0 : 1;
@@ -1023,9 +949,11 @@ static int forward_impl(const MskMoeCfg* cfg, const void* packed13, const void* 
     p.logits = logits; p.bias = bias; p.ids_in = topk_ids; p.ids_out = ids_out; p.tw_out = tw_out;
     p.T = n_tokens; p.E = cfg->n_experts; p.lo = cfg->local_start; p.mode = cfg->routing_mode;
     p.route_scale = cfg->route_scale;
-    p.fold = 1; p.tw = topk_weights; p.out = static_cast<__nv_bfloat16*>(out);
+    p.fold = post_norm_w != nullptr ? 1 : 2; p.tw = topk_weights; p.out = static_cast<__nv_bfloat16*>(out);
     p.tok_tickets = reinterpret_cast<int32_t*>(b + k.few_ctl);
-    p.grid_bar = reinterpret_cast<unsigned int*>(b + k.few_ctl + 128);
+    p.grid_bar = reinterpret_cast<unsigned int*>(b + k.few_ctl + 4096);
+    p.tile_done = reinterpret_cast<unsigned int*>(b + k.few_ctl + 4352);
+    p.tile_seen = p.tile_done + 384;
     p.x_bf16 = static_cast<const __nv_bfloat16*>(x);
     if (ev) { cudaEventRecord(ev[0], st); cudaEventRecord(ev[1], st); }
     if (plan.path == 0 && pre_norm_w == nullptr) {
@@ -1338,19 +1266,21 @@ int msk_moe_forward_static(const MskMoeCfg* cfg, const void* packed13, const voi
   return static_cast<int>(cudaGetLastError());
 }
 
-int msk_moe_share_pieces(int n_base, int n_stages, int shares, int mode, int cta, int* host_out, int capacity,
-                         int* host_count) {
+int msk_moe_share_pieces(int n_base, int n_stages, int shares, int flat, int cta, int heavy, int skip, int* host_out,
+                         int capacity, int* host_count) {
   if (!host_out || !host_count) return MSK_ERR_NULL;
-  if (n_base < 0 || n_stages < 1 || shares < 1 || cta < 0 || cta >= shares || mode < 0 || mode > 2 || capacity < 0)
+  if (n_base < 0 || n_stages < 1 || shares < 1 || cta < 0 || cta >= shares || capacity < 0 || heavy < 0 || heavy >= shares ||
+      skip < 0)
     return MSK_ERR_SHAPE;
-  PieceIter it = make_piece_iter(mode, n_base, n_stages, cta, shares);
-  const long long items = static_cast<long long>(n_base) * n_stages;
+  if (static_cast<long long>(n_base) * n_stages * shares >= FLAT_MAX_PRODUCT) return MSK_ERR_TOO_LARGE;
+  PieceIter it = make_piece_iter(flat, n_base, n_stages, cta, shares, heavy, skip);
+  const int items = (n_base - it.tail_base) * n_stages;
   int n = 0, base, ks0, ks1;
   while (it.next(base, ks0, ks1)) {
     if (n < capacity) {
       int* o = host_out + 6 * n;
       const bool whole = ks0 == 0 && ks1 == n_stages;
-      const long long b0 = static_cast<long long>(base) * n_stages;
+      const int b0 = (base - it.tail_base) * n_stages;
       o[0] = base; o[1] = ks0; o[2] = ks1;
       o[3] = whole ? -1 : piece_slot(cta, ks0 == 0);
       o[4] = whole ? cta : share_owner(items, shares, b0);
@@ -1360,6 +1290,27 @@ int msk_moe_share_pieces(int n_base, int n_stages, int shares, int mode, int cta
   }
   *host_count = n;
   return n <= capacity ? MSK_OK : MSK_ERR_TOO_LARGE;
+}
+
+// L2 sweep for cold-cache timing: every thread reads 16-byte words of the buffer with ordinary loads,
+// so the lines land in L2 clean and displace what was there. (Zeroing a buffer also displaces it, but
+// leaves L2 full of dirty lines whose write-back then competes with the kernel being timed; the
+// reference sweeps by reading for the same reason, muse_decode_layer/py/05_tune.py:74-94.)
+__global__ void __launch_bounds__(256) l2_sweep_kernel(const uint4* __restrict__ buf, size_t n16, uint32_t* sink) {
+  uint32_t acc = 0;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * 256 + threadIdx.x; i < n16; i += static_cast<size_t>(gridDim.x) * 256) {
+    const uint4 v = buf[i];
+    acc ^= v.x ^ v.y ^ v.z ^ v.w;
+  }
+  if (acc == 0x9E3779B9u) atomicAdd(sink, acc);  // keeps the loads alive
+}
+
+int msk_l2_sweep(const void* buf, size_t bytes, uint32_t* sink, void* stream) {
+  if (!buf || !sink) return MSK_ERR_NULL;
+  if (!aligned16(buf)) return MSK_ERR_ALIGN;
+  if (bytes < 16) return MSK_OK;
+  l2_sweep_kernel<<<1184, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const uint4*>(buf), bytes / 16, sink);
+  return static_cast<int>(cudaGetLastError());
 }
 
 #ifndef MSK_BUILD_ID

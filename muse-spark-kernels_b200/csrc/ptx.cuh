@@ -101,6 +101,25 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   }
 }
 
+// The same wait for hand-offs that complete within a few hundred cycles (the 128 epilogue threads
+// meeting at their barrier): poll without parking first, so that the wake-up latency of a parked
+// thread is not paid on every meeting; then fall back to the parked wait.
+__device__ __forceinline__ bool mbar_wait_short(uint64_t* bar, uint32_t parity, volatile int* abort_word) {
+#pragma unroll 1
+  for (int i = 0; i < 64; ++i) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    if (ok) return true;
+  }
+  return mbar_wait(bar, parity, abort_word);
+}
+
 // ------------------------------------------------------- async-proxy fences
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");

@@ -431,6 +431,76 @@ __global__ void __launch_bounds__(SORT_THREADS) route_sort_kernel(const float* _
   sort_entries_block(sm, ids, T * k, lo, nloc, cnt, off, perm, inv);
 }
 
+// Top-k of one token by one warp with the scores in shared memory: the same keys, the same k rounds of
+// arg-max and the same weight arithmetic as route_one_token (so the same ids and weights, bit for
+// bit), written as plain loops. Compact code matters where it runs: in the prologue of the GEMM kernel
+// of a one-token step every instruction-cache line that has to come from memory is on the critical
+// path. key_s / raw_s: this warp's E words each.
+__device__ __noinline__ void route_token_compact(const float* __restrict__ row, const float* __restrict__ bias,
+                                                 uint32_t* key_s, float* raw_s, int32_t* ids_row, float* wts_row, int E,
+                                                 int k, int mode, float scale, int lane) {
+#pragma unroll 1
+  for (int e = lane; e < E; e += 32) {
+    const float l = row[e];
+    float sel = l, r = l;
+    if (mode == 1) {
+      r = 1.0f / (1.0f + expf(-l * scale));
+      sel = r + (bias ? bias[e] : 0.f);
+    }
+    raw_s[e] = r;
+    key_s[e] = orderable_u32(sel);
+  }
+  __syncwarp();
+  float my_val = 0.f;  // lane s keeps the value of slot s
+  int my_id = 0;
+#pragma unroll 1
+  for (int s = 0; s < k; ++s) {
+    uint64_t best = 0ull;
+#pragma unroll 1
+    for (int e = lane; e < E; e += 32) {
+      const uint32_t hi = key_s[e];
+      // an expert already taken has its key word cleared and so loses to every remaining one
+      const uint64_t key = hi == 0u ? 0ull : ((static_cast<uint64_t>(hi) << 32) | static_cast<uint64_t>(0xFFFFFFFFu - e));
+      best = key > best ? key : best;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const uint64_t other = __shfl_xor_sync(0xffffffffu, best, o);
+      best = other > best ? other : best;
+    }
+    const int e = static_cast<int>(0xFFFFFFFFu - static_cast<uint32_t>(best & 0xFFFFFFFFull));
+    const float v = raw_s[e];
+    __syncwarp();
+    if (lane == 0) key_s[e] = 0u;
+    __syncwarp();
+    if (lane == s) {
+      my_val = v;
+      my_id = e;
+    }
+  }
+  float w;
+  if (mode == 0) {
+    float m = lane < k ? my_val : -INFINITY;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    const float ex = lane < k ? expf(my_val - m) : 0.f;
+    float sum = ex;  // fixed butterfly: same order on every run
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    w = ex / sum;
+  } else {
+    float sum = lane < k ? my_val : 0.f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    w = my_val / (sum + 1e-15f);
+  }
+  if (lane < k) {
+    ids_row[lane] = my_id;
+    wts_row[lane] = w;
+  }
+  __syncwarp();  // key_s / raw_s may be refilled for the warp's next token
+}
+
 // ---- routing + stable sort of a few entries inside another kernel's prologue
 // For up to 256 (token, slot) entries every CTA of the gate/up GEMM kernel derives the tables itself,
 // as every CTA of the reference kernel does (muse_moe_w4a16/cuda/moe.cu:313-433), so the step needs no
@@ -439,17 +509,88 @@ __global__ void __launch_bounds__(SORT_THREADS) route_sort_kernel(const float* _
 constexpr int SMALL_SORT_MAX_ENTRIES = 256;
 constexpr int SMALL_SORT_WARPS = SMALL_SORT_MAX_ENTRIES / 32;
 
+constexpr int SMALL_ROUTE_WARPS = 24;   // warps that route (one token each per turn)
+constexpr int SMALL_RANK_MAX_PAIRS = 4096;   // (token, expert) pairs up to which the top-k is taken by rank
+constexpr int SMALL_RANK_MAX_COMPARES = 1 << 20;
 struct SmallSortScratch {
   int wcnt[SMALL_SORT_WARPS][MAX_LOCAL_EXPERTS];
   int wsum[SMALL_SORT_WARPS];
   int32_t ids[SMALL_SORT_MAX_ENTRIES];
   float tw[SMALL_SORT_MAX_ENTRIES];
+  uint32_t key[SMALL_ROUTE_WARPS][MAX_EXPERTS];   // routing: orderable scores of the token a warp works on
+  float raw[SMALL_ROUTE_WARPS][MAX_EXPERTS];      //          and the values the weights are formed from
+  // routing by rank (few tokens x experts): one packed key and one raw value per (token, expert)
+  unsigned long long key64[SMALL_RANK_MAX_PAIRS];
+  float raw_all[SMALL_RANK_MAX_PAIRS];
 };
+
+// Top-k of a few tokens by rank, all threads of the CTA at once: the packed key of (token, expert) is
+// the one route_one_token uses (orderable score << 32 | ~expert), keys of a token are distinct, so the
+// number of larger keys of the same token is the expert's position in the descending order, and the
+// experts of rank < k are the top-k in slot order: the same ids as k rounds of arg-max, with no
+// dependent rounds. The weights are then formed by one warp per token with route_one_token's
+// arithmetic (same butterflies, same padding). Called by every thread; n_threads = blockDim.x.
+__device__ __noinline__ void route_by_rank_cta(SmallSortScratch& sc, const float* __restrict__ logits,
+                                               const float* __restrict__ bias, int T, int E, int k, int mode,
+                                               float scale) {
+  const int tid = threadIdx.x, n_threads = blockDim.x, warp = tid >> 5, lane = tid & 31;
+  const int n_pairs = T * E;
+#pragma unroll 1
+  for (int i = tid; i < n_pairs; i += n_threads) {
+    const int e = i % E;
+    const float l = logits[i];
+    float sel = l, r = l;
+    if (mode == 1) {
+      r = 1.0f / (1.0f + expf(-l * scale));
+      sel = r + (bias ? bias[e] : 0.f);
+    }
+    sc.raw_all[i] = r;
+    sc.key64[i] = (static_cast<unsigned long long>(orderable_u32(sel)) << 32) |
+                  static_cast<unsigned long long>(0xFFFFFFFFu - static_cast<uint32_t>(e));
+  }
+  __syncthreads();
+#pragma unroll 1
+  for (int i = tid; i < n_pairs; i += n_threads) {
+    const int t = i / E, e = i - t * E;
+    const unsigned long long mine = sc.key64[i];
+    const unsigned long long* row = sc.key64 + t * E;
+    int rank = 0;
+#pragma unroll 4
+    for (int j = 0; j < E; ++j) rank += row[j] > mine ? 1 : 0;
+    if (rank < k) {
+      sc.ids[t * k + rank] = e;
+      sc.tw[t * k + rank] = sc.raw_all[i];
+    }
+  }
+  __syncthreads();
+#pragma unroll 1
+  for (int t = warp; t < T; t += n_threads / 32) {
+    const float my_val = lane < k ? sc.tw[t * k + lane] : 0.f;
+    float w;
+    if (mode == 0) {
+      float m = lane < k ? my_val : -INFINITY;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+      const float ex = lane < k ? expf(my_val - m) : 0.f;
+      float sum = ex;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+      w = ex / sum;
+    } else {
+      float sum = lane < k ? my_val : 0.f;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+      w = my_val / (sum + 1e-15f);
+    }
+    __syncwarp();
+    if (lane < k) sc.tw[t * k + lane] = w;
+  }
+}
 
 // Called by every thread of the CTA (block size a multiple of 32, at least 256). ids_s: the entries
 // in shared memory. Results: cnt_s[nloc], off_s[nloc + 1], perm8_s[q] = entry index (fits a byte) in
 // shared memory; when `global` the calling CTA also writes cnt, off, perm, inv to global memory.
-__device__ __forceinline__ void sort_small_cta(SmallSortScratch& sc, int n, int lo, int nloc, int* cnt_s, int* off_s,
+__device__ __noinline__ void sort_small_cta(SmallSortScratch& sc, int n, int lo, int nloc, int* cnt_s, int* off_s,
                                                uint8_t* perm8_s, bool global, int32_t* cnt_g, int32_t* off_g,
                                                int32_t* perm_g, int32_t* inv_g) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, nthreads = blockDim.x;

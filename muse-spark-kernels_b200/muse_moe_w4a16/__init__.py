@@ -37,7 +37,7 @@ def _stream():
 
 def prepare(weights, *, local_start=0, n_experts=None, top_k=8, max_tokens=8192, routing_mode="softmax_topk",
             route_scale=0.1767766952966369, post_norm_eps=1e-8, num_ctas=0, decode_path=0, no_pdl=0, token_tile=0,
-            trace=0, stop_after=0, pre_norm_eps=1e-5):
+            trace=0, stop_after=0, pre_norm_eps=1e-5, flat_shares=0):
     """Repack the NVFP4 weights into the tile layout the GEMM kernel streams (bit and byte
     permutations only, never requantised) and allocate the workspace. Returns `state`."""
     w13 = _u8(weights["w13"])
@@ -56,7 +56,8 @@ def prepare(weights, *, local_start=0, n_experts=None, top_k=8, max_tokens=8192,
     cfg = MskMoeCfg(hidden=H, inter=I, n_experts=n_experts or n_local, local_start=local_start,
                     local_count=n_local, top_k=top_k, routing_mode=_MODES[routing_mode], route_scale=route_scale,
                     post_norm_eps=post_norm_eps, num_ctas=num_ctas, decode_path=decode_path, no_pdl=no_pdl,
-                    token_tile=token_tile, max_tokens=max_tokens, trace=trace, stop_after=stop_after)
+                    token_tile=token_tile, max_tokens=max_tokens, trace=trace, stop_after=stop_after,
+                    flat_shares=flat_shares)
     b13, b2 = ctypes.c_size_t(), ctypes.c_size_t()
     _lib.check(lib.msk_moe_packed_bytes(ctypes.byref(cfg), ctypes.byref(b13), ctypes.byref(b2)), "msk_moe_packed_bytes")
     with torch.cuda.device(dev):
@@ -319,9 +320,10 @@ def workspace_views(state, T):
 
 
 def trace_stamps(state):
-    """(stamps int64 [2, 256, 16], events int64 [2, 3, 256]) of the last step's two GEMM launches
-    (prepare(trace=1)): per-CTA %globaltimer stamps, and CTA 0's event list per role
-    (dequant thread, MMA issuer, weight producer), each event = ns << 8 | code."""
+    """(stamps int64 [2, 256, 16], events int64 [2, 6, 128]) of the last step's GEMM launches
+    (prepare(trace=1)): per-CTA %globaltimer stamps, and one CTA's event list per role (dequant
+    thread, MMA issuer, weight producer, epilogue thread, gather warp; only in a library built with
+    MSK_TRACE_DETAIL), each event = ns << 8 | code."""
     cfg, lib = state["cfg"], state["lib"].lib
     ws = state["workspace"]
     p = ctypes.c_void_p()
@@ -329,7 +331,19 @@ def trace_stamps(state):
     o = p.value - ws.data_ptr()
     words = 256 * 16 + 3 * 256
     t = ws[o:o + 2 * words * 8].view(torch.int64).view(2, words).clone()
-    return t[:, :256 * 16].reshape(2, 256, 16), t[:, 256 * 16:].reshape(2, 3, 256)
+    return t[:, :256 * 16].reshape(2, 256, 16), t[:, 256 * 16:].reshape(2, 6, 128)
+
+
+class L2Sweep:
+    """Cold-cache timing aid: sweep() reads a buffer larger than L2 (256 MiB) on the current stream."""
+
+    def __init__(self, device, nbytes=256 << 20):
+        self.buf = torch.zeros(nbytes, dtype=torch.uint8, device=device)
+        self.sink = torch.zeros(4, dtype=torch.int32, device=device)
+        self.lib = _lib.load()
+
+    def sweep(self):
+        _lib.check(self.lib.msk_l2_sweep(_lib.ptr(self.buf), self.buf.numel(), _lib.ptr(self.sink), _stream()), "msk_l2_sweep")
 
 
 def attrs(which, token_tile=16):

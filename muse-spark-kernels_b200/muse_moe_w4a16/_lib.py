@@ -43,6 +43,7 @@ class MskMoeCfg(ctypes.Structure):
         ("max_tokens", ctypes.c_int32),
         ("trace", ctypes.c_int32),
         ("stop_after", ctypes.c_int32),
+        ("flat_shares", ctypes.c_int32),
     ]
 
     def __deepcopy__(self, memo):
@@ -77,13 +78,15 @@ SIGNATURES = {
     "msk_moe_forward_static": [_CFG, _P, _P, _P, _P, _P, _P, _P, _P, _P, ctypes.c_int, _P],
     "msk_moe_static_status": [_INTP, _P],
     "msk_moe_plan": [_CFG, ctypes.c_int, _INTP],
-    "msk_moe_share_pieces": [ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, _INTP, ctypes.c_int, _INTP],
+    "msk_moe_share_pieces": [ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                             _INTP, ctypes.c_int, _INTP],
     "msk_moe_workspace_view": [_CFG, _P, ctypes.c_int, ctypes.POINTER(_P)],
     "msk_moe_read_status": [_P, _INTP, _P],
     "msk_moe_attrs": [ctypes.c_int, ctypes.c_int, _INTP],
     "msk_ep_combine": [_P, _P, ctypes.c_int, _P, ctypes.c_int, ctypes.c_int, _P, ctypes.c_int, ctypes.c_int, ctypes.c_int, _P],
     "msk_ep_flag_write": [_P, ctypes.c_uint32, _P],
     "msk_ep_flag_wait": [_P, ctypes.c_uint32, _P],
+    "msk_l2_sweep": [_P, ctypes.c_size_t, _P, _P],
     "msk_bw_probe": [_P, ctypes.c_size_t, ctypes.c_int, ctypes.c_int, ctypes.c_int, _P, _P],
 }
 

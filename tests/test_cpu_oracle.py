@@ -185,18 +185,20 @@ def test_host_side_validation_rejects_bad_arguments():
     assert lib.msk_moe_plan(ctypes.byref(cfg), 4, plan) == 0 and plan[0] in (8, 16, 32, 64, 128)
 
 
-def _pieces(lib, n_base, nst, shares, mode, cta):
+def _pieces(lib, n_base, nst, shares, mode, cta, heavy=0, skip=0):
     cap = 4096
     buf = (ctypes.c_int * (6 * cap))()
     n = ctypes.c_int()
-    assert lib.msk_moe_share_pieces(n_base, nst, shares, mode, cta, buf, cap, ctypes.byref(n)) == 0
+    assert lib.msk_moe_share_pieces(n_base, nst, shares, mode, cta, heavy, skip, buf, cap, ctypes.byref(n)) == 0
     return [tuple(buf[6 * i:6 * i + 6]) for i in range(n.value)]
 
 
 @pytest.mark.parametrize("n_base,nst,shares", [(96, 16, 148), (128, 6, 148), (600, 16, 148), (3, 28, 148), (1, 1, 7),
                                                (0, 16, 148), (37, 5, 5), (224, 8, 148), (50, 2, 1)])
 def test_flat_shares_cover_every_stage_once_and_name_their_pieces(n_base, nst, shares):
-    """The work distribution of the GEMM kernels (host twin of the device code): with flat shares
+    """The work distribution of the GEMM kernels (host twin of the device code): with flat shares (full
+    rounds of whole units, then the last full round and the left-over units cut into equal shares of
+    stages; nothing is cut when there are fewer units than CTAs)
     every (unit, stage) item belongs to exactly one CTA, shares differ by at most one item, a cut unit's
     pieces sit in consecutive CTAs in ascending K order, each in a slot of its own, and the first / last
     owner every piece computes is the CTA that really holds the unit's first / last stage."""
@@ -207,7 +209,7 @@ def test_flat_shares_cover_every_stage_once_and_name_their_pieces(n_base, nst, s
     sizes = []
     slots = set()
     for c in range(shares):
-        pcs = _pieces(lib, n_base, nst, shares, 2, c)
+        pcs = _pieces(lib, n_base, nst, shares, 1, c)
         sizes.append(sum(k1 - k0 for _, k0, k1, *_ in pcs))
         for base, k0, k1, slot, first, last in pcs:
             assert 0 <= k0 < k1 <= nst
@@ -220,28 +222,57 @@ def test_flat_shares_cover_every_stage_once_and_name_their_pieces(n_base, nst, s
             else:
                 assert (k0, k1) == (0, nst)
     assert len(seen) == n_base * nst
-    assert max(sizes) - min(sizes) <= 1
+    if n_base >= shares:
+        assert max(sizes) - min(sizes) <= 1
+    else:                       # fewer units than CTAs: nothing is cut
+        assert set(sizes) <= {0, nst} and not slots
     for c in range(shares):
-        for base, k0, k1, slot, first, last in _pieces(lib, n_base, nst, shares, 2, c):
+        for base, k0, k1, slot, first, last in _pieces(lib, n_base, nst, shares, 1, c):
             assert first == seen[(base, 0)] and last == seen[(base, nst - 1)]
             owners = [seen[(base, ks)] for ks in range(nst)]
             assert owners == sorted(owners) and first <= min(owners) and max(owners) <= last
-            # every share between the first and the last owner either holds a piece of the unit or is empty
-            assert all(c in owners or sizes[c] == 0 for c in range(first, last + 1))
+            # every share between the first and the last owner either holds a piece of the unit or has an empty
+            # share of the tail (the units left over after the full rounds of whole units)
+            tail_first = n_base if n_base < shares else (n_base // shares - 1) * shares
+            tail_items = (n_base - tail_first) * nst
+            empty = lambda c: tail_items * (c + 1) // shares == tail_items * c // shares
+            assert all(c in owners or empty(c) for c in range(first, last + 1))
 
 
-@pytest.mark.parametrize("mode", [0, 1])
-def test_whole_unit_modes_give_every_unit_to_one_cta(mode):
+def test_whole_unit_mode_gives_every_unit_to_one_cta():
     from muse_moe_w4a16 import _lib
 
     lib = _lib.load()
     n_base, nst, shares = 301, 16, 148
     got = []
     for c in range(shares):
-        for base, k0, k1, slot, first, last in _pieces(lib, n_base, nst, shares, mode, c):
+        for base, k0, k1, slot, first, last in _pieces(lib, n_base, nst, shares, 0, c):
             assert (k0, k1, slot) == (0, nst, -1)
             got.append(base)
     assert sorted(got) == list(range(n_base))
+
+
+@pytest.mark.parametrize("n0,nst0,n1,nst1,shares", [(600, 16, 800, 6, 148), (96, 16, 128, 6, 148), (1356, 16, 1808, 6, 148),
+                                                     (300, 28, 100, 8, 148), (5, 2, 3, 1, 4)])
+def test_skewed_dealing_of_the_second_phase_balances_both_phases(n0, nst0, n1, nst1, shares):
+    """One launch for both GEMMs: the CTAs that hold one more gate/up unit are left out of the first
+    rounds of down units. Every down unit still goes to exactly one CTA, each CTA takes its units in
+    ascending order, and the largest total (in K stages) is no larger than with plain round-robin."""
+    from muse_moe_w4a16 import _lib
+
+    lib = _lib.load()
+    heavy = n0 % shares if n0 >= shares else 0   # the rule of the kernel (phase1_skew)
+    skip = (nst0 + nst1 // 2) // nst1 if heavy else 0
+    load0 = [len(_pieces(lib, n0, nst0, shares, 0, c)) * nst0 for c in range(shares)]
+    got, skewed, plain = [], [], []
+    for c in range(shares):
+        mine = [b for b, *_ in _pieces(lib, n1, nst1, shares, 0, c, heavy, skip)]
+        assert mine == sorted(mine)
+        got += mine
+        skewed.append(load0[c] + len(mine) * nst1)
+        plain.append(load0[c] + len(_pieces(lib, n1, nst1, shares, 0, c)) * nst1)
+    assert sorted(got) == list(range(n1))
+    assert max(skewed) <= max(plain)
 
 
 def test_plan_is_a_function_of_the_configuration_only():
@@ -252,16 +283,20 @@ def test_plan_is_a_function_of_the_configuration_only():
     lib = _lib.load()
     plan = (ctypes.c_int * 4)()
     cfg = _lib.MskMoeCfg(hidden=4096, inter=1536, n_experts=128, local_start=0, local_count=128, top_k=8, max_tokens=8192)
-    want = {1: (16, 0, 1, 148), 8: (16, 0, 1, 148), 32: (16, 0, 1, 148), 64: (16, 1, 0, 148), 256: (64, 1, 0, 148),
+    want = {1: (16, 0, 0, 148), 8: (16, 0, 0, 148), 32: (16, 1, 0, 148), 64: (16, 1, 0, 148), 256: (64, 1, 0, 148),
             8192: (128, 1, 0, 148)}
     for T, w in want.items():
         assert lib.msk_moe_plan(ctypes.byref(cfg), T, plan) == 0
         assert tuple(plan) == w, (T, tuple(plan))
     cfg.decode_path = 2
+    cfg.flat_shares = 1
     assert lib.msk_moe_plan(ctypes.byref(cfg), 8, plan) == 0 and tuple(plan) == (16, 2, 1, 148)
+    cfg.decode_path = 3
+    assert lib.msk_moe_plan(ctypes.byref(cfg), 32, plan) == 0 and tuple(plan) == (16, 0, 0, 148)
     cfg.decode_path = 1
     cfg.num_ctas = 37
     assert lib.msk_moe_plan(ctypes.byref(cfg), 8, plan) == 0 and tuple(plan) == (16, 1, 1, 37)
+    assert lib.msk_moe_plan(ctypes.byref(cfg), 64, plan) == 0 and tuple(plan) == (16, 1, 0, 37)
 
 
 def test_module_refuses_cpu_tensors():

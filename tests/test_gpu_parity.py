@@ -208,7 +208,7 @@ def test_forward_small_shapes(cuda_dev, T, tile, path, post):
     copy + routing gate/up kernel + combining down kernel)."""
     m, inputs, _lib, orc = _mods()
     out, ref, parts, views, st, _ = _run_forward(m, inputs, orc, cuda_dev, 512, 256, 8, 2, T, seed=T, post_norm=post,
-                                                 token_tile=tile, decode_path=path)
+                                                 token_tile=tile, decode_path=path or 3, flat_shares=1)
     if T <= 32:
         assert m.plan(st, T)[1] == path
     _check_forward(out, ref, parts, views)
@@ -226,13 +226,14 @@ def test_forward_few_token_paths_and_grids(cuda_dev, T, path, ctas, post):
     m, inputs, _lib, orc = _mods()
     H, I, E, k = 1024, 512, 16, 4
     out, ref, parts, views, st, (x, ids, tw, w) = _run_forward(m, inputs, orc, cuda_dev, H, I, E, k, T, seed=60 + T,
-                                                               post_norm=post, decode_path=path, num_ctas=ctas)
+                                                               post_norm=post, decode_path=path or 3, num_ctas=ctas,
+                                                               flat_shares=1)
     plan = m.plan(st, T)
-    assert plan[1] == path and plan[2] == 1 and plan[3] == (ctas or 148)
+    assert plan[1] == path and plan[2] == (0 if path == 0 else 1) and plan[3] == (ctas or 148)
     _check_forward(out, ref, parts, views)
     again = m.kernel_fn({"hidden_states": x, "topk_ids": ids, "topk_weights": tw}, st)
     assert torch.equal(again, out)
-    chain = m.prepare(w, n_experts=E, top_k=k, max_tokens=T, decode_path=1, token_tile=16, num_ctas=3)
+    chain = m.prepare(w, n_experts=E, top_k=k, max_tokens=T, decode_path=1, token_tile=16, num_ctas=3, flat_shares=1)
     other = m.kernel_fn({"hidden_states": x, "topk_ids": ids, "topk_weights": tw}, chain)
     assert _rel(out, other) <= 8e-3   # same products, other cut points: a bf16 ulp or two of the output
     torch.cuda.synchronize()
@@ -244,8 +245,8 @@ def test_forward_decode_shape_T1_and_T8(cuda_dev):
     m, inputs, _lib, orc = _mods()
     for T, path in ((1, 0), (8, 0), (1, 2), (8, 2), (8, 1)):
         out, ref, parts, views, st, _ = _run_forward(m, inputs, orc, cuda_dev, 4096, 1536, 16, 8, T, seed=10 + T,
-                                                     decode_path=path)
-        assert m.plan(st, T)[:3] == (16, path, 1)
+                                                     decode_path=path or 3, flat_shares=1)
+        assert m.plan(st, T)[:3] == (16, path, 0 if path == 0 else 1)
         _check_forward(out, ref, parts, views)
 
 
@@ -270,34 +271,15 @@ def test_ep_combine_kernel_matches_rank_order_sum(cuda_dev):
     assert torch.equal(own, got)
 
 
-@pytest.mark.parametrize("T,post,ctas", [(1, False, 0), (1, True, 5), (3, True, 37), (8, False, 0), (8, True, 148),
-                                         (2, False, 1)])
-def test_forward_few_token_kernel(cuda_dev, T, post, ctas):
-    """The single-launch kernel for up to 8 tokens (token_tile=8 forces it), on several grid sizes:
-    the shares of the weight stream, and with them the pieces each output sums, change with the
-    grid; the result must not."""
-    m, inputs, _lib, orc = _mods()
-    out, ref, parts, views, st, (x, ids, tw, w) = _run_forward(m, inputs, orc, cuda_dev, 1024, 512, 16, 4, T,
-                                                               seed=20 + T, post_norm=post, token_tile=8, num_ctas=ctas)
-    assert m.plan(st, T)[0] == 8
-    _check_forward(out, ref, parts, views)
-    # given routing instead of logits, and the chain of launches on the same inputs
-    again = m.kernel_fn({"hidden_states": x, "topk_ids": ids, "topk_weights": tw}, st)
-    assert torch.equal(again, out)
-    chain = m.prepare(w, n_experts=16, top_k=4, max_tokens=T, token_tile=16, decode_path=1)
-    other = m.kernel_fn({"hidden_states": x, "topk_ids": ids, "topk_weights": tw}, chain)
-    assert _rel(out, other) <= 8e-3   # same products, different summation order: a bf16 ulp or two of the output
-    assert m.read_status(st) == 0 and m.read_status(chain) == 0
-
-
-@pytest.mark.parametrize("tile,path", [(8, 0), (16, 0), (16, 1), (16, 2)])
+@pytest.mark.parametrize("tile,path", [(16, 0), (16, 1), (16, 2), (32, 0)])
 def test_forward_local_range_negative_ids_and_empty_tokens(cuda_dev, tile, path):
     """Experts [4, 12) of 16 resident: routes outside the range and negative ids are dropped (the
     reference's filter, muse_moe_w4a16/cuda/moe.cu:347-350); a token left without any route is zero."""
     m, inputs, _lib, orc = _mods()
     H, I, E, k, T, lo, nloc = 512, 256, 16, 4, 6, 4, 8
     w = inputs.make_weights(H, I, nloc, 31, cuda_dev, post_norm=True)
-    st = m.prepare(w, local_start=lo, n_experts=E, top_k=k, max_tokens=T, token_tile=tile, decode_path=path)
+    st = m.prepare(w, local_start=lo, n_experts=E, top_k=k, max_tokens=T, token_tile=tile, decode_path=path or 3,
+                   flat_shares=1)
     g = torch.Generator(device=cuda_dev).manual_seed(5)
     x = torch.randn((T, H), generator=g, device=cuda_dev).to(torch.bfloat16)
     ids = torch.stack([torch.randperm(E, generator=g, device=cuda_dev)[:k] for _ in range(T)]).to(torch.int32)
