@@ -129,14 +129,19 @@ int msk_moe_sort(const MskMoeCfg* cfg, const int32_t* topk_ids, int n_tokens, in
  * on cfg->max_tokens only, so every call must pass the cfg the workspace was sized with. */
 int msk_moe_workspace_bytes(const MskMoeCfg* cfg, size_t* host_bytes);
 
-/* Zero the control words of a fresh workspace (status, split-K tickets). Once, after allocation. */
+/* Zero the control words of a workspace (status word, sort tables, unit and token tickets, grid and
+ * tile counters). Once after allocation, and again after a step whose status word came back
+ * non-zero: a kernel that gave up leaves tickets and counters half-way, and the status word itself
+ * is sticky. */
 int msk_moe_workspace_init(const MskMoeCfg* cfg, void* workspace, size_t workspace_bytes, void* stream);
 
 /* out[t, :] = bf16( sum_{slot, local} w[t,slot] * post(y[t,slot]) ),
  *   y = (bf16(silu(x W13g^T gs13) * (x W13u^T gs13))) W2^T gs2,
  *   post(y) = y                                  when post_norm_w == NULL
  *           = y(1+w) * rsqrt(mean((y(1+w))^2)+eps)  otherwise
- * (muse_moe_w4a16/cuda/moe.cu:440-478, 2604-2766). x: bf16 [T, H]; topk_ids int32 [T, k]
+ * (muse_moe_w4a16/cuda/moe.cu:440-478, 2604-2766). x: bf16 [T, H], values within the F16 range
+ * (|x| <= 65504; the MMA operands are F16, larger magnitudes saturate there, magnitudes below 2^-24
+ * vanish; the reference's layers hand over RMS-normed rows, far inside it); topk_ids int32 [T, k]
  * (global ids); topk_weights fp32 [T, k]; gs13/gs2 fp32 [local_count]; post_norm_w bf16 [H]
  * or NULL; out bf16 [T, H], fully overwritten (zeros for tokens without a local route).
  * Launches: sort, [row copy,] gate/up GEMM, down GEMM, combine; a single launch for a few tokens
@@ -217,6 +222,8 @@ int msk_moe_share_pieces(int n_base, int n_stages, int shares, int flat, int cta
 /* Views into the workspace after msk_moe_forward (device pointers, for parity tests):
  * which: 0 cnt, 1 off, 2 perm, 3 inv, 4 inter (fp16 [R, I], holding bf16-rounded values), 5 y (fp32 [R, H]; bf16 [R, H] when the plan's
  * token tile is 128),
+ * 7 unit tickets, 8 control words of the few-token paths, 9 per-CTA counts of the multi-CTA sort (all three
+ * zeroed by msk_moe_workspace_init, like everything below view 4),
  * 6 trace (uint64 [2 launches][256 CTAs x 16 stamps, then 6 x 128 event words], ns; written when cfg->trace != 0). */
 int msk_moe_workspace_view(const MskMoeCfg* cfg, void* workspace, int which, void** host_ptr);
 
@@ -258,9 +265,14 @@ const char* msk_build_id(void);
 
 /* HBM streaming probe: every CTA pulls its share of `bytes` from `src` through a ring of
  * bulk async copies, as the GEMM kernel's weight producer does, and adds a checksum to
- * sink[0] (twin of muse_moe_w4a16/cuda/moe_bw.cu). */
+ * sink[0] (twin of muse_moe_w4a16/cuda/moe_bw.cu). sink is two words; sink[1] receives the device
+ * status (0, or 1 when a bounded wait gave up), like word 0 of a workspace. skip_release > 0 is a
+ * test hook for that path: every CTA withholds the release of its chunk number skip_release, so
+ * the producer's wait for the slot runs into its limit (MSK_WAIT_LIMIT_NS, one second), the kernel
+ * unwinds and returns with sink[1] = 1. Nothing traps or spins for ever; the context stays usable
+ * (the reference's counterpart is its SK2_DELAY_ESC knob, muse_decode_layer/py/01_moe.py:340). */
 int msk_bw_probe(const void* src, size_t bytes, int stages, int stage_bytes, int num_ctas, uint32_t* sink,
-                 void* stream);
+                 int skip_release, void* stream);
 
 #ifdef __cplusplus
 }

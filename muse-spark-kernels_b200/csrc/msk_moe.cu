@@ -390,7 +390,7 @@ static int stream_value32(const char* name, void* addr, uint32_t value, unsigned
 // copies, one elected thread issuing, one warp consuming (twin of the reference's
 // muse_moe_w4a16/cuda/moe_bw.cu tma_kernel).
 __global__ void __launch_bounds__(64) bw_probe_kernel(const uint8_t* src, unsigned long long bytes, int stages,
-                                                      int stage_bytes, uint32_t* sink) {
+                                                      int stage_bytes, uint32_t* sink, int skip_release) {
   extern __shared__ __align__(1024) uint8_t psm[];
   __shared__ uint64_t full[8], empty[8];
   __shared__ int abort_word;
@@ -422,7 +422,9 @@ __global__ void __launch_bounds__(64) bw_probe_kernel(const uint8_t* src, unsign
       if (!mbar_wait(&full[slot], par, &abort_word)) break;
       sum += *reinterpret_cast<const uint32_t*>(psm + static_cast<size_t>(slot) * stage_bytes + lane * 16);
       __syncwarp();
-      if (lane == 0) mbar_arrive(&empty[slot]);
+      // skip_release (test hook): chunk number skip_release of every CTA is never handed back, so the
+      // producer's bounded wait for that slot runs out and the kernel leaves through its time-out path
+      if (lane == 0 && !(skip_release > 0 && it + 1 == static_cast<uint32_t>(skip_release))) mbar_arrive(&empty[slot]);
     }
     if (sum == 0x9E3779B9u) atomicAdd(sink, sum);  // keeps the reads alive
   }
@@ -872,6 +874,9 @@ int msk_moe_workspace_view(const MskMoeCfg* cfg, void* workspace, int which, voi
     case 4: *host_ptr = b + k.inter; break;
     case 5: *host_ptr = b + k.y; break;
     case 6: *host_ptr = b + k.trace; break;
+    case 7: *host_ptr = b + k.tickets; break;
+    case 8: *host_ptr = b + k.few_ctl; break;
+    case 9: *host_ptr = b + k.sort_blk; break;
     default: return MSK_ERR_SHAPE;
   }
   return MSK_OK;
@@ -1393,7 +1398,7 @@ int msk_ep_flag_wait(void* addr, uint32_t value, void* stream) {
 }
 
 int msk_bw_probe(const void* src, size_t bytes, int stages, int stage_bytes, int num_ctas, uint32_t* sink,
-                 void* stream) {
+                 int skip_release, void* stream) {
   if (!src || !sink) return MSK_ERR_NULL;
   if (!aligned16(src)) return MSK_ERR_ALIGN;
   if (stages < 1 || stages > 8 || stage_bytes < 16 || stage_bytes % 16 != 0) return MSK_ERR_SHAPE;
@@ -1404,7 +1409,7 @@ int msk_bw_probe(const void* src, size_t bytes, int stages, int stage_bytes, int
                                        static_cast<int>(smem));
   if (e != cudaSuccess) return static_cast<int>(e);
   bw_probe_kernel<<<grid, 64, smem, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const uint8_t*>(src), static_cast<unsigned long long>(bytes), stages, stage_bytes, sink);
+      static_cast<const uint8_t*>(src), static_cast<unsigned long long>(bytes), stages, stage_bytes, sink, skip_release);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -20,7 +20,8 @@ import torch
 from . import _lib
 from ._lib import ROUTE_SIGMOID_BIAS, ROUTE_SOFTMAX_TOPK, MskMoeCfg
 
-__all__ = ["prepare", "kernel_fn", "export_weights", "read_status", "workspace_views", "attrs"]
+__all__ = ["prepare", "kernel_fn", "export_weights", "read_status", "reinit_workspace", "state_dict", "load_state_dict",
+           "workspace_views", "attrs"]
 
 _MODES = {"softmax_topk": ROUTE_SOFTMAX_TOPK, "sigmoid_bias": ROUTE_SIGMOID_BIAS}
 
@@ -65,30 +66,80 @@ def prepare(weights, *, local_start=0, n_experts=None, top_k=8, max_tokens=8192,
         packed2 = torch.empty(b2.value, dtype=torch.uint8, device=dev)
         _lib.check(lib.msk_moe_repack(ctypes.byref(cfg), _lib.ptr(w13), _lib.ptr(w13_sf), _lib.ptr(w2), _lib.ptr(w2_sf),
                                       _lib.ptr(packed13), _lib.ptr(packed2), _stream()), "msk_moe_repack")
-        wsb = ctypes.c_size_t()
-        _lib.check(lib.msk_moe_workspace_bytes(ctypes.byref(cfg), ctypes.byref(wsb)), "msk_moe_workspace_bytes")
-        workspace = torch.empty(wsb.value, dtype=torch.uint8, device=dev)
-        _lib.check(lib.msk_moe_workspace_init(ctypes.byref(cfg), _lib.ptr(workspace), wsb.value, _stream()),
-                   "msk_moe_workspace_init")
-        torch.cuda.synchronize(dev)
     prw = weights.get("pre_norm_w")
     if prw is not None and (prw.dtype != torch.bfloat16 or prw.numel() != 2 * weights["w13"].shape[2]):
         raise RuntimeError("muse_moe_w4a16.prepare: pre_norm_w must be bfloat16 [hidden]")
     pnw = weights.get("post_norm_w")
     if pnw is not None and pnw.dtype != torch.bfloat16:
         raise RuntimeError("muse_moe_w4a16.prepare: post_norm_w must stay bfloat16")
-    state = {
-        "cfg": cfg, "lib": _lib.LibHandle(), "lo": local_start, "cnt": n_local,
+    return _make_state(cfg, packed13, packed2, weights["w13_gs"], weights["w2_gs"], pnw, prw, pre_norm_eps,
+                       weights.get("router"), weights.get("route_bias"))
+
+
+def _make_state(cfg, packed13, packed2, gs13, gs2, post_norm_w, pre_norm_w, pre_norm_eps, router, route_bias):
+    """The state dict around already packed weights: allocates and initialises the workspace."""
+    lib = _lib.load()
+    dev = packed13.device
+    with torch.cuda.device(dev):
+        wsb = ctypes.c_size_t()
+        _lib.check(lib.msk_moe_workspace_bytes(ctypes.byref(cfg), ctypes.byref(wsb)), "msk_moe_workspace_bytes")
+        workspace = torch.empty(wsb.value, dtype=torch.uint8, device=dev)
+        _lib.check(lib.msk_moe_workspace_init(ctypes.byref(cfg), _lib.ptr(workspace), wsb.value, _stream()),
+                   "msk_moe_workspace_init")
+        torch.cuda.synchronize(dev)
+    return {
+        "cfg": cfg, "lib": _lib.LibHandle(), "lo": cfg.local_start, "cnt": cfg.local_count,
         "packed13": packed13, "packed2": packed2,
-        "gs13": weights["w13_gs"].contiguous(), "gs2": weights["w2_gs"].contiguous(),
-        "post_norm_w": None if pnw is None else pnw.contiguous(),
-        "pre_norm_w": None if prw is None else prw.contiguous(),
+        "gs13": gs13.contiguous(), "gs2": gs2.contiguous(),
+        "post_norm_w": None if post_norm_w is None else post_norm_w.contiguous(),
+        "pre_norm_w": None if pre_norm_w is None else pre_norm_w.contiguous(),
         "pre_norm_eps": float(pre_norm_eps),
-        "router": None if weights.get("router") is None else weights["router"].float().contiguous(),
-        "route_bias": None if weights.get("route_bias") is None else weights["route_bias"].float().contiguous(),
+        "router": None if router is None else router.float().contiguous(),
+        "route_bias": None if route_bias is None else route_bias.float().contiguous(),
         "workspace": workspace, "workspace_bytes": wsb.value,
     }
-    return state
+
+
+_SD_TENSORS = ("packed13", "packed2", "gs13", "gs2", "post_norm_w", "pre_norm_w", "router", "route_bias")
+
+
+def state_dict(state):
+    """What a checkpoint needs to rebuild `state` without the original weights and without the repack:
+    the packed weight tiles, the scales and norm weights, and the configuration as plain numbers. The
+    workspace is scratch and is not part of it. (The reference keeps no such state: its prepare() is
+    re-run from the weights every time, muse_moe_w4a16/py/02_prepare.py:2-81.)"""
+    cfg = state["cfg"]
+    sd = {k: state[k] for k in _SD_TENSORS if state.get(k) is not None}
+    sd["config"] = {name: getattr(cfg, name) for name, _ in MskMoeCfg._fields_}
+    sd["pre_norm_eps"] = state["pre_norm_eps"]
+    return sd
+
+
+def load_state_dict(sd, device=None):
+    """Inverse of state_dict: a ready state on `device` (default: where the tensors are). No repack runs;
+    the packed tiles are taken as they are, so kernel_fn gives the same bits as on the state they came from."""
+    lib = _lib.load()
+    cfg = MskMoeCfg(**sd["config"])
+    t = {k: (sd[k] if device is None else sd[k].to(device)) for k in _SD_TENSORS if sd.get(k) is not None}
+    if not t["packed13"].is_cuda:
+        raise RuntimeError("muse_moe_w4a16.load_state_dict: tensors must be CUDA tensors (there is no CPU path)")
+    b13, b2 = ctypes.c_size_t(), ctypes.c_size_t()
+    _lib.check(lib.msk_moe_packed_bytes(ctypes.byref(cfg), ctypes.byref(b13), ctypes.byref(b2)), "msk_moe_packed_bytes")
+    if t["packed13"].numel() != b13.value or t["packed2"].numel() != b2.value:
+        raise RuntimeError("muse_moe_w4a16.load_state_dict: packed weights do not match the configuration")
+    return _make_state(cfg, t["packed13"].contiguous(), t["packed2"].contiguous(), t["gs13"], t["gs2"],
+                       t.get("post_norm_w"), t.get("pre_norm_w"), sd.get("pre_norm_eps", 1e-5), t.get("router"),
+                       t.get("route_bias"))
+
+
+def reinit_workspace(state):
+    """Puts the control words of the workspace back to their initial state (status word, tickets, grid
+    and tile counters). Call it when read_status() returned non-zero before using the state again: a
+    kernel that gave up on a bounded wait leaves tickets and counters half-way, and the status word is
+    sticky. Synchronises."""
+    _lib.check(state["lib"].lib.msk_moe_workspace_init(ctypes.byref(state["cfg"]), _lib.ptr(state["workspace"]),
+                                                       state["workspace_bytes"], _stream()), "msk_moe_workspace_init")
+    torch.cuda.synchronize(state["workspace"].device)
 
 
 def _logits(data, state, x, T):
@@ -344,6 +395,22 @@ class L2Sweep:
 
     def sweep(self):
         _lib.check(self.lib.msk_l2_sweep(_lib.ptr(self.buf), self.buf.numel(), _lib.ptr(self.sink), _stream()), "msk_l2_sweep")
+
+
+def bw_probe(nbytes=1 << 30, stages=5, stage_bytes=36864, num_ctas=0, skip_release=0, device=None):
+    """HBM streaming probe (msk_bw_probe). Returns (GB/s, device status): status 1 means a bounded
+    wait inside the kernel gave up (what skip_release > 0 provokes on purpose)."""
+    lib = _lib.load()
+    dev = device or torch.device("cuda", torch.cuda.current_device())
+    src = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    sink = torch.zeros(2, dtype=torch.int32, device=dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    _lib.check(lib.msk_bw_probe(_lib.ptr(src), nbytes, stages, stage_bytes, num_ctas, _lib.ptr(sink), skip_release,
+                                _stream()), "msk_bw_probe")
+    e1.record()
+    torch.cuda.synchronize(dev)
+    return nbytes / (e0.elapsed_time(e1) * 1e-3) / 1e9, int(sink[1].item())
 
 
 def attrs(which, token_tile=16):

@@ -87,7 +87,7 @@ SIGNATURES = {
     "msk_ep_flag_write": [_P, ctypes.c_uint32, _P],
     "msk_ep_flag_wait": [_P, ctypes.c_uint32, _P],
     "msk_l2_sweep": [_P, ctypes.c_size_t, _P, _P],
-    "msk_bw_probe": [_P, ctypes.c_size_t, ctypes.c_int, ctypes.c_int, ctypes.c_int, _P, _P],
+    "msk_bw_probe": [_P, ctypes.c_size_t, ctypes.c_int, ctypes.c_int, ctypes.c_int, _P, ctypes.c_int, _P],
 }
 
 _lock = threading.Lock()

@@ -30,6 +30,20 @@ import torch
 import torch.distributed as dist
 
 
+def wait_deadline(event, seconds, what):
+    """Host-side deadline for a stream that may be blocked on a peer's flag: polls event.query() and
+    raises TimeoutError after `seconds`. A flag wait is a stream operation that the device cannot
+    bound; a peer that died would block this rank's stream until the launcher ends the job, so callers
+    that need to notice sooner (at the price of one host synchronisation per step) poll here."""
+    import time
+
+    t0 = time.time()
+    while not event.query():
+        if time.time() - t0 > seconds:
+            raise TimeoutError(f"expert-parallel exchange: {what} did not complete within {seconds} s (a peer is not answering)")
+        time.sleep(0.0005)
+
+
 def owner_rank(ids, experts_per_rank):
     return torch.div(ids, experts_per_rank, rounding_mode="floor")
 
@@ -154,8 +168,11 @@ class SymmExchange:
         _lib.check(self.lib.msk_ep_flag_wait(ctypes.c_void_p(self.flag_base[self.rank] + 4 * word), value,
                                              ctypes.c_void_p(stream.cuda_stream)), "msk_ep_flag_wait")
 
-    def step(self, x, ids, tw, expert_fn, experts_per_rank):
-        """expert_fn(rows, ids, weights, out) as in ep_step, writing its partial rows into `out`."""
+    def step(self, x, ids, tw, expert_fn, experts_per_rank, deadline_s=None):
+        """expert_fn(rows, ids, weights, out) as in ep_step, writing its partial rows into `out`.
+        deadline_s: when given, the host waits (polling, wait_deadline) until the last pull of the step has
+        completed and raises TimeoutError if a peer does not answer in time; None keeps the step free of
+        host synchronisation."""
         n, r, m, T, H, k = self.n, self.rank, self.m, self.T, self.H, self.k
         self.epoch += 1
         e, b = self.epoch, self.epoch & 1
@@ -197,6 +214,8 @@ class SymmExchange:
                 self.back[q].copy_(self.peer_part[q][b, j], non_blocking=True)
             ev_back = torch.cuda.Event()
             ev_back.record(s1)
+        if deadline_s is not None:
+            wait_deadline(ev_back, deadline_s, f"step {e} on rank {r}")
         s0.wait_event(ev_back)
         return combine_partials(self.back, gids[0], experts_per_rank, self_rank=r, self_rows=part[0])
 
@@ -205,12 +224,13 @@ class EPModule:
     """prepare/kernel_fn for one rank of an expert-parallel group."""
 
     def __init__(self, local_weights, rank, world, n_experts, top_k, tokens_per_rank, group=None, transport="symm",
-                 chunks=None, **prep):
+                 chunks=None, deadline_s=None, **prep):
         import muse_moe_w4a16 as moe
 
         self.moe, self.rank, self.world, self.group = moe, rank, world, group
         self.n_experts, self.top_k, self.per_rank = n_experts, top_k, n_experts // world
         self.transport = transport
+        self.deadline_s = deadline_s
         if transport == "symm":
             # from four ranks on, chunks of two source ranks: measured on 8 GPUs, 4 chunks 4.63 ms per step,
             # 2 chunks 5.45 ms (less of the exchange hidden), 8 chunks lose more in half-filled token tiles
@@ -249,5 +269,5 @@ class EPModule:
         else:
             ids, tw = self.route(data["router_logits"].float().contiguous())
         if self.exchange is not None:
-            return self.exchange.step(x, ids, tw, self._experts, self.per_rank)
+            return self.exchange.step(x, ids, tw, self._experts, self.per_rank, deadline_s=self.deadline_s)
         return ep_step(x, ids, tw, self._experts, self.per_rank, self.group)

@@ -299,6 +299,32 @@ def test_plan_is_a_function_of_the_configuration_only():
     assert lib.msk_moe_plan(ctypes.byref(cfg), 64, plan) == 0 and tuple(plan) == (16, 1, 0, 37)
 
 
+def test_workspace_init_covers_every_control_word():
+    """msk_moe_workspace_init zeroes everything in front of `inter`: the status word, the sort tables,
+    both ticket regions, the control words of the few-token paths (token tickets, grid and tile
+    counters) and the per-CTA counts of the multi-CTA sort must all lie there."""
+    from muse_moe_w4a16 import _lib
+
+    lib = _lib.load()
+    cfg = _lib.MskMoeCfg(hidden=4096, inter=1536, n_experts=128, local_start=0, local_count=128, top_k=8, max_tokens=256)
+    base = 1 << 20
+
+    def off(which):
+        p = ctypes.c_void_p()
+        assert lib.msk_moe_workspace_view(ctypes.byref(cfg), ctypes.c_void_p(base), which, ctypes.byref(p)) == 0
+        return p.value - base
+
+    inter = off(4)
+    pairs = max(1536 // 128, 4096 // 256)
+    tiles = 256 * 8 // 16 + 128
+    for which, nbytes in ((0, 128 * 4), (1, 129 * 4), (2, 2048 * 4), (3, 2048 * 4), (7, 2 * tiles * pairs * 4),
+                          (8, 8192), (9, 64 * 256 * 4)):
+        assert 256 <= off(which) and off(which) + nbytes <= inter, which
+    ws = ctypes.c_size_t()
+    assert lib.msk_moe_workspace_bytes(ctypes.byref(cfg), ctypes.byref(ws)) == 0
+    assert ws.value < 200 << 20      # the pieces of cut units take two slots per CTA, not a split-K buffer per unit
+
+
 def test_module_refuses_cpu_tensors():
     import muse_moe_w4a16 as moe
     from muse_moe_w4a16 import inputs

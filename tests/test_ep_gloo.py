@@ -83,3 +83,77 @@ def test_combine_partials_skips_ranks_without_a_route():
     assert float((out.float() - want).abs().max()) <= 2e-2
     own = ep.combine_partials(poisoned, ids, per, self_rank=2, self_rows=back[2])
     assert torch.equal(own, out)
+
+
+def _worker_peer_leaves(rank, world, port, ret):
+    """Rank 1 leaves between steps (it never joins the exchange); rank 0 must get an error from its
+    collective within the process group's time limit instead of waiting for ever."""
+    import datetime
+    import sys
+    import time
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    sys.path[:0] = [root, os.path.join(root, "muse-spark-kernels_b200")]
+    from muse_moe_w4a16 import ep
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=4))
+    dist.barrier()                                   # both ranks are up
+    if rank == 1:
+        ret[rank] = "left"
+        return                                       # gone before the step, nothing of it in flight
+    T, H, k, per = 5, 64, 2, 4
+    x = torch.zeros((T, H), dtype=torch.bfloat16)
+    ids = torch.zeros((T, k), dtype=torch.int64)
+    tw = torch.ones((T, k))
+    t0 = time.time()
+    try:
+        ep.ep_step(x, ids, tw, lambda rows, rids, rw: rows, per)
+        ret[rank] = "no error"
+    except Exception as exc:                         # a time-out / connection error of the collective
+        ret[rank] = ("error", type(exc).__name__, time.time() - t0)
+
+
+def test_ep_step_surfaces_a_missing_rank_as_an_error():
+    world = 2
+    port = _free_port()
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    ctx = mp.spawn(_worker_peer_leaves, args=(world, port, ret), nprocs=world, join=False)
+    ctx.join(timeout=60)
+    for proc in ctx.processes:
+        if proc.is_alive():
+            proc.terminate()
+    assert ret.get(1) == "left"
+    assert isinstance(ret.get(0), tuple) and ret[0][0] == "error", ret.get(0)
+    assert ret[0][2] < 30.0
+
+
+def test_exchange_deadline_raises_when_an_event_never_completes():
+    """Host-side deadline of the GPU exchange, against a fake event: a peer that never answers leaves
+    the last event of a step incomplete; wait_deadline must raise after the limit, not block."""
+    import time
+
+    from muse_moe_w4a16 import ep
+
+    class NeverDone:
+        def query(self):
+            return False
+
+    class DoneAfter:
+        def __init__(self, n):
+            self.n = n
+
+        def query(self):
+            self.n -= 1
+            return self.n <= 0
+
+    t0 = time.time()
+    try:
+        ep.wait_deadline(NeverDone(), 0.2, "step 7")
+        raised = False
+    except TimeoutError as exc:
+        raised = "step 7" in str(exc)
+    assert raised and 0.15 < time.time() - t0 < 5.0
+    ep.wait_deadline(DoneAfter(3), 5.0, "step 8")    # completes: returns

@@ -616,3 +616,133 @@ def test_state_hygiene_token_sequence_and_guard_words(cuda_dev):
             _, ids, tw = m.kernel_fn(data, fresh, return_routing=True)
             ref = orc.moe_forward(data["hidden_states"], ids, tw, w).float()
             assert _rel(got, ref) <= TOL
+
+
+def test_bounded_wait_runs_out_cleanly_and_the_state_recovers(cuda_dev):
+    """Failure detection without a fault: the streaming probe is told to withhold one slot release, so
+    its producer's bounded wait (one second) runs out; the kernel must come back by itself with the
+    time-out status, leave the context usable, and the library must work normally afterwards. Then the
+    recovery path of a state: a workspace whose control words were left dirty (as a kernel that gave
+    up would leave them) is put back by reinit_workspace and gives the clean result again."""
+    import time
+
+    m, inputs, _lib, orc = _mods()
+    t0 = time.time()
+    gbs, status = m.bw_probe(nbytes=64 << 20, skip_release=2, device=cuda_dev)
+    assert status == 1                       # MSK_DEV_ERR_TIMEOUT, reported, not trapped
+    assert 0.5 < time.time() - t0 < 30.0     # the one-second limit, not an endless spin
+    gbs, status = m.bw_probe(nbytes=256 << 20, device=cuda_dev)
+    assert status == 0 and gbs > 500.0       # the context is alive and the same kernel streams again
+    H, I, E, k, T = 1024, 512, 16, 4, 8
+    w = inputs.make_weights(H, I, E, 7, cuda_dev, post_norm=True)
+    st = m.prepare(w, n_experts=E, top_k=k, max_tokens=32, flat_shares=1, decode_path=1)
+    g = torch.Generator(device=cuda_dev).manual_seed(3)
+    data = {"hidden_states": torch.randn((T, H), generator=g, device=cuda_dev).to(torch.bfloat16),
+            "router_logits": torch.randn((T, E), generator=g, device=cuda_dev)}
+    clean = m.kernel_fn(data, st).clone()
+    torch.cuda.synchronize()
+    views = {}
+    for which in (7, 8):                     # unit tickets, control words of the few-token paths
+        ptr = ctypes.c_void_p()
+        _lib.check(st["lib"].lib.msk_moe_workspace_view(ctypes.byref(st["cfg"]), _lib.ptr(st["workspace"]), which,
+                                                        ctypes.byref(ptr)), "view")
+        views[which] = ptr.value - st["workspace"].data_ptr()
+    st["workspace"][views[7]:views[7] + 64].fill_(1)      # tickets half-way
+    st["workspace"][views[8]:views[8] + 8192].fill_(3)    # token tickets, grid and tile counters
+    st["workspace"][:4].copy_(torch.tensor([1, 0, 0, 0], dtype=torch.uint8))   # sticky status word
+    assert m.read_status(st) == 1
+    m.reinit_workspace(st)
+    assert m.read_status(st) == 0
+    for path in (1, 3):
+        st["cfg"].decode_path = path
+        got = m.kernel_fn(data, st)
+        assert torch.equal(got, clean) if path == 1 else _rel(got, clean) <= 8e-3
+        torch.cuda.synchronize()
+        assert m.read_status(st) == 0
+
+
+def test_state_dict_round_trip_skips_the_repack(cuda_dev):
+    """state_dict() / load_state_dict(): the packed tiles, scales and configuration are enough to
+    rebuild a state; kernel_fn on the rebuilt state gives the same bits."""
+    import copy
+    import io
+
+    m, inputs, _lib, orc = _mods()
+    H, I, E, k, T = 1024, 512, 8, 2, 40
+    w = inputs.make_weights(H, I, E, 19, cuda_dev, post_norm=True)
+    g = torch.Generator(device=cuda_dev).manual_seed(5)
+    w["pre_norm_w"] = (torch.randn((H,), generator=g, device=cuda_dev) * 0.1).to(torch.bfloat16)
+    w["router"] = torch.randn((E, H), generator=g, device=cuda_dev) * 0.02
+    st = m.prepare(w, n_experts=E, top_k=k, max_tokens=64, routing_mode="softmax_topk")
+    x = torch.randn((T, H), generator=g, device=cuda_dev).to(torch.bfloat16)
+    want = m.kernel_fn({"hidden_states": x}, st)
+    buf = io.BytesIO()
+    torch.save(m.state_dict(st), buf)
+    buf.seek(0)
+    st2 = m.load_state_dict(torch.load(buf, map_location="cpu"), device=cuda_dev)
+    assert st2["cfg"].hidden == H and st2["cfg"].max_tokens == 64
+    assert torch.equal(m.kernel_fn({"hidden_states": x}, st2), want)
+    assert torch.equal(m.kernel_fn({"hidden_states": x}, copy.deepcopy(st2)), want)
+    back = m.export_weights(st2)
+    assert torch.equal(back["w13"], w["w13"]) and torch.equal(back["w2_sf"], w["w2_sf"].view(torch.uint8))
+
+
+def test_prefill_moe_runs_the_prefill_layer_call_site(cuda_dev):
+    """The prefill layer's expert step (muse_prefill_layer/py/04_moe_forward.py:6-52 followed by its
+    combine): un-normed pooler rows, local ids with -1, routing weights in; pre-expert norm, both
+    GEMMs, post-expert norm and weighted sum out. T = 700 with the reference's skewed counts."""
+    m, inputs, _lib, orc = _mods()
+    from muse_moe_w4a16.compat import PrefillMoe
+
+    H, I, k, T = 1024, 512, 8, 700
+    counts = [300, 200, 100, 60, 33, 17, 14, 5, 1]
+    E = len(counts)
+    lid = torch.full((T * k,), -1, dtype=torch.int32)
+    pos = torch.zeros((T * k,), dtype=torch.int32)
+    r = 0
+    for e, c in enumerate(counts):
+        idx = torch.arange(r, r + c)
+        lid[(idx % T) * k + idx // T] = e
+        pos[(idx % T) * k + idx // T] = torch.arange(c, dtype=torch.int32)
+        r += c
+    lid, pos = lid.view(T, k).to(cuda_dev), pos.view(T, k).to(cuda_dev)
+    cnt = torch.tensor(counts, dtype=torch.int32, device=cuda_dev)
+    w = inputs.make_weights(H, I, E, 23, cuda_dev, post_norm=True)
+    g = torch.Generator(device=cuda_dev).manual_seed(29)
+    w["pre_norm_w"] = (torch.randn((H,), generator=g, device=cuda_dev) * 0.1).to(torch.bfloat16)
+    ext = PrefillMoe(m.prepare(w, local_start=0, n_experts=E, top_k=k, max_tokens=T))
+    p = (torch.randn((T, H), generator=g, device=cuda_dev) * 2.0).to(torch.bfloat16)
+    topw = torch.rand((T, k), generator=g, device=cuda_dev)
+    moe_out = torch.full((T, H), float("nan"), dtype=torch.bfloat16, device=cuda_dev)
+    ex = ext.moe_forward(p, lid, pos, cnt, T, topw, out=moe_out)
+    ext.moe_combine(None, ex["rrow"], lid, topw, w["post_norm_w"], moe_out)
+    torch.cuda.synchronize()
+    ref, parts = orc.moe_forward(p, lid, topw, w, return_parts=True)
+    assert _rel(moe_out, parts["out_fp32"]) <= TOL
+    assert ex["out"].data_ptr() == moe_out.data_ptr()
+    assert np.array_equal(ex["rrow"].tensor().cpu().numpy().reshape(-1), parts["inv"])
+
+
+def test_activations_outside_the_f16_range_saturate_as_documented(cuda_dev):
+    """The MMA operands are F16: a BF16 activation beyond +-65504 enters the GEMM as +-65504 (and one
+    below 2^-24 as zero), and so does a SwiGLU value that large. The result must equal the oracle
+    evaluated with its operands saturated the same way, and rows inside the range must not be affected
+    by a saturating neighbour."""
+    m, inputs, _lib, orc = _mods()
+    H, I, E, k, T = 512, 256, 8, 2, 6
+    w = inputs.make_weights(H, I, E, 31, cuda_dev)
+    st = m.prepare(w, n_experts=E, top_k=k, max_tokens=T)
+    g = torch.Generator(device=cuda_dev).manual_seed(37)
+    x = torch.randn((T, H), generator=g, device=cuda_dev).to(torch.bfloat16)
+    x[1, 5] = 3.0e5          # beyond the F16 range
+    x[1, 9] = -1.0e6
+    x[2, 7] = 1.0e-9         # below the smallest F16 subnormal
+    logits = torch.randn((T, E), generator=g, device=cuda_dev)
+    out, ids, tw = m.kernel_fn({"hidden_states": x, "router_logits": logits}, st, return_routing=True)
+    torch.cuda.synchronize()
+    ref = orc.moe_forward(x, ids, tw, w, f16_operands=True).float()   # x and inter saturated as the F16 operands are
+    assert torch.isfinite(out.float()).all()
+    assert _rel(out, ref) <= TOL
+    plain = orc.moe_forward(x, ids, tw, w).float()
+    keep = [0, 2, 3, 4, 5]
+    assert _rel(out[keep], plain[keep]) <= TOL
