@@ -472,7 +472,10 @@ def run_ep(args, spec, dev):
     dist.broadcast(single_ms, 0)
     dist.broadcast(ref_rows, 0)
 
-    mod = ep.EPModule(rank_weights(rank), rank, world, E, k, T, chunks=(args.ep_chunks or None))
+    chunks = None
+    if args.ep_chunks:
+        chunks = [int(v) for v in args.ep_chunks.split(",")] if "," in args.ep_chunks else int(args.ep_chunks)
+    mod = ep.EPModule(rank_weights(rank), rank, world, E, k, T, chunks=chunks)
     torch.cuda.empty_cache()
     pool = [rank_input(rank, i) for i in range(4)]
     host_pool = [{"hidden_states": d["hidden_states"].cpu().pin_memory(),
@@ -516,6 +519,26 @@ def run_ep(args, spec, dev):
     run(max(args.warmup, 3), True)
     ms_e2e = run(args.steps, True)
     clocks = sampler.stop()
+    timeline = None
+    if args.ep_timeline and mod.exchange is not None:
+        # where a step's time goes: CUDA events on the main stream of every rank (ms after the step's start;
+        # median of 5 steps), reduced to the slowest rank per mark
+        rows = []
+        for i in range(7):
+            mod.exchange.marks = []
+            dist.barrier()
+            mod.kernel_fn(pool[i % len(pool)])
+            torch.cuda.synchronize()
+            if i >= 2:
+                m0 = mod.exchange.marks[0][1]
+                rows.append([m0.elapsed_time(ev) for _, ev in mod.exchange.marks])
+        labels = [lab for lab, _ in mod.exchange.marks]
+        mod.exchange.marks = None
+        med = torch.tensor(rows, device=dev).median(0).values
+        worst, best = med.clone(), med.clone()
+        dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+        dist.all_reduce(best, op=dist.ReduceOp.MIN)
+        timeline = {lab: {"max_ms": float(a), "min_ms": float(b)} for lab, a, b in zip(labels, worst.tolist(), best.tolist())}
     status = torch.tensor([moe.read_status(mod.state)], device=dev)
     dist.all_reduce(status, op=dist.ReduceOp.MAX)
     if int(status.item()) != 0:
@@ -534,13 +557,13 @@ def run_ep(args, spec, dev):
             "config": {"workload": spec["name"], "tokens_per_gpu": T, "hidden": H, "inter": I, "experts": E,
                        "top_k": k, "parallelism": f"ep{world}",
                        "l2": "inputs and weights exceed L2 (792 MB of weights per rank at 8 ranks)",
-                       "dispatch": f"{mod.transport}, {mod.chunks} chunk(s) of source ranks", "build_id": _lib.build_id()},
+                       "dispatch": f"{mod.transport}, source ranks in chunks of {mod.sizes}", "build_id": _lib.build_id()},
             "e2e": {"value": T * world * args.steps / (ms_e2e * 1e-3), "unit": UNIT,
                     "h2d_bytes_per_step": (T * H * 2 + T * E * 4) * world, "d2h_bytes_per_step": T * H * 2 * world,
                     "ms_per_step": ms_e2e / args.steps},
             # per rank and step: top-k, the final rank-order sum, and per chunk the sort (three launches from
             # 16384 entries on), the F16 row copy, two GEMMs and the combine
-            "gpu_launches": (2 + (7 if (world // mod.chunks) * T * k >= 16384 else 5) * mod.chunks) * args.steps * world,
+            "gpu_launches": (2 + sum(7 if m * T * k >= 16384 else 5 for m in mod.sizes)) * args.steps * world,
             "ep_parity_max_rel": ep_parity, "ep_parity_tokens_per_rank": CHECK,
             "single_gpu_same_shape_ms": float(single_ms.item()),
             "scaling_efficiency": float(single_ms.item()) / step_ms,
@@ -553,6 +576,8 @@ def run_ep(args, spec, dev):
             "cpu_baseline": None,
             "clocks": clocks,
         }
+        if timeline is not None:
+            line["ep_timeline_ms"] = timeline
         print(json.dumps(line), flush=True)
     dist.barrier()
     dist.destroy_process_group()
@@ -567,7 +592,9 @@ def main():
     ap.add_argument("--workload", default="auto")
     ap.add_argument("--no-sweep", action="store_true", help="one GPU, default workload: leave out the other points of the metric")
     ap.add_argument("--experts", type=int, default=0, help="resident experts (smaller case for profiler captures)")
-    ap.add_argument("--ep-chunks", type=int, default=0, help="expert-parallel runs: chunks of source ranks (0 = default)")
+    ap.add_argument("--ep-chunks", default="", help="expert-parallel runs: number of equal chunks of source ranks, or their sizes "
+                                                    "as a comma list (own rank first), e.g. 1,3,3,1; empty = default")
+    ap.add_argument("--ep-timeline", action="store_true", help="expert-parallel runs: add per-chunk event times of a step to the line")
     ap.add_argument("--token-tile", type=int, default=0, help="force a kernel: 16/32/64/128, 8 = the mma.sync single-launch kernel")
     ap.add_argument("--decode-path", type=int, default=0, help="few tokens: 0 one launch, 1 chain of launches, 2 three launches")
     ap.add_argument("--flush", default="read", choices=["read", "write"], help="how L2 is flushed before a timed step")

@@ -107,6 +107,17 @@ int msk_moe_dequant_packed(const MskMoeCfg* cfg, const void* packed13, const voi
 int msk_moe_router_logits(const MskMoeCfg* cfg, const void* x, const float* router_w, float* logits, int n_tokens,
                           void* stream);
 
+/* The same logits as a tensor-core GEMM (tcgen05, FP32 accumulation) for 16 tokens and more, with the
+ * FP32 router weight held the way the reference's layers hold it: an exact-sum pair of BF16 matrices
+ * hi = bf16(w), lo = bf16(w - hi), stacked [hi; lo] as bf16 [2E, H]
+ * (muse_decode_layer/py/05_tune.py:279-286, muse_prefill_layer/py/00_layer.py:369-374). Products are
+ * exact; every logit is accumulated in one fixed order, so repeated calls give the same bits. The
+ * logits differ from the FP32 product by what w - hi - lo drops (about 2^-17 of a weight), so a
+ * top-k taken from them can differ from the FP32 one where two scores are closer than that.
+ * status_word (nullable): receives 1 when a bounded wait in the kernel gave up. */
+int msk_moe_router_logits_hilo(const MskMoeCfg* cfg, const void* x, const void* router_hilo, float* logits,
+                               int32_t* status_word, int n_tokens, void* stream);
+
 /* Top-k of fp32 logits [T, E]; ties go to the lowest expert index. bias may be NULL
  * (softmax mode ignores it). Writes ids int32 [T, k] (global ids, descending score) and
  * weights fp32 [T, k]. */

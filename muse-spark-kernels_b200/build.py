@@ -13,7 +13,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "muse_moe_w4a16", "libmsk_moe.so")
 SOURCES = ["msk_moe.cu"]
-HEADERS = ["ptx.cuh", "layout.cuh", "route_sort.cuh", "gemm.cuh", "gemm_producer.inl", "gemm_mma.inl",
+HEADERS = ["ptx.cuh", "layout.cuh", "route_sort.cuh", "router_gemm.cuh", "gemm.cuh", "gemm_producer.inl", "gemm_mma.inl",
            "gemm_gather.inl", "gemm_dequant.inl", "gemm_epilogue.inl", os.path.join("..", "..", "include", "msk_moe.h")]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",  # the explicit pair: -arch=sm_100a drops the 'a' features

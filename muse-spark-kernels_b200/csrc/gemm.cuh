@@ -85,8 +85,12 @@ struct GemmCfg {
   static constexpr int SLOT_COLS = 64;
   static constexpr int A_GROUP_COLS = NSLOT * SLOT_COLS;
   // Token tiles of 64 and more fetch the activation operand with TMA (2-D boxes of 64 K x N rows,
-  // 128-byte swizzle) from rows that are contiguous in sorted order; narrower tiles gather rows
-  // through the permutation with cp.async (gemm_gather.inl).
+  // 128-byte swizzle) from rows that are contiguous in sorted order (the sorted F16 copy of the token
+  // rows for the gate/up GEMM, `inter` for the down GEMM); narrower tiles gather rows through the
+  // permutation with cp.async (gemm_gather.inl). Gathering the wide tiles' rows with cp.async as well
+  // (four warps, straight from the unsorted F16 rows, no sorted copy) was built and measured: the
+  // 16-byte requests load L2 so much less efficiently than TMA's full lines that the gate/up GEMM of
+  // the 8192-token step took 3.08 ms instead of 1.48 ms, far more than the 0.22 ms the copy costs.
   static constexpr bool TMA_B = N >= 64;
   static constexpr int LUT_BYTES = 0;
   static constexpr int CTRL_BYTES = 1024;  // barriers, TMEM base, abort word, tile table header
@@ -466,7 +470,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) moe_gemm_kernel(const __grid_
   constexpr int NDBUF = C::NDBUF;
   constexpr int PH_FIRST = MODE == 1 ? 1 : 0, PH_LAST = MODE == 0 ? 0 : 1;
   constexpr bool FUSED = MODE == 2;
-  static_assert(!(FUSED && (C::TMA_B || NDBUF == 1)), "the one-launch mode is built for the narrow token tiles");
+  constexpr bool TMA_B = C::TMA_B;
+  static_assert(!(FUSED && (TMA_B || NDBUF == 1)), "the one-launch mode is built for the narrow token tiles");
   extern __shared__ __align__(1024) uint8_t smem[];
   uint8_t* ring = smem;                                        // NST x [tile g0 | tile g1 | B]
   GemmCtrl& ctl = *reinterpret_cast<GemmCtrl*>(smem + NST * C::STAGE_BYTES + C::LUT_BYTES);

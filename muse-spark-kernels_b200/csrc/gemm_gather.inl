@@ -5,7 +5,8 @@
 // 128-byte core matrix, so shared-memory writes are conflict free. A stage is published a few
 // stages late, once its copies have landed and a proxy fence has ordered them before the
 // tensor core's reads.
-    if (!C::TMA_B) {
+    if (!TMA_B) {
+    constexpr int NG = N / 8;   // 8-token groups of the tile
     const int n_sub = lane & 7, c_sub = lane >> 3;  // token within an 8-group, chunk within a 4-chunk group
     // A stage is published GLAG stages after it was issued, so the loop never waits for the
     // copies it has just started (one stage of lag made every iteration a full memory latency).
@@ -41,9 +42,9 @@
       while (ok && pieces.next(base, ks0, ks1)) {
         const UnitInfo ui = decode_unit(base, tile_start, pp.n_pairs, p.nloc, N);
         // source row of token n = ng*8 + n_sub, for every 8-group ng
-        const __half* src[N / 8];
+        const __half* src[NG];
 #pragma unroll
-        for (int ng = 0; ng < N / 8; ++ng) {
+        for (int ng = 0; ng < NG; ++ng) {
           const int n = ng * 8 + n_sub;
           src[ng] = nullptr;
           if (n < ui.rows) {
@@ -85,7 +86,7 @@
           if (!mbar_wait(&ctl.b_empty[slot], par ^ 1u, abortw)) { ok = false; break; }
           uint8_t* dstB = ring + slot * C::STAGE_BYTES + 2 * TILE_BYTES;
 #pragma unroll
-          for (int ng = 0; ng < N / 8; ++ng) {
+          for (int ng = 0; ng < NG; ++ng) {
             const bool valid = src[ng] != nullptr;
             const __half* s = valid ? src[ng] + static_cast<size_t>(ks) * KS : static_cast<const __half*>(pp.act);
 #pragma unroll

@@ -38,7 +38,7 @@
 #pragma unroll
               for (int kk = 0; kk < 8; ++kk) {
                 const int k16 = sl * 8 + kk;
-                const uint64_t bdesc = C::TMA_B ? smem_desc_kmajor_sw128(b_addr + (k16 >> 2) * (N * 128) + (k16 & 3) * 32)
+                const uint64_t bdesc = TMA_B ? smem_desc_kmajor_sw128(b_addr + (k16 >> 2) * (N * 128) + (k16 & 3) * 32)
                                                 : smem_desc_kmajor_noswz(b_addr + k16 * 256, B_LBO, B_SBO);
                 const uint32_t acc = (ks > ks0 || k16 > 0) ? 1u : 0u;
                 mma_ts(d_tmem, a_base + as * C::SLOT_COLS + kk * 8, bdesc, idesc_u, acc);

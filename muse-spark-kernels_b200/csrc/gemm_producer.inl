@@ -25,7 +25,7 @@
             bulk_g2s(dst, g0 + static_cast<size_t>(ks) * TILE_BYTES, TILE_BYTES, &ctl.raw_full[slot], pol);
             bulk_g2s(dst + TILE_BYTES, g1 + static_cast<size_t>(ks) * TILE_BYTES, TILE_BYTES, &ctl.raw_full[slot], pol);
             if (it == 0) MSK_TR(TR_FIRST_BULK);
-            if (C::TMA_B) {
+            if (TMA_B) {
               // activation tile of the stage: four boxes of 64 K x N rows, rows row0.. of the sorted matrix
               if (MODE == 1 && it == 0) pdl_wait();  // inter comes from the gate/up GEMM
               if (!mbar_wait(&ctl.b_empty[slot], par ^ 1u, abortw)) { ok = false; break; }

@@ -13,6 +13,7 @@
 #include "../../include/msk_moe.h"
 #include "route_sort.cuh"
 #include "gemm.cuh"
+#include "router_gemm.cuh"
 
 namespace msk {
 
@@ -572,7 +573,8 @@ typedef CUresult (*TensorMapEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint3
                                       const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                       CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-static int encode_act_map(CUtensorMap* map, const void* base, size_t rows, int K, int box_rows) {
+static int encode_act_map(CUtensorMap* map, const void* base, size_t rows, int K, int box_rows,
+                          CUtensorMapDataType dtype = CU_TENSOR_MAP_DATA_TYPE_FLOAT16) {
   static TensorMapEncodeFn fn = nullptr;
   if (fn == nullptr) {
     void* ptr = nullptr;
@@ -586,7 +588,7 @@ static int encode_act_map(CUtensorMap* map, const void* base, size_t rows, int K
   const cuuint64_t strides[1] = {static_cast<cuuint64_t>(K) * 2};
   const cuuint32_t box[2] = {64u, static_cast<cuuint32_t>(box_rows)};
   const cuuint32_t estr[2] = {1u, 1u};
-  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+  const CUresult r = fn(map, dtype, 2, const_cast<void*>(base), dims, strides, box, estr,
                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : static_cast<int>(cudaErrorInvalidValue);
@@ -660,6 +662,31 @@ static RepackGeom geom2(const MskMoeCfg* c) {
 }
 static long long n_tiles_of(const MskMoeCfg* c, const RepackGeom& g) {
   return static_cast<long long>(c->local_count) * g.tiles_per_expert * g.n_stages;
+}
+
+template <int N>
+static int launch_router_hilo(const CUtensorMap& mw, const CUtensorMap& mx, float* logits, int32_t* status, int T, int E,
+                              int H, cudaStream_t st) {
+  const int smem = RG_STAGES * (2 * RG_A_BYTES + N * RG_KSTEP * 2) + static_cast<int>(sizeof(RouterGemmCtrl));
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    const cudaError_t e = cudaFuncSetAttribute(router_hilo_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    attr_set[dev] = true;
+  }
+  cudaLaunchConfig_t lc{};
+  lc.gridDim = dim3(static_cast<unsigned>((E + 127) / 128), static_cast<unsigned>((T + N - 1) / N));
+  lc.blockDim = dim3(RG_THREADS);
+  lc.dynamicSmemBytes = smem;
+  lc.stream = st;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  lc.attrs = at;
+  lc.numAttrs = 1;
+  return static_cast<int>(cudaLaunchKernelEx(&lc, router_hilo_kernel<N>, mw, mx, logits, status, T, E, H));
 }
 
 }  // namespace msk
@@ -743,6 +770,31 @@ int msk_moe_router_logits(const MskMoeCfg* cfg, const void* x, const float* rout
   router_logits_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(x), router_w, logits, cfg->hidden, cfg->n_experts);
   return static_cast<int>(cudaGetLastError());
+}
+
+int msk_moe_router_logits_hilo(const MskMoeCfg* cfg, const void* x, const void* router_hilo, float* logits,
+                               int32_t* status_word, int n_tokens, void* stream) {
+  const int rc = check_cfg(cfg);
+  if (rc != MSK_OK) return rc;
+  if (!x || !router_hilo || !logits) return MSK_ERR_NULL;
+  if (!aligned16(x) || !aligned16(router_hilo) || !aligned16(logits)) return MSK_ERR_ALIGN;
+  if (n_tokens < 0) return MSK_ERR_SHAPE;
+  if (n_tokens == 0) return MSK_OK;
+  if (n_tokens < 16) return MSK_ERR_SHAPE;   // fewer tokens than the narrowest MMA tile: use msk_moe_router_logits
+  const int N = n_tokens >= 128 ? 128 : n_tokens >= 64 ? 64 : n_tokens >= 32 ? 32 : 16;
+  CUtensorMap mw, mx;
+  int e = encode_act_map(&mw, router_hilo, static_cast<size_t>(2) * cfg->n_experts, cfg->hidden, 128,
+                         CU_TENSOR_MAP_DATA_TYPE_BFLOAT16);
+  if (e != 0) return e;
+  e = encode_act_map(&mx, x, static_cast<size_t>(n_tokens), cfg->hidden, N, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16);
+  if (e != 0) return e;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (N) {
+    case 128: return launch_router_hilo<128>(mw, mx, logits, status_word, n_tokens, cfg->n_experts, cfg->hidden, st);
+    case 64: return launch_router_hilo<64>(mw, mx, logits, status_word, n_tokens, cfg->n_experts, cfg->hidden, st);
+    case 32: return launch_router_hilo<32>(mw, mx, logits, status_word, n_tokens, cfg->n_experts, cfg->hidden, st);
+    default: return launch_router_hilo<16>(mw, mx, logits, status_word, n_tokens, cfg->n_experts, cfg->hidden, st);
+  }
 }
 
 int msk_moe_route(const MskMoeCfg* cfg, const float* logits, const float* bias, int32_t* topk_ids,

@@ -76,6 +76,19 @@ def prepare(weights, *, local_start=0, n_experts=None, top_k=8, max_tokens=8192,
                        weights.get("router"), weights.get("route_bias"))
 
 
+ROUTER_GEMM_MIN_TOKENS = 16   # from here on the router logits come from the tensor-core GEMM
+
+
+def split_router(router):
+    """FP32 router weight [E, H] -> bf16 [2E, H] = [hi; lo] with hi = bf16(w), lo = bf16(w - hi): the
+    pair whose sum the reference's layers feed to their BF16 GEMM
+    (muse_decode_layer/py/05_tune.py:279-286, muse_prefill_layer/py/00_layer.py:369-374)."""
+    w = router.float()
+    hi = w.to(torch.bfloat16)
+    lo = (w - hi.float()).to(torch.bfloat16)
+    return torch.cat([hi, lo], 0).contiguous()
+
+
 def _make_state(cfg, packed13, packed2, gs13, gs2, post_norm_w, pre_norm_w, pre_norm_eps, router, route_bias):
     """The state dict around already packed weights: allocates and initialises the workspace."""
     lib = _lib.load()
@@ -95,6 +108,7 @@ def _make_state(cfg, packed13, packed2, gs13, gs2, post_norm_w, pre_norm_w, pre_
         "pre_norm_w": None if pre_norm_w is None else pre_norm_w.contiguous(),
         "pre_norm_eps": float(pre_norm_eps),
         "router": None if router is None else router.float().contiguous(),
+        "router_hilo": None if router is None else split_router(router),
         "route_bias": None if route_bias is None else route_bias.float().contiguous(),
         "workspace": workspace, "workspace_bytes": wsb.value,
     }
@@ -153,8 +167,14 @@ def _logits(data, state, x, T):
         if state["router"] is None:
             raise RuntimeError("muse_moe_w4a16.kernel_fn: need topk_ids/topk_weights, router_logits or weights['router']")
         logits = torch.empty((T, cfg.n_experts), dtype=torch.float32, device=x.device)
-        _lib.check(lib.msk_moe_router_logits(ctypes.byref(cfg), _lib.ptr(x), _lib.ptr(state["router"]),
-                                             _lib.ptr(logits), T, _stream()), "msk_moe_router_logits")
+        if T >= ROUTER_GEMM_MIN_TOKENS and state.get("router_hilo") is not None and state.get("router_gemm", True):
+            # tensor-core GEMM on the BF16 hi + lo pair of the router weight
+            _lib.check(lib.msk_moe_router_logits_hilo(ctypes.byref(cfg), _lib.ptr(x), _lib.ptr(state["router_hilo"]),
+                                                      _lib.ptr(logits), _lib.ptr(state["workspace"]), T, _stream()),
+                       "msk_moe_router_logits_hilo")
+        else:   # few tokens: FP32 matvec in a fixed summation order
+            _lib.check(lib.msk_moe_router_logits(ctypes.byref(cfg), _lib.ptr(x), _lib.ptr(state["router"]),
+                                                 _lib.ptr(logits), T, _stream()), "msk_moe_router_logits")
     return logits.to(torch.float32).contiguous()
 
 

@@ -65,6 +65,7 @@ SIGNATURES = {
     "msk_moe_unpack": [_CFG, _P, _P, _P, _P, _P, _P, _P],
     "msk_moe_dequant_packed": [_CFG, _P, _P, _P, _P, _P],
     "msk_moe_router_logits": [_CFG, _P, _P, _P, ctypes.c_int, _P],
+    "msk_moe_router_logits_hilo": [_CFG, _P, _P, _P, _P, ctypes.c_int, _P],
     "msk_moe_route": [_CFG, _P, _P, _P, _P, ctypes.c_int, _P],
     "msk_moe_sort": [_CFG, _P, ctypes.c_int, _P, _P, _P, _P, _P],
     "msk_moe_workspace_bytes": [_CFG, _SZP],

@@ -44,6 +44,29 @@ def wait_deadline(event, seconds, what):
         time.sleep(0.0005)
 
 
+def chunk_sizes(world, chunks=None):
+    """How the `world` source ranks (slot 0 = this rank's own tokens, slot j = rank + j) are grouped into
+    chunks that are processed one after the other. chunks: None (default), a number of equal chunks,
+    or the sizes themselves. The default starts with the rank's own tokens alone (they need no transfer,
+    so nothing is waited for at the head of the step) and ends with a single source rank (so that only
+    one rank's partial rows are still on their way back when the expert kernels have finished)."""
+    if chunks is None:
+        if world <= 2:
+            return [world]
+        if world == 3:
+            return [1, 2]
+        mid = world - 2
+        return [1] + ([mid] if mid <= 2 else [mid - mid // 2, mid // 2]) + [1]
+    if isinstance(chunks, int):
+        if chunks < 1 or world % chunks != 0:
+            raise ValueError("the number of chunks must divide the number of ranks")
+        return [world // chunks] * chunks
+    sizes = [int(v) for v in chunks]
+    if sum(sizes) != world or min(sizes) < 1:
+        raise ValueError("chunk sizes must be positive and add up to the number of ranks")
+    return sizes
+
+
 def owner_rank(ids, experts_per_rank):
     return torch.div(ids, experts_per_rank, rounding_mode="floor")
 
@@ -129,10 +152,10 @@ class SymmExchange:
 
         from . import _lib
 
-        if world % chunks != 0:
-            raise ValueError("chunks must divide the number of ranks")
         self.rank, self.n, self.T, self.H, self.k = rank, world, tokens, hidden, top_k
-        self.chunks, self.m = chunks, world // chunks
+        self.sizes = chunk_sizes(world, chunks)
+        self.chunks = len(self.sizes)
+        self.bounds = [sum(self.sizes[:i]) for i in range(self.chunks + 1)]   # chunk c = slots [bounds[c], bounds[c+1])
         self.lib = _lib.load()
         g = group if group is not None else dist.group.WORLD
 
@@ -153,6 +176,7 @@ class SymmExchange:
         self.back = torch.empty((n, T, H), dtype=torch.bfloat16, device=device)
         self.comm = torch.cuda.Stream(device)
         self.epoch = 0
+        self.marks = None      # set to a list to have step() record (label, CUDA event) pairs on the main stream
         torch.cuda.synchronize(device)
         dist.barrier(group)                      # every rank's flags are zero before anyone writes
 
@@ -173,11 +197,19 @@ class SymmExchange:
         deadline_s: when given, the host waits (polling, wait_deadline) until the last pull of the step has
         completed and raises TimeoutError if a peer does not answer in time; None keeps the step free of
         host synchronisation."""
-        n, r, m, T, H, k = self.n, self.rank, self.m, self.T, self.H, self.k
+        n, r, T, H, k = self.n, self.rank, self.T, self.H, self.k
+        bounds = self.bounds
         self.epoch += 1
         e, b = self.epoch, self.epoch & 1
         gx, gids, gtw, part = self.gx[b], self.gids[b], self.gtw[b], self.part[b]
         s0, s1 = torch.cuda.current_stream(), self.comm
+        def mark(label):
+            if self.marks is not None:
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record(s0)
+                self.marks.append((label, ev))
+
+        mark("start")
         gx[0].copy_(x)
         gids[0].copy_(ids)
         gtw[0].copy_(tw)
@@ -195,16 +227,19 @@ class SymmExchange:
                 gx[j].copy_(self.peer_gx[p][b, 0], non_blocking=True)
                 gids[j].copy_(self.peer_gids[p][b, 0], non_blocking=True)
                 gtw[j].copy_(self.peer_gtw[p][b, 0], non_blocking=True)
-                if (j + 1) % m == 0:
-                    ready[j // m] = torch.cuda.Event()
-                    ready[j // m].record(s1)
+                if j + 1 in bounds:                      # the last slot of a chunk has been issued
+                    c = bounds.index(j + 1) - 1
+                    ready[c] = torch.cuda.Event()
+                    ready[c].record(s1)
         # main stream: the local expert step chunk by chunk, own rows first
         for c in range(self.chunks):
             if c in ready:
                 s0.wait_event(ready[c])
-            sl = slice(c * m, (c + 1) * m)
+            mark(f"chunk{c}_rows_in")
+            sl, m = slice(bounds[c], bounds[c + 1]), self.sizes[c]
             expert_fn(gx[sl].view(m * T, H), gids[sl].view(m * T, k), gtw[sl].view(m * T, k), part[sl].view(m * T, H))
-            for j in range(max(c * m, 1), (c + 1) * m):
+            mark(f"chunk{c}_experts_done")
+            for j in range(max(bounds[c], 1), bounds[c + 1]):
                 self._write((r + j) % n, 2 * n + 2 * r + b, e, s0)
         # copy stream: pull this rank's partial rows back, in the order the peers finish them
         with torch.cuda.stream(s1):
@@ -217,7 +252,10 @@ class SymmExchange:
         if deadline_s is not None:
             wait_deadline(ev_back, deadline_s, f"step {e} on rank {r}")
         s0.wait_event(ev_back)
-        return combine_partials(self.back, gids[0], experts_per_rank, self_rank=r, self_rows=part[0])
+        mark("partials_back")
+        out = combine_partials(self.back, gids[0], experts_per_rank, self_rank=r, self_rows=part[0])
+        mark("combined")
+        return out
 
 
 class EPModule:
@@ -232,11 +270,11 @@ class EPModule:
         self.transport = transport
         self.deadline_s = deadline_s
         if transport == "symm":
-            # from four ranks on, chunks of two source ranks: measured on 8 GPUs, 4 chunks 4.63 ms per step,
-            # 2 chunks 5.45 ms (less of the exchange hidden), 8 chunks lose more in half-filled token tiles
-            self.chunks = chunks if chunks is not None else (world // 2 if world >= 4 and world % 2 == 0 else 1)
-            rows = (world // self.chunks) * tokens_per_rank
+            sizes = chunk_sizes(world, chunks)
+            self.sizes = sizes
+            self.chunks, rows = len(sizes), max(sizes) * tokens_per_rank
         elif transport == "collective":
+            self.sizes = [world]
             self.chunks, rows = 1, world * tokens_per_rank
         else:
             raise ValueError("transport must be 'symm' or 'collective'")
@@ -245,8 +283,7 @@ class EPModule:
         self.exchange = None
         if transport == "symm":
             dev = self.state["packed13"].device
-            self.exchange = SymmExchange(rank, world, tokens_per_rank, self.state["cfg"].hidden, top_k, self.chunks, dev,
-                                         group)
+            self.exchange = SymmExchange(rank, world, tokens_per_rank, self.state["cfg"].hidden, top_k, chunks, dev, group)
 
     def _experts(self, rows, ids, w, out=None):
         return self.moe.kernel_fn({"hidden_states": rows, "topk_ids": ids, "topk_weights": w}, self.state, out=out)

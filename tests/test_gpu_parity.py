@@ -746,3 +746,69 @@ def test_activations_outside_the_f16_range_saturate_as_documented(cuda_dev):
     plain = orc.moe_forward(x, ids, tw, w).float()
     keep = [0, 2, 3, 4, 5]
     assert _rel(out[keep], plain[keep]) <= TOL
+
+
+@pytest.mark.parametrize("T,E,H", [(16, 128, 512), (50, 256, 1024), (300, 8, 512), (1000, 128, 4096), (130, 384, 2048)])
+def test_router_logits_gemm_on_the_hi_lo_pair(cuda_dev, T, E, H):
+    """msk_moe_router_logits_hilo: the FP32 router weight as the reference's exact-sum BF16 pair
+    (muse_decode_layer/py/05_tune.py:279-286) through the tensor-core GEMM. The logits must equal the
+    FP64 product of x with hi + lo up to FP32 accumulation, stay within what w - hi - lo drops of the
+    FP32 product, repeat bit for bit, and give the FP32 matvec's top-k except where two scores are
+    closer than that difference (reported as tie-risk, not as a failure)."""
+    m, inputs, _lib, orc = _mods()
+    lib = _lib.load()
+    g = torch.Generator(device=cuda_dev).manual_seed(T + E)
+    w = torch.randn((E, H), generator=g, device=cuda_dev) * 0.02
+    x = torch.randn((T, H), generator=g, device=cuda_dev).to(torch.bfloat16)
+    hilo = m.split_router(w)
+    assert hilo.dtype == torch.bfloat16 and tuple(hilo.shape) == (2 * E, H)
+    k = min(8, E)
+    cfg = _lib.MskMoeCfg(hidden=H, inter=256, n_experts=E, local_start=0, local_count=min(E, 256), top_k=k, max_tokens=T)
+    st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    status = torch.zeros(4, dtype=torch.int32, device=cuda_dev)
+
+    def gemm():
+        out = torch.full((T, E), float("nan"), device=cuda_dev)
+        _lib.check(lib.msk_moe_router_logits_hilo(ctypes.byref(cfg), _lib.ptr(x), _lib.ptr(hilo), _lib.ptr(out),
+                                                  _lib.ptr(status), T, st), "router_logits_hilo")
+        return out
+
+    a = gemm()
+    b = gemm()
+    mv = torch.empty((T, E), device=cuda_dev)
+    _lib.check(lib.msk_moe_router_logits(ctypes.byref(cfg), _lib.ptr(x), _lib.ptr(w), _lib.ptr(mv), T, st), "router_logits")
+    torch.cuda.synchronize()
+    assert int(status[0]) == 0 and torch.equal(a, b) and torch.isfinite(a).all()
+    xd = x.double()
+    pair = xd @ (hilo[:E].double() + hilo[E:].double()).T
+    full = xd @ w.double().T
+    scale = float(full.abs().max())
+    assert float((a.double() - pair).abs().max()) <= 2e-5 * scale      # FP32 accumulation of exact products (up to 8192 of them)
+    assert float((a.double() - full).abs().max()) <= 5e-5 * scale      # plus the part of w the pair drops
+    ia, _ = orc.route_topk(a.cpu(), k)
+    ib, _ = orc.route_topk(mv.cpu(), k)
+    rows, slots = np.nonzero(ia.numpy() != ib.numpy())
+    fl = full.cpu().numpy()
+    for r, c in zip(rows, slots):      # tie-risk: the two candidates' exact scores are closer than the logits' error
+        assert abs(fl[r, ia[r, c]] - fl[r, ib[r, c]]) <= 1e-4 * scale, (r, c)
+    assert len(set(rows.tolist())) <= max(1, T // 50)
+
+
+def test_kernel_fn_with_router_weight_uses_the_gemm_from_sixteen_tokens(cuda_dev):
+    """weights["router"]: few tokens take the FP32 matvec, 16 and more the hi + lo GEMM; both feed the
+    same routing and expert kernels, and the output matches the oracle on the routing the module used."""
+    m, inputs, _lib, orc = _mods()
+    H, I, E, k = 1024, 512, 16, 4
+    w = inputs.make_weights(H, I, E, 41, cuda_dev)
+    g = torch.Generator(device=cuda_dev).manual_seed(43)
+    w["router"] = torch.randn((E, H), generator=g, device=cuda_dev) * 0.02
+    st = m.prepare(w, n_experts=E, top_k=k, max_tokens=256)
+    for T in (5, 16, 200):
+        x = torch.randn((T, H), generator=g, device=cuda_dev).to(torch.bfloat16)
+        out, ids, tw = m.kernel_fn({"hidden_states": x}, st, return_routing=True)
+        torch.cuda.synchronize()
+        assert m.read_status(st) == 0
+        rid, _ = orc.route_topk(orc.router_logits(x.cpu(), w["router"].cpu()), k)
+        assert float((ids.cpu() == rid).all(dim=1).float().mean()) >= 0.97      # near-ties may pick the neighbour
+        ref = orc.moe_forward(x, ids, tw, w).float()
+        assert _rel(out, ref) <= TOL
