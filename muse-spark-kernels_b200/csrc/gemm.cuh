@@ -196,7 +196,7 @@ struct UnitInfo {
 
 // base unit index -> (token tile, pair); the token tile is located in the per-expert exclusive
 // prefix of tile counts by binary search.
-__device__ __forceinline__ UnitInfo decode_unit(int base, const int* tile_start, int n_pairs, int nloc, int N) {
+__device__ __noinline__ UnitInfo decode_unit(int base, const int* tile_start, int n_pairs, int nloc, int N) {
   // tile_start is followed in shared memory by copies of cnt[] and off[] (GemmCfg::TABLE_INTS apart)
   const int* cnt_s = tile_start + (MAX_LOCAL_EXPERTS + 4);
   const int* off_s = cnt_s + (MAX_LOCAL_EXPERTS + 4);
@@ -630,6 +630,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) moe_gemm_kernel(const __grid_
   if (tid == 0) MSK_TR(TR_SETUP);
   const int iter_mode = (N < 128 && p.flat) ? 1 : 0;
   volatile int* abortw = &ctl.abort_word;
+#define MSK_WAIT(bar, par, ab) (N >= 64 ? mbar_wait_inline((bar), (par), (ab)) : mbar_wait((bar), (par), (ab)))
 #define MSK_PHASES for (int phase = PH_FIRST; phase <= PH_LAST; ++phase)
 #define MSK_PHASE_SETUP                                                                                           \
   const PhaseParams& pp = p.ph[phase];                                                                            \
@@ -655,6 +656,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) moe_gemm_kernel(const __grid_
 #include "gemm_epilogue.inl"
   }
 #undef MSK_PHASES
+#undef MSK_WAIT
 #undef MSK_PHASE_SETUP
 
   // -------------------------------------------------------------- teardown

@@ -24,13 +24,39 @@
       pending = false;
     };
     uint32_t unit_i = 0;
+    // Single accumulator buffer (the 128-token tile): the main loop cannot go on until the accumulators
+    // are drained, and the sixteen dequant warps drain them together (the four warps of a lane quarter
+    // split the columns). The drain of a unit is put off until this warp has decoded the first stage
+    // of the next unit into the A slots, which are free by then: when the drain ends, the MMA warps find
+    // their operands ready, and the bubble between two units is the drain alone, not the drain plus
+    // a refill of the decode pipeline.
+    bool owe_drain = false;
+    UnitInfo owed_ui;
+    uint32_t owed_unit_i = 0;
     MSK_PHASES {
       MSK_PHASE_SETUP;
+      auto drain = [&]() -> bool {
+        if (!MSK_WAIT(&ctl.d_full[0], owed_unit_i & 1u, abortw)) return false;
+        tc_fence_after();
+        if (tid == 256) { if (owed_unit_i == 0) MSK_TR(TR_FIRST_DFULL); MSK_TR(TR_LAST_DFULL); }
+        if (phase == 0) {
+          const int part = kh * 2 + g;  // 0..3: a quarter of the token columns, gate and up of this lane
+          epilogue_columns<N>(p, pp, phase, owed_ui, tmem + lane_base, row, part * (N / 4), (part + 1) * (N / 4), 0);
+        } else {
+          epilogue_columns<N>(p, pp, phase, owed_ui, tmem + lane_base, row, kh * (N / 2), (kh + 1) * (N / 2), g);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&ctl.d_empty[0]);
+        if (tid == 256 && owed_unit_i == 0) MSK_TR(TR_FIRST_EPI_DONE);
+        owe_drain = false;
+        return true;
+      };
       for (; ok && pieces.next(base, ks0, ks1); ++unit_i) {
         const UnitInfo ui = decode_unit(base, tile_start, pp.n_pairs, p.nloc, N);
         for (int ks = ks0; ks < ks1 && ok; ++ks, ++it) {
           const uint32_t slot = it % NST, par = (it / NST) & 1u;
-          if (!mbar_wait(&ctl.raw_full[slot], par, abortw)) { ok = false; break; }
+          if (!MSK_WAIT(&ctl.raw_full[slot], par, abortw)) { ok = false; break; }
           if (it == 0 && tid == 256) MSK_TR(TR_FIRST_RAW);
           if (tid == 256) MSK_TRD(0, tri, 1);
           const uint32_t tile = smem_u32(ring + slot * C::STAGE_BYTES + g * TILE_BYTES);
@@ -54,7 +80,7 @@
               if (c == 0) {
                 // hand over the previous slot (its stores had the decode above to land), claim this one
                 if (pending) retire();
-                if (!mbar_wait(&ctl.a_empty[g][as], apar ^ 1u, abortw)) { ok = false; break; }
+                if (!MSK_WAIT(&ctl.a_empty[g][as], apar ^ 1u, abortw)) { ok = false; break; }
                 tc_fence_after();
               }
               tmem_st16(a_tmem + as * C::SLOT_COLS + c * 16, o);
@@ -70,26 +96,19 @@
           if (!ok) break;
           __syncwarp();
           if (lane == 0) mbar_arrive(&ctl.raw_empty[slot]);
+          if (NDBUF == 1 && owe_drain) {
+            if (pending) retire();   // the first stage of this unit is ready for the MMA warps
+            if (!drain()) { ok = false; break; }
+          }
         }
         if (!ok) break;
         if (pending) retire();  // the accumulators need every slot of the piece
         if (NDBUF == 1) {
-          // single accumulator buffer: the main loop cannot go on until it is drained, so all sixteen
-          // dequant warps drain it together. The four warps of a lane quarter split the columns.
-          if (!mbar_wait(&ctl.d_full[0], unit_i & 1u, abortw)) { ok = false; break; }
-          tc_fence_after();
-          if (tid == 256) { if (unit_i == 0) MSK_TR(TR_FIRST_DFULL); MSK_TR(TR_LAST_DFULL); }
-          if (phase == 0) {
-            const int part = kh * 2 + g;  // 0..3: a quarter of the token columns, gate and up of this lane
-            epilogue_columns<N>(p, pp, phase, ui, tmem + lane_base, row, part * (N / 4), (part + 1) * (N / 4), 0);
-          } else {
-            epilogue_columns<N>(p, pp, phase, ui, tmem + lane_base, row, kh * (N / 2), (kh + 1) * (N / 2), g);
-          }
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&ctl.d_empty[0]);
-          if (tid == 256 && unit_i == 0) MSK_TR(TR_FIRST_EPI_DONE);
+          owe_drain = true;
+          owed_ui = ui;
+          owed_unit_i = unit_i;
         }
       }
+      if (ok && NDBUF == 1 && owe_drain && !drain()) ok = false;   // the last unit of the phase
       if (!ok) break;
     }

@@ -26,7 +26,7 @@
       for (; ok && pieces.next(base, ks0, ks1); ++unit_i) {
         const UnitInfo ui = decode_unit(base, tile_start, pp.n_pairs, p.nloc, N);
         const uint32_t db = unit_i % NDBUF, duse = unit_i / NDBUF;
-        if (!mbar_wait(&ctl.d_full[db], duse & 1u, abortw)) { ok = false; break; }
+        if (!MSK_WAIT(&ctl.d_full[db], duse & 1u, abortw)) { ok = false; break; }
         tc_fence_after();
         if (tid == 128) { if (unit_i == 0) MSK_TR(TR_FIRST_DFULL); MSK_TR(TR_LAST_DFULL); MSK_TRD(3, tri, 1); }
         const uint32_t d_tmem = tmem + lane_base + db * (2 * N);

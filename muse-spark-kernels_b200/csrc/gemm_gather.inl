@@ -83,7 +83,7 @@
         }
         for (int ks = ks0; ks < ks1; ++ks, ++it) {
           const uint32_t slot = it % NST, par = (it / NST) & 1u;
-          if (!mbar_wait(&ctl.b_empty[slot], par ^ 1u, abortw)) { ok = false; break; }
+          if (!MSK_WAIT(&ctl.b_empty[slot], par ^ 1u, abortw)) { ok = false; break; }
           uint8_t* dstB = ring + slot * C::STAGE_BYTES + 2 * TILE_BYTES;
 #pragma unroll
           for (int ng = 0; ng < NG; ++ng) {

@@ -16,7 +16,7 @@
       for (; ok && pieces.next(base, ks0, ks1); ++unit_i) {
         const UnitInfo ui = decode_unit(base, tile_start, pp.n_pairs, p.nloc, N);
         const uint32_t db = unit_i % NDBUF, duse = unit_i / NDBUF;
-        if (!mbar_wait(&ctl.d_empty[db], (duse & 1u) ^ 1u, abortw)) { ok = false; break; }
+        if (!MSK_WAIT(&ctl.d_empty[db], (duse & 1u) ^ 1u, abortw)) { ok = false; break; }
         tc_fence_after();
         if (mg == 0 && lane == 0) MSK_TRD(1, tri, 3);
         const uint32_t d_tmem = tmem + db * (2 * N) + mg * N;
@@ -26,12 +26,12 @@
         const uint32_t a_base = tmem + C::A_BASE + mg * C::A_GROUP_COLS;
         for (int ks = ks0; ks < ks1 && ok; ++ks, ++it) {
           const uint32_t slot = it % NST, par = (it / NST) & 1u;
-          if (!mbar_wait(&ctl.b_full[slot], par, abortw)) { ok = false; break; }
+          if (!MSK_WAIT(&ctl.b_full[slot], par, abortw)) { ok = false; break; }
           if (mg == 0 && lane == 0) MSK_TRD(1, tri, 1);
           const uint32_t b_addr = smem_u32(ring + slot * C::STAGE_BYTES + 2 * TILE_BYTES);
 #pragma unroll
           for (int sl = 0; sl < 2; ++sl, ++sc) {
-            if (!mbar_wait(&ctl.a_full[mg][as], apar, abortw)) { ok = false; break; }
+            if (!MSK_WAIT(&ctl.a_full[mg][as], apar, abortw)) { ok = false; break; }
             tc_fence_after();
             if (elect_one()) {  // warp-uniform control flow keeps addresses and descriptors in uniform registers
               if (sc == 0 && mg == 0) MSK_TR(TR_FIRST_MMA);

@@ -19,7 +19,7 @@
           const uint8_t* g1 = g0 + static_cast<size_t>(nst_total) * TILE_BYTES;
           for (int ks = ks0; ks < ks1; ++ks, ++it) {
             const uint32_t slot = it % NST, par = (it / NST) & 1u;
-            if (!mbar_wait(&ctl.raw_empty[slot], par ^ 1u, abortw)) { ok = false; break; }
+            if (!MSK_WAIT(&ctl.raw_empty[slot], par ^ 1u, abortw)) { ok = false; break; }
             uint8_t* dst = ring + slot * C::STAGE_BYTES;
             mbar_arrive_expect_tx(&ctl.raw_full[slot], 2 * TILE_BYTES);
             bulk_g2s(dst, g0 + static_cast<size_t>(ks) * TILE_BYTES, TILE_BYTES, &ctl.raw_full[slot], pol);
@@ -28,7 +28,7 @@
             if (TMA_B) {
               // activation tile of the stage: four boxes of 64 K x N rows, rows row0.. of the sorted matrix
               if (MODE == 1 && it == 0) pdl_wait();  // inter comes from the gate/up GEMM
-              if (!mbar_wait(&ctl.b_empty[slot], par ^ 1u, abortw)) { ok = false; break; }
+              if (!MSK_WAIT(&ctl.b_empty[slot], par ^ 1u, abortw)) { ok = false; break; }
               uint8_t* dstB = dst + 2 * TILE_BYTES;
               mbar_arrive_expect_tx(&ctl.b_full[slot], C::B_STAGE_BYTES);
 #pragma unroll

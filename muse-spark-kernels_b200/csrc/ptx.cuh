@@ -85,7 +85,40 @@ __device__ __forceinline__ bool mbar_try_wait_parked(uint64_t* bar, uint32_t par
 // role sets non-zero when it gave up; a set word makes every later wait return
 // false at once so that all roles unwind together. Returns true when the phase
 // completed.
+// The polling part is one shared function, not inlined at the several dozen call sites: a step of one
+// token starts with a cold instruction cache, and every copy of this loop that a role runs into for the
+// first time would be another line to fetch from memory.
+__device__ __noinline__ bool mbar_wait_poll(uint32_t bar_addr, uint32_t parity, volatile int* abort_word) {
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t polls = 0;
+  while (true) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar_addr), "r"(parity), "r"(4000u)
+        : "memory");
+    if (ok) return true;
+    if ((++polls & 15u) == 0u) {
+      if (*abort_word != 0) return false;
+      if (globaltimer_ns() - t0 > MSK_WAIT_LIMIT_NS) {
+        *abort_word = 1;
+        return false;
+      }
+    }
+  }
+}
+
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_word) {
+  if (mbar_try_wait(bar, parity)) return true;
+  return mbar_wait_poll(smem_u32(bar), parity, abort_word);
+}
+
+// The same wait with the polling loop inlined: for the wide token tiles, whose warps wait at every
+// stage of a long, warm main loop (measured: the call cost the 8192-token step about 10 %).
+__device__ __forceinline__ bool mbar_wait_inline(uint64_t* bar, uint32_t parity, volatile int* abort_word) {
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = globaltimer_ns();
   uint32_t polls = 0;
