@@ -56,9 +56,16 @@
         const UnitInfo ui = decode_unit(base, tile_start, pp.n_pairs, p.nloc, N);
         for (int ks = ks0; ks < ks1 && ok; ++ks, ++it) {
           const uint32_t slot = it % NST, par = (it / NST) & 1u;
+#ifdef MSK_TRACE_DETAIL
+          // first and last dequant warp (roles 0 and 5): 1 the stage had landed before the warp asked for it, 3 it had not
+          if (lane == 0 && (didx == 0 || didx == 15)) {
+            if (mbar_test(&ctl.raw_full[slot], par)) MSK_TRD(didx ? 5 : 0, tri, 1);
+            else MSK_TRD(didx ? 5 : 0, tri, 3);
+          }
+#endif
           if (!MSK_WAIT(&ctl.raw_full[slot], par, abortw)) { ok = false; break; }
           if (it == 0 && tid == 256) MSK_TR(TR_FIRST_RAW);
-          if (tid == 256) MSK_TRD(0, tri, 1);
+          if (lane == 0 && (didx == 0 || didx == 15)) MSK_TRD(didx ? 5 : 0, tri, 5);
           const uint32_t tile = smem_u32(ring + slot * C::STAGE_BYTES + g * TILE_BYTES);
           const uint32_t tile_row = tile + row * 16;
           uint32_t sfa[4];
@@ -80,7 +87,12 @@
               if (c == 0) {
                 // hand over the previous slot (its stores had the decode above to land), claim this one
                 if (pending) retire();
+#ifdef MSK_TRACE_DETAIL
+                if (lane == 0 && (didx == 0 || didx == 15) && !mbar_test(&ctl.a_empty[g][as], apar ^ 1u))
+                  MSK_TRD(didx ? 5 : 0, tri, 9);   // the A slot was not free yet
+#endif
                 if (!MSK_WAIT(&ctl.a_empty[g][as], apar ^ 1u, abortw)) { ok = false; break; }
+                if (lane == 0 && (didx == 0 || didx == 15)) MSK_TRD(didx ? 5 : 0, tri, 6);
                 tc_fence_after();
               }
               tmem_st16(a_tmem + as * C::SLOT_COLS + c * 16, o);
@@ -96,6 +108,7 @@
           if (!ok) break;
           __syncwarp();
           if (lane == 0) mbar_arrive(&ctl.raw_empty[slot]);
+          if (lane == 0 && (didx == 0 || didx == 15)) MSK_TRD(didx ? 5 : 0, tri, 7);
           if (NDBUF == 1 && owe_drain) {
             if (pending) retire();   // the first stage of this unit is ready for the MMA warps
             if (!drain()) { ok = false; break; }

@@ -83,6 +83,9 @@
         }
         for (int ks = ks0; ks < ks1; ++ks, ++it) {
           const uint32_t slot = it % NST, par = (it / NST) & 1u;
+#ifdef MSK_TRACE_DETAIL
+          if (lane == 0 && !mbar_test(&ctl.b_empty[slot], par ^ 1u)) MSK_TRD(4, tri, 6);   // B slot still in use
+#endif
           if (!MSK_WAIT(&ctl.b_empty[slot], par ^ 1u, abortw)) { ok = false; break; }
           uint8_t* dstB = ring + slot * C::STAGE_BYTES + 2 * TILE_BYTES;
 #pragma unroll

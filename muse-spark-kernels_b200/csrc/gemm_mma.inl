@@ -26,12 +26,19 @@
         const uint32_t a_base = tmem + C::A_BASE + mg * C::A_GROUP_COLS;
         for (int ks = ks0; ks < ks1 && ok; ++ks, ++it) {
           const uint32_t slot = it % NST, par = (it / NST) & 1u;
+#ifdef MSK_TRACE_DETAIL
+          if (mg == 0 && lane == 0 && !mbar_test(&ctl.b_full[slot], par)) MSK_TRD(1, tri, 4);   // B tile not there yet
+#endif
           if (!MSK_WAIT(&ctl.b_full[slot], par, abortw)) { ok = false; break; }
           if (mg == 0 && lane == 0) MSK_TRD(1, tri, 1);
           const uint32_t b_addr = smem_u32(ring + slot * C::STAGE_BYTES + 2 * TILE_BYTES);
 #pragma unroll
           for (int sl = 0; sl < 2; ++sl, ++sc) {
+#ifdef MSK_TRACE_DETAIL
+            if (mg == 0 && lane == 0 && !mbar_test(&ctl.a_full[mg][as], apar)) MSK_TRD(1, tri, 5);   // A slot not there yet
+#endif
             if (!MSK_WAIT(&ctl.a_full[mg][as], apar, abortw)) { ok = false; break; }
+            if (mg == 0 && lane == 0) MSK_TRD(1, tri, 6);
             tc_fence_after();
             if (elect_one()) {  // warp-uniform control flow keeps addresses and descriptors in uniform registers
               if (sc == 0 && mg == 0) MSK_TR(TR_FIRST_MMA);

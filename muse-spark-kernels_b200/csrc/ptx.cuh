@@ -153,6 +153,20 @@ __device__ __forceinline__ bool mbar_wait_short(uint64_t* bar, uint32_t parity, 
   return mbar_wait(bar, parity, abort_word);
 }
 
+// Non-blocking probe of a phase (mbarrier.test_wait): true when the phase has completed. Unlike
+// try_wait it never suspends the thread, so it tells whether a wait that follows will have to wait.
+__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
 // ------------------------------------------------------- async-proxy fences
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");

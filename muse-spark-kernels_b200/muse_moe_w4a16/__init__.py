@@ -21,7 +21,7 @@ from . import _lib
 from ._lib import ROUTE_SIGMOID_BIAS, ROUTE_SOFTMAX_TOPK, MskMoeCfg
 
 __all__ = ["prepare", "kernel_fn", "export_weights", "read_status", "reinit_workspace", "state_dict", "load_state_dict",
-           "workspace_views", "attrs"]
+           "workspace_views", "attrs", "GraphedStep", "HostMappedStep"]
 
 _MODES = {"softmax_topk": ROUTE_SOFTMAX_TOPK, "sigmoid_bias": ROUTE_SIGMOID_BIAS}
 
@@ -301,6 +301,92 @@ class GraphedStep:
                 self.static[k].copy_(data[k], non_blocking=True)
         self.graph.replay()
         return self.out
+
+
+class HostMappedStep:
+    """kernel_fn for a fixed, small token count whose inputs and output stay in pinned host memory:
+    the captured kernels read hidden_states and router_logits straight from a pinned block over PCIe
+    (pinned memory is device-addressable under unified addressing) and write the BF16 output rows
+    straight into a pinned host tensor, so a step that starts and ends on the host has no copy
+    launches around the kernel at all. At a few tokens the copies are a quarter of the step (launches
+    of several microseconds each around a 45 us kernel); the reads they replace are 8 KB per token
+    once, plus the logits row every CTA needs, and cost one PCIe round trip.
+
+    step(data) copies data's host tensors into a pinned block, replays the graph captured over that
+    block on the current stream and returns the pinned output tensor of that block; it holds this
+    step's rows once the stream (or step.done) has been synchronised. STAGES blocks (each with its own
+    graph and output) are used in turn, so the host may run ahead of the device by that many steps; a
+    block is reused only after the replay that read it has finished. Needs hidden_states and
+    router_logits (or topk_ids + topk_weights) in `like`."""
+
+    STAGES = 4
+    _DTYPES = {"hidden_states": torch.bfloat16, "router_logits": torch.float32, "topk_ids": torch.int32,
+               "topk_weights": torch.float32}
+
+    def __init__(self, state, like):
+        self.state = state
+        cfg = state["cfg"]
+        dev = state["packed13"].device
+        if state.get("pre_norm_w") is not None:
+            raise RuntimeError("HostMappedStep: states with a pre-expert norm are not supported")
+        self.routed = like.get("topk_ids") is not None
+        self.keys = ["hidden_states"] + (["topk_ids", "topk_weights"] if self.routed else ["router_logits"])
+        if any(like.get(k) is None for k in self.keys):
+            raise RuntimeError("HostMappedStep: need hidden_states and router_logits (or topk_ids + topk_weights)")
+        self.T = T = like["hidden_states"].shape[0]
+        spans, total = {}, 0
+        for k in self.keys:
+            nbytes = like[k].numel() * torch.empty((), dtype=self._DTYPES[k]).element_size()
+            spans[k] = (total, nbytes)
+            total += (nbytes + 255) // 256 * 256
+        self.blocks = [torch.empty(total, dtype=torch.uint8).pin_memory() for _ in range(self.STAGES)]
+        self.inputs = [{k: b[o:o + n].view(self._DTYPES[k]).view(tuple(like[k].shape)) for k, (o, n) in spans.items()}
+                       for b in self.blocks]
+        self.outs = [torch.empty((T, cfg.hidden), dtype=torch.bfloat16).pin_memory() for _ in range(self.STAGES)]
+        self.ids = torch.empty((T, cfg.top_k), dtype=torch.int32, device=dev)
+        self.tw = torch.empty((T, cfg.top_k), dtype=torch.float32, device=dev)
+        self.events = [None] * self.STAGES
+        self.done = None
+        self.turn = 0
+        for inp in self.inputs:
+            for k in self.keys:
+                inp[k].copy_(like[k])
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):                      # warm-up outside the capture
+            self._launch(0)
+        torch.cuda.current_stream(dev).wait_stream(side)
+        self.graphs = []
+        for i in range(self.STAGES):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self._launch(i)
+            self.graphs.append(g)
+
+    def _launch(self, i):
+        state, inp = self.state, self.inputs[i]
+        cfg, lib = state["cfg"], state["lib"].lib
+        args = (ctypes.byref(cfg), _lib.ptr(state["packed13"]), _lib.ptr(state["packed2"]), _lib.ptr(state["gs13"]),
+                _lib.ptr(state["gs2"]), _lib.ptr(state["post_norm_w"]), _lib.ptr(inp["hidden_states"]))
+        tail = (_lib.ptr(self.outs[i]), _lib.ptr(state["workspace"]), state["workspace_bytes"], self.T, _stream())
+        if self.routed:
+            _lib.check(lib.msk_moe_forward(*args, _lib.ptr(inp["topk_ids"]), _lib.ptr(inp["topk_weights"]), *tail),
+                       "msk_moe_forward")
+        else:
+            _lib.check(lib.msk_moe_forward_logits(*args, _lib.ptr(inp["router_logits"]), _lib.ptr(state["route_bias"]),
+                                                  _lib.ptr(self.ids), _lib.ptr(self.tw), *tail), "msk_moe_forward_logits")
+
+    def __call__(self, data):
+        i = self.turn
+        self.turn = (i + 1) % self.STAGES
+        if self.events[i] is not None:
+            self.events[i].synchronize()   # the replay that last used this block has finished
+        for k in self.keys:
+            self.inputs[i][k].copy_(data[k])
+        self.graphs[i].replay()
+        self.done = self.events[i] = torch.cuda.Event()
+        self.done.record()
+        return self.outs[i]
 
 
 def kernel_fn_timed(data, state):

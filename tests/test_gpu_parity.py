@@ -374,6 +374,36 @@ def test_graphed_step_with_pinned_host_inputs(cuda_dev):
     assert m.read_status(st) == 0
 
 
+@pytest.mark.parametrize("T,routed", [(1, False), (5, False), (8, True), (40, False)])
+def test_host_mapped_step_reads_and_writes_pinned_host_memory(cuda_dev, T, routed):
+    """HostMappedStep (kernels read the inputs from, and write the output to, pinned host memory; no copy
+    launches) returns what kernel_fn returns on device tensors, bit for bit, call after call and across
+    its ring of blocks: one-launch path (1, 5, 8 tokens), chain (40 tokens), given ids and logits."""
+    m, inputs, _lib, orc = _mods()
+    H, I, E, k = 1024, 512, 16, 4
+    w = inputs.make_weights(H, I, E, 52, cuda_dev, post_norm=True)
+    st = m.prepare(w, n_experts=E, top_k=k, max_tokens=T)
+    g = torch.Generator(device=cuda_dev).manual_seed(10 + T)
+    datas = []
+    for _ in range(6):
+        d = {"hidden_states": torch.randn((T, H), generator=g, device=cuda_dev).to(torch.bfloat16)}
+        logits = torch.randn((T, E), generator=g, device=cuda_dev)
+        if routed:
+            tw, ids = torch.softmax(logits, dim=-1).topk(k, dim=-1)
+            d["topk_ids"], d["topk_weights"] = ids.to(torch.int32), tw.contiguous()
+        else:
+            d["router_logits"] = logits
+        datas.append(d)
+    step = m.HostMappedStep(st, {key: v.cpu() for key, v in datas[0].items()})
+    for d in datas:
+        want = m.kernel_fn(d, st)
+        got = step({key: v.cpu() for key, v in d.items()})
+        assert not got.is_cuda and got.is_pinned()
+        step.done.synchronize()
+        assert torch.equal(got, want.cpu())
+    assert m.read_status(st) == 0
+
+
 def test_okc_ext_runs_the_decode_layer_call_site(cuda_dev):
     """The decode layer's call (muse_decode_layer/py/06_kernel_fn.py:140-149): local ids with -1 for
     another GPU's expert, lo = 0, an output slice filled in place, in chunks."""
