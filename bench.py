@@ -708,18 +708,25 @@ def main():
     ap.add_argument("--ep-chunks", default="", help="expert-parallel runs: number of equal chunks of source ranks, or their sizes "
                                                     "as a comma list (own rank first), e.g. 1,3,3,1; empty = default")
     ap.add_argument("--ep-timeline", action="store_true", help="expert-parallel runs: add per-chunk event times of a step to the line")
-    ap.add_argument("--token-tile", type=int, default=0, help="force a kernel: 16/32/64/128, 8 = the mma.sync single-launch kernel")
-    ap.add_argument("--decode-path", type=int, default=0, help="few tokens: 0 one launch, 1 chain of launches, 2 three launches")
+    ap.add_argument("--token-tile", type=int, default=0, help="force the token tile of the GEMM kernels: 16/32/64/128")
+    ap.add_argument("--decode-path", type=int, default=0, help="few tokens: 0 auto, 1 chain of launches, 2 three launches, 3 one launch")
     ap.add_argument("--weight-sets", type=int, default=6,
                     help="weight sets of the rotating-weights timing of the few-token points (0 or 1: leave it out)")
     ap.add_argument("--flush", default="read", choices=["read", "write"], help="how L2 is flushed before a timed step")
     ap.add_argument("--profile-only", action="store_true", help="run warmup+steps eager steps and exit (for ncu)")
     args = ap.parse_args()
     spec = workload_spec(args.workload, args.gpus)
+    # Standard output carries the one JSON line and nothing else: libraries that write to file descriptor 1
+    # themselves (NCCL prints its version there when the first communicator comes up) go to standard error.
+    sys.stdout.flush()
+    line_fd = os.dup(1)
+    os.dup2(2, 1)
+    sys.stdout = os.fdopen(line_fd, "w")
     if args.impl == "reference":
         run_reference(args, spec)
     else:
         run_gpu(args, spec)
+    sys.stdout.flush()
 
 
 if __name__ == "__main__":

@@ -48,15 +48,17 @@ def chunk_sizes(world, chunks=None):
     """How the `world` source ranks (slot 0 = this rank's own tokens, slot j = rank + j) are grouped into
     chunks that are processed one after the other. chunks: None (default), a number of equal chunks,
     or the sizes themselves. The default starts with the rank's own tokens alone (they need no transfer,
-    so nothing is waited for at the head of the step) and ends with a single source rank (so that only
-    one rank's partial rows are still on their way back when the expert kernels have finished)."""
+    so nothing is waited for at the head of the step), ends with a single source rank (so that only
+    one rank's partial rows are still on their way back when the expert kernels have finished) and
+    takes the ranks in between two at a time (measured on 8 B200s, 4096 tokens per GPU:
+    [1, 2, 2, 2, 1] 3.87 ms, [1, 3, 3, 1] 3.99 ms, [2, 2, 2, 2] 4.12 ms a step)."""
     if chunks is None:
         if world <= 2:
             return [world]
         if world == 3:
             return [1, 2]
         mid = world - 2
-        return [1] + ([mid] if mid <= 2 else [mid - mid // 2, mid // 2]) + [1]
+        return [1] + [2] * (mid // 2) + ([1] if mid % 2 else []) + [1]
     if isinstance(chunks, int):
         if chunks < 1 or world % chunks != 0:
             raise ValueError("the number of chunks must divide the number of ranks")
@@ -217,6 +219,20 @@ class SymmExchange:
         ev_in.record(s0)
         for j in range(1, n):
             self._write((r + j) % n, 2 * r + b, e, s0)
+        def run_chunk(c):
+            mark(f"chunk{c}_rows_in")
+            sl, m = slice(bounds[c], bounds[c + 1]), self.sizes[c]
+            expert_fn(gx[sl].view(m * T, H), gids[sl].view(m * T, k), gtw[sl].view(m * T, k), part[sl].view(m * T, H))
+            mark(f"chunk{c}_experts_done")
+            for j in range(max(bounds[c], 1), bounds[c + 1]):
+                self._write((r + j) % n, 2 * n + 2 * r + b, e, s0)
+
+        # A first chunk that holds this rank's own rows only needs no transfer: its launches are issued
+        # before the host spends its time on the copy stream's calls below (some forty of them; issued
+        # first they kept the main stream idle for a quarter of a millisecond at the head of the step)
+        own_first = self.sizes[0] == 1
+        if own_first:
+            run_chunk(0)
         # copy stream: pull the other ranks' rows, nearest rank first
         s1.wait_event(ev_in)
         ready = {}
@@ -231,16 +247,11 @@ class SymmExchange:
                     c = bounds.index(j + 1) - 1
                     ready[c] = torch.cuda.Event()
                     ready[c].record(s1)
-        # main stream: the local expert step chunk by chunk, own rows first
-        for c in range(self.chunks):
+        # main stream: the local expert step chunk by chunk
+        for c in range(1 if own_first else 0, self.chunks):
             if c in ready:
                 s0.wait_event(ready[c])
-            mark(f"chunk{c}_rows_in")
-            sl, m = slice(bounds[c], bounds[c + 1]), self.sizes[c]
-            expert_fn(gx[sl].view(m * T, H), gids[sl].view(m * T, k), gtw[sl].view(m * T, k), part[sl].view(m * T, H))
-            mark(f"chunk{c}_experts_done")
-            for j in range(max(bounds[c], 1), bounds[c + 1]):
-                self._write((r + j) % n, 2 * n + 2 * r + b, e, s0)
+            run_chunk(c)
         # copy stream: pull this rank's partial rows back, in the order the peers finish them
         with torch.cuda.stream(s1):
             for j in range(1, n):

@@ -157,3 +157,25 @@ def test_exchange_deadline_raises_when_an_event_never_completes():
         raised = "step 7" in str(exc)
     assert raised and 0.15 < time.time() - t0 < 5.0
     ep.wait_deadline(DoneAfter(3), 5.0, "step 8")    # completes: returns
+
+
+def test_default_chunks_start_with_the_own_rank_and_end_with_one_rank():
+    """chunk_sizes: every layout covers all source ranks; from four ranks on the default starts with the
+    rank's own rows alone, ends with a single rank and takes at most two ranks at a time in between;
+    explicit layouts are checked."""
+    import pytest
+
+    from muse_moe_w4a16 import ep
+
+    for world in range(1, 17):
+        sizes = ep.chunk_sizes(world)
+        assert sum(sizes) == world and min(sizes) >= 1
+        if world >= 4:
+            assert sizes[0] == 1 and sizes[-1] == 1 and max(sizes) <= 2
+    assert ep.chunk_sizes(8) == [1, 2, 2, 2, 1]
+    assert ep.chunk_sizes(8, 4) == [2, 2, 2, 2]
+    assert ep.chunk_sizes(8, [1, 3, 3, 1]) == [1, 3, 3, 1]
+    with pytest.raises(ValueError):
+        ep.chunk_sizes(8, 3)
+    with pytest.raises(ValueError):
+        ep.chunk_sizes(8, [4, 3])
