@@ -233,7 +233,8 @@ int msk_moe_share_pieces(int n_base, int n_stages, int shares, int flat, int cta
 /* Views into the workspace after msk_moe_forward (device pointers, for parity tests):
  * which: 0 cnt, 1 off, 2 perm, 3 inv, 4 inter (fp16 [R, I], holding bf16-rounded values), 5 y (fp32 [R, H]; bf16 [R, H] when the plan's
  * token tile is 128),
- * 7 unit tickets, 8 control words of the few-token paths, 9 per-CTA counts of the multi-CTA sort (all three
+ * 7 unit tickets, 8 control words of the few-token paths, 9 per-CTA counts of the multi-CTA sort, 10 the
+ * per-tile counters that hand `inter` from the gate/up launch to the down launch tile by tile (all four
  * zeroed by msk_moe_workspace_init, like everything below view 4),
  * 6 trace (uint64 [2 launches][256 CTAs x 16 stamps, then 6 x 128 event words], ns; written when cfg->trace != 0). */
 int msk_moe_workspace_view(const MskMoeCfg* cfg, void* workspace, int which, void** host_ptr);

@@ -127,6 +127,8 @@ struct GemmParams {
   int top_k;
   int flat;                  // 1: equal shares of the flat (base unit, K stage) list; 0: whole units
   int evict_first;
+  int handover;              // two launches: gate/up units count per token tile (tile_done), down units wait for their
+                             // tile's count instead of for the whole gate/up grid (see gemm_gather.inl)
   int y_bf16;                // phase 1, token tile 128: y rows as BF16 instead of FP32
   // Phase 0 with route != 0 (at most 256 entries): every CTA derives the sort tables in its prologue.
   // route 1: top-k of `logits` first (CTA 0 writes ids_out / tw_out); route 2: ids_in given.
@@ -629,6 +631,13 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) moe_gemm_kernel(const __grid_
   const uint32_t tmem = ctl.tmem_base;
   if (tid == 0) MSK_TR(TR_SETUP);
   const int iter_mode = (N < 128 && p.flat) ? 1 : 0;
+  // Down launch behind a gate/up launch with the per-tile hand-over: its CTAs start as the gate/up CTAs
+  // leave, in block order, so the last blocks start on the SMs whose gate/up CTA held one unit more than
+  // the others. They are dealt fewer down units, the way the one-launch kernel deals its second phase
+  // (phase1_skew), with the block order reversed so that "heavy" means "started last". Only the balance
+  // depends on that order, not the result.
+  const bool chained_skew = MODE == 1 && p.handover != 0;
+  const int deal_index = chained_skew ? static_cast<int>(n_ctas) - 1 - static_cast<int>(blockIdx.x) : static_cast<int>(blockIdx.x);
   volatile int* abortw = &ctl.abort_word;
 #define MSK_WAIT(bar, par, ab) (N >= 64 ? mbar_wait_inline((bar), (par), (ab)) : mbar_wait((bar), (par), (ab)))
 #define MSK_PHASES for (int phase = PH_FIRST; phase <= PH_LAST; ++phase)
@@ -637,8 +646,8 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) moe_gemm_kernel(const __grid_
   const int nst_total = pp.K / KS;                                                                                \
   const int n_base = ctl.n_tiles * pp.n_pairs;                                                                    \
   int heavy_ = 0, skip_ = 0;                                                                                     \
-  if (FUSED && phase == 1) phase1_skew(ctl.n_tiles * p.ph[0].n_pairs, p.ph[0].K / KS, nst_total, static_cast<int>(n_ctas), heavy_, skip_); \
-  PieceIter pieces = make_piece_iter(iter_mode, n_base, nst_total, static_cast<int>(blockIdx.x), static_cast<int>(n_ctas), heavy_, skip_); \
+  if ((FUSED || chained_skew) && phase == 1) phase1_skew(ctl.n_tiles * p.ph[0].n_pairs, p.ph[0].K / KS, nst_total, static_cast<int>(n_ctas), heavy_, skip_); \
+  PieceIter pieces = make_piece_iter(iter_mode, n_base, nst_total, deal_index, static_cast<int>(n_ctas), heavy_, skip_); \
   const int tail_base = pieces.tail_base;                                                                         \
   (void)tail_base;                                                                                                \
   int base, ks0, ks1;                                                                                             \
@@ -663,6 +672,11 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) moe_gemm_kernel(const __grid_
   __syncwarp();
   tc_fence_before();
   __syncthreads();
+  // With the per-tile hand-over nothing in this kernel has waited for the gate/up grid as a whole (all of
+  // its units are done, or the tiles would not have been released; its CTAs may still be leaving). Waiting
+  // here, where it costs nothing, keeps "this grid has completed" implying "the one before has" for
+  // whatever follows in the stream.
+  if (MODE == 1 && p.handover) pdl_wait();
   if (fold && p.fold == 1 && ctl.abort_word == 0) {
     // the tokens whose last base unit this CTA retired (the ring is free by now: scratch for the sums)
     FoldScratch& fs = *reinterpret_cast<FoldScratch*>(ring);

@@ -10,7 +10,9 @@
     uint32_t unit_i = 0, epi_par = 0;
     int tri = 0;
     (void)tri;
-    if (MODE == 1) pdl_wait();  // y rows and tickets must not be touched before the previous grid is done
+    // y rows and tickets must not be touched before the previous grid is done; with the per-tile hand-over a
+    // unit gets here only after its tile's gate/up units have finished, which is later than that grid's own wait
+    if (MODE == 1 && !p.handover) pdl_wait();
     bool ok = true;
     // bounded barrier over the 128 epilogue threads (a plain bar.sync could not time out)
     auto epi_sync = [&]() -> bool {
@@ -145,9 +147,10 @@
           if (lane == 0) mbar_arrive(&ctl.d_empty[db]);
         }
         if (tid == 128) MSK_TRD(3, tri, 5);
-        if (FUSED && phase == 0) {
-          // one launch: this unit's columns of inter are complete; count it for its token tile, whose down
-          // units wait for the count to reach the number of gate/up pairs
+        if ((FUSED || p.handover) && phase == 0) {
+          // this unit's columns of inter are complete; count it for its token tile, whose down units (the
+          // second phase of this launch, or the down GEMM launched behind it) wait for the count to reach
+          // the number of gate/up pairs
           __threadfence();
           if (!epi_sync()) { ok = false; break; }
           if (finish && tid == 128) { atomicAdd(p.tile_done + ui.tile, 1u); MSK_TRD(3, tri, 7); }

@@ -37,7 +37,8 @@
       // that copy have been worked out)
       bool must_wait = FUSED && phase == 0;
       int last_tile = -1;
-      if (!FUSED && (MODE == 1 || routed_here)) pdl_wait();
+      const bool per_tile = FUSED || (MODE == 1 && p.handover != 0);   // inter is handed over tile by tile
+      if (!FUSED && ((MODE == 1 && !per_tile) || routed_here)) pdl_wait();
       const size_t act_ld = static_cast<size_t>(pp.K);
       while (ok && pieces.next(base, ks0, ks1)) {
         const UnitInfo ui = decode_unit(base, tile_start, pp.n_pairs, p.nloc, N);
@@ -55,7 +56,7 @@
           }
         }
         bool first_piece = false;
-        if (FUSED && (must_wait || (phase == 1 && ui.tile != last_tile))) {
+        if (per_tile && (must_wait || (phase == 1 && ui.tile != last_tile))) {
           // phase 0: every CTA's slice of the F16 token rows; phase 1: the gate/up units of this token
           // tile. Everything issued so far is handed over first, so that the MMA warps never starve on
           // copies that have long landed.
@@ -72,7 +73,7 @@
           must_wait = false;
           last_tile = ui.tile;
         }
-        if (FUSED && phase == 1 && lane == 0) {
+        if (per_tile && phase == 1 && lane == 0) {
           // every down unit of the tile reports that it has seen the count complete; the last one puts both
           // counters back to zero for the next launch
           const unsigned seen = atomicAdd(p.tile_seen + ui.tile, 1u);

@@ -510,6 +510,14 @@ static int sm_count() {
 // shares of the weight stream (and with them the order in which a cut unit's pieces are summed)
 // depend on the configuration, not on the device the library happens to run on.
 constexpr int DEFAULT_CTAS = 148;
+// MSK_NO_HANDOVER=1 switches the per-tile hand-over between the two GEMM launches off (measurements).
+static bool handover_env_off() {
+  static const bool v = [] {
+    const char* e = std::getenv("MSK_NO_HANDOVER");
+    return e != nullptr && e[0] == '1';
+  }();
+  return v;
+}
 constexpr int MAX_CTAS = 512;
 constexpr int FLAT_MAX_ROWS = SMALL_SORT_MAX_ENTRIES;  // up to here the weight stream may be cut into equal shares
 constexpr int ONE_LAUNCH_MAX_TOKENS = 8;               // up to here the step is one launch by default
@@ -564,7 +572,7 @@ static Plan make_plan(const MskMoeCfg* c, int T) {
 
 // Workspace carving. Everything is sized for max_tokens with the worst plan.
 struct Carve {
-  size_t status, trace, cnt, off, perm, inv, tickets, few_ctl, sort_blk, inter, y, partial, xs, total;
+  size_t status, trace, cnt, off, perm, inv, tickets, few_ctl, sort_blk, tile_ctr, inter, y, partial, xs, total;
 };
 constexpr size_t TRACE_CTAS = 256;
 constexpr size_t TRACE_WORDS = TRACE_CTAS * 16 + 3 * 256;
@@ -600,6 +608,9 @@ static Carve carve(const MskMoeCfg* c, int T) {
   k.few_ctl = o; o += 8192;    // few-token paths of the GEMM kernel: tickets [32 tokens][up to 32 pairs] at +0, grid counters [2] at
                                // +4096, per-tile counters [2][up to 384 tiles] at +4352
   k.sort_blk = o; o += static_cast<size_t>(SORT_MULTI_BLOCKS) * MAX_LOCAL_EXPERTS * 4;  // per-CTA counts of the multi-CTA sort
+  // tile hand-over between the gate/up and the down launch: per token tile the finished gate/up units and
+  // the down units that have seen them all (two counters per tile, zero between steps)
+  k.tile_ctr = o; o += round_up(2 * max_tiles(c, T) * 4, 256);
   // everything above is control state: msk_moe_workspace_init zeroes [0, inter)
   k.inter = o; o += round_up(R * c->inter * 2, 256);
   k.y = o; o += round_up(R * c->hidden * 4, 256);
@@ -970,6 +981,7 @@ int msk_moe_workspace_view(const MskMoeCfg* cfg, void* workspace, int which, voi
     case 7: *host_ptr = b + k.tickets; break;
     case 8: *host_ptr = b + k.few_ctl; break;
     case 9: *host_ptr = b + k.sort_blk; break;
+    case 10: *host_ptr = b + k.tile_ctr; break;
     default: return MSK_ERR_SHAPE;
   }
   return MSK_OK;
@@ -1159,6 +1171,21 @@ static int forward_impl(const MskMoeCfg* cfg, const void* packed13, const void* 
   }
   if (ev) cudaEventRecord(ev[5], st);
   p.y_bf16 = plan.N == 128 ? 1 : 0;  // the wide tile: half the y bytes written and read back
+  // Tile hand-over: the down GEMM's CTAs start on the SMs the gate/up CTAs leave (programmatic launch) and
+  // would then wait for that whole grid, whose last CTAs run a unit longer than the others (the units do not
+  // divide evenly): a tenth of the gate/up time with every SM but a few idle. Instead each down unit waits
+  // for the gate/up units of its own token tile, and the blocks that start last are dealt fewer down units.
+  // Needs every gate/up CTA resident while down CTAs wait (grid within the SM count: a waiting CTA must not
+  // keep a producing one off the machine), whole units (a cut unit would be counted once per piece) and
+  // both launches of the step. Narrow token tiles only, where the gather warp does the waiting: measured at
+  // H4096 I1536 E128, 16 / 32 / 64 / 128 tokens take 187 / 242 / 257 / 270 us with it against 190 / 248 /
+  // 266 / 274 without. With the wide tiles, whose weight producer also fetches the activation tiles and so
+  // would stand still at every new token tile, the same hand-over was slower (256 tokens 326 against 320 us,
+  // 8192 tokens 2.62 against 2.58 ms) and is not built.
+  p.handover = (pdl != 0 && !tma_b && plan.flat == 0 && plan.grid <= sm_count() && cfg->stop_after == 0) ? 1 : 0;
+  if (handover_env_off()) p.handover = 0;
+  p.tile_done = reinterpret_cast<unsigned int*>(b + k.tile_ctr);
+  p.tile_seen = p.tile_done + max_tiles(cfg, cfg->max_tokens);
   e = launch_gemm_n<0>(plan.N, p, plan.grid, st, pdl);
   if (e != 0) return e;
   if (ev) cudaEventRecord(ev[2], st);

@@ -302,7 +302,8 @@ def test_plan_is_a_function_of_the_configuration_only():
 def test_workspace_init_covers_every_control_word():
     """msk_moe_workspace_init zeroes everything in front of `inter`: the status word, the sort tables,
     both ticket regions, the control words of the few-token paths (token tickets, grid and tile
-    counters) and the per-CTA counts of the multi-CTA sort must all lie there."""
+    counters), the per-CTA counts of the multi-CTA sort and the tile counters of the hand-over between the
+    two GEMM launches must all lie there."""
     from muse_moe_w4a16 import _lib
 
     lib = _lib.load()
@@ -318,7 +319,7 @@ def test_workspace_init_covers_every_control_word():
     pairs = max(1536 // 128, 4096 // 256)
     tiles = 256 * 8 // 16 + 128
     for which, nbytes in ((0, 128 * 4), (1, 129 * 4), (2, 2048 * 4), (3, 2048 * 4), (7, 2 * tiles * pairs * 4),
-                          (8, 8192), (9, 64 * 256 * 4)):
+                          (8, 8192), (9, 64 * 256 * 4), (10, 2 * tiles * 4)):
         assert 256 <= off(which) and off(which) + nbytes <= inter, which
     ws = ctypes.c_size_t()
     assert lib.msk_moe_workspace_bytes(ctypes.byref(cfg), ctypes.byref(ws)) == 0

@@ -672,13 +672,14 @@ def test_bounded_wait_runs_out_cleanly_and_the_state_recovers(cuda_dev):
     clean = m.kernel_fn(data, st).clone()
     torch.cuda.synchronize()
     views = {}
-    for which in (7, 8):                     # unit tickets, control words of the few-token paths
+    for which in (7, 8, 10):                 # unit tickets, control words of the few-token paths, tile hand-over counters
         ptr = ctypes.c_void_p()
         _lib.check(st["lib"].lib.msk_moe_workspace_view(ctypes.byref(st["cfg"]), _lib.ptr(st["workspace"]), which,
                                                         ctypes.byref(ptr)), "view")
         views[which] = ptr.value - st["workspace"].data_ptr()
     st["workspace"][views[7]:views[7] + 64].fill_(1)      # tickets half-way
     st["workspace"][views[8]:views[8] + 8192].fill_(3)    # token tickets, grid and tile counters
+    st["workspace"][views[10]:views[10] + 64].fill_(5)    # gate/up units counted for tiles that no down unit took over
     st["workspace"][:4].copy_(torch.tensor([1, 0, 0, 0], dtype=torch.uint8))   # sticky status word
     assert m.read_status(st) == 1
     m.reinit_workspace(st)
