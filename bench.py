@@ -344,7 +344,8 @@ def measure(moe, inputs, state, spec, steps, warmup, peaks, dev, flush_fn, with_
     mean_touched = sum(touched[i % POOL] for i in range(n_prof)) / n_prof
     R = T * k
     plan = moe.plan(state, T)
-    one_launch = plan[0] == 8 or (plan[1] == 0 and T <= 32 and R <= 256)
+    one_launch = plan[1] == 0 and T <= 32 and R <= 256
+    both_gemms = plan[1] == 4     # sort launch(es), both GEMMs in one launch, combine
     step_bytes = sum(inputs.algorithmic_bytes(H, I, E, k, T, touched[i % POOL]) for i in range(steps)) / steps
     step_flops = inputs.algorithmic_flops(H, I, R)
     if one_launch:
@@ -353,7 +354,17 @@ def measure(moe, inputs, state, spec, steps, warmup, peaks, dev, flush_fn, with_
         roof = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                 "frac": achieved / peaks["hbm_gbs"], "traffic": alg * NCU_TRAFFIC_RATIO,
                 "traffic_source": "ncu dram bytes of a weight-streaming GEMM capture / its algorithmic bytes (1.015), scaled",
-                "kernel": ("moe_small_kernel" if plan[0] == 8 else "moe_gemm_kernel<N,2>") + " (whole step in one launch)",
+                "kernel": "moe_gemm_kernel<N,2> (whole step in one launch)",
+                "peak_source": peaks["source"] + " (burst copy)"}
+    elif both_gemms:
+        # both GEMMs in one launch: the touched experts' tiles of both, x read and converted, inter written and
+        # read back, y written
+        alg = mean_touched * (3 * I * H * 0.5625 + 8) + 4.0 * T * H + 4.0 * R * I + 4.0 * R * H
+        achieved = alg / (k_ms[2] * 1e-3) / 1e9
+        roof = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                "frac": achieved / peaks["hbm_gbs"], "traffic": alg * NCU_TRAFFIC_RATIO,
+                "traffic_source": "ncu dram bytes of a weight-streaming GEMM capture / its algorithmic bytes (1.015), scaled",
+                "kernel": "moe_gemm_kernel<N,2> (gate/up and down GEMM in one launch)",
                 "peak_source": peaks["source"] + " (burst copy)"}
     elif T <= 1024:
         # gate/up GEMM: touched experts' W13 tiles + the x rows it gathers + the inter rows it writes
@@ -375,6 +386,8 @@ def measure(moe, inputs, state, spec, steps, warmup, peaks, dev, flush_fn, with_
         launches = 1
     elif plan[1] == 2 and T <= 32 and R <= 256:
         launches = 3      # row copy, gate/up kernel (routes, sorts), down kernel (combines)
+    elif both_gemms:      # [top-k +] sort (one launch up to 32 tokens), both GEMMs, combine
+        launches = 3 if T <= 32 else 4
     else:                 # [top-k +] sort (one launch up to 32 tokens, three from 16384 entries), row copy, two GEMMs, combine
         launches = 4 if T <= 32 else 6 + (2 if T * k >= 16384 else 0)
     return {

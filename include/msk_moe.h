@@ -62,7 +62,9 @@ typedef struct MskMoeCfg {
                             0 = chosen by token count (one launch up to 8 tokens, the chain beyond),
                             1 = the chain of launches used for many tokens,
                             2 = row copy, gate/up kernel that routes and sorts, down kernel that combines,
-                            3 = one launch (routing, sort, both GEMMs and the combine in one kernel) */
+                            3 = one launch (routing, sort, both GEMMs and the combine in one kernel);
+                            any token count with a token tile <= 32 (0 picks it from 9 tokens on):
+                            4 = sort launch(es), both GEMMs in one cooperative launch, combine */
   int32_t no_pdl;        /* non-zero: launches are not chained with programmatic dependent launch (the reference's
                             okc_set_pdl(0), muse_moe_w4a16/cuda/moe.cu:2348,2565) */
   int32_t token_tile;    /* MMA N (tokens per tile): 16/32/64/128, or 8 = the single-launch kernel for
@@ -214,7 +216,7 @@ int msk_moe_forward_static(const MskMoeCfg* cfg, const void* packed13, const voi
 int msk_moe_static_status(int* host_status, void* stream);
 
 /* The launch plan msk_moe_forward uses for n_tokens: host_out[4] = token tile N, path (as
- * MskMoeCfg.decode_path; always 1 beyond a few tokens), 1 when the weight stream is cut into equal
+ * MskMoeCfg.decode_path; 1 or 4 beyond a few tokens), 1 when the weight stream is cut into equal
  * shares (else whole units), persistent grid size. The reference picks its build by
  * token count the same way (muse_moe_w4a16/py/03_kernel_fn.py:33-40). */
 int msk_moe_plan(const MskMoeCfg* cfg, int n_tokens, int* host_out);

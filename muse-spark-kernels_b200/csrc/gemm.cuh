@@ -91,6 +91,10 @@ struct GemmCfg {
   // (four warps, straight from the unsorted F16 rows, no sorted copy) was built and measured: the
   // 16-byte requests load L2 so much less efficiently than TMA's full lines that the gate/up GEMM of
   // the 8192-token step took 3.08 ms instead of 1.48 ms, far more than the 0.22 ms the copy costs.
+  // Fetching them by index with TMA itself (tile::gather4 from the unsorted rows, a one-row box, every
+  // lane of the producer warp issuing the four copies of its four rows per stage: 128 copies of 512
+  // bytes where four tiled copies of 16 KB do) gave the same bits and was slower still: 4.07 ms for that
+  // GEMM, 0.54 against 0.19 ms at 256 tokens. The copy engine's rate per request, not the bytes, bounds it.
   static constexpr bool TMA_B = N >= 64;
   static constexpr int LUT_BYTES = 0;
   static constexpr int CTRL_BYTES = 1024;  // barriers, TMEM base, abort word, tile table header

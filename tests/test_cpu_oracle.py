@@ -277,14 +277,15 @@ def test_skewed_dealing_of_the_second_phase_balances_both_phases(n0, nst0, n1, n
 
 def test_plan_is_a_function_of_the_configuration_only():
     """Token tile, path and grid follow from the shapes and the token count (never from the device:
-    the default grid is a constant), few tokens take the one-launch path with flat shares."""
+    the default grid is a constant): up to 8 tokens the whole step is one launch, beyond that the narrow
+    token tiles run both GEMMs in one launch behind the sort (path 4), the wide tiles the chain."""
     from muse_moe_w4a16 import _lib
 
     lib = _lib.load()
     plan = (ctypes.c_int * 4)()
     cfg = _lib.MskMoeCfg(hidden=4096, inter=1536, n_experts=128, local_start=0, local_count=128, top_k=8, max_tokens=8192)
-    want = {1: (16, 0, 0, 148), 8: (16, 0, 0, 148), 32: (16, 1, 0, 148), 64: (16, 1, 0, 148), 256: (64, 1, 0, 148),
-            8192: (128, 1, 0, 148)}
+    want = {1: (16, 0, 0, 148), 8: (16, 0, 0, 148), 9: (16, 4, 0, 148), 32: (16, 4, 0, 148), 64: (16, 4, 0, 148),
+            256: (64, 1, 0, 148), 8192: (128, 1, 0, 148)}
     for T, w in want.items():
         assert lib.msk_moe_plan(ctypes.byref(cfg), T, plan) == 0
         assert tuple(plan) == w, (T, tuple(plan))
@@ -293,6 +294,9 @@ def test_plan_is_a_function_of_the_configuration_only():
     assert lib.msk_moe_plan(ctypes.byref(cfg), 8, plan) == 0 and tuple(plan) == (16, 2, 1, 148)
     cfg.decode_path = 3
     assert lib.msk_moe_plan(ctypes.byref(cfg), 32, plan) == 0 and tuple(plan) == (16, 0, 0, 148)
+    cfg.decode_path = 4
+    assert lib.msk_moe_plan(ctypes.byref(cfg), 190, plan) == 0 and tuple(plan) == (32, 4, 0, 148)
+    assert lib.msk_moe_plan(ctypes.byref(cfg), 256, plan) == 0 and tuple(plan) == (64, 1, 0, 148)   # wide tile: the chain
     cfg.decode_path = 1
     cfg.num_ctas = 37
     assert lib.msk_moe_plan(ctypes.byref(cfg), 8, plan) == 0 and tuple(plan) == (16, 1, 1, 37)

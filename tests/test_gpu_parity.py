@@ -404,6 +404,32 @@ def test_host_mapped_step_reads_and_writes_pinned_host_memory(cuda_dev, T, route
     assert m.read_status(st) == 0
 
 
+@pytest.mark.parametrize("T,tile", [(9, 0), (40, 0), (100, 16), (100, 32), (260, 32)])
+def test_both_gemms_in_one_launch_behind_the_sort_gives_the_chain_bits(cuda_dev, T, tile):
+    """decode_path = 4 (sort launches, then the gate/up and the down GEMM in one cooperative launch that
+    hands `inter` over tile by tile, then the combine) computes every unit exactly as the chain of
+    launches does: same output bits, same sort tables, status word clean, call after call."""
+    m, inputs, _lib, orc = _mods()
+    H, I, E, k = 1024, 512, 16, 4
+    w = inputs.make_weights(H, I, E, 53, cuda_dev, post_norm=True)
+    chain = m.prepare(w, n_experts=E, top_k=k, max_tokens=T, decode_path=1, token_tile=tile)
+    both = m.prepare(w, n_experts=E, top_k=k, max_tokens=T, decode_path=4, token_tile=tile)
+    assert m.plan(both, T)[1] == 4 and m.plan(chain, T)[1] == 1
+    g = torch.Generator(device=cuda_dev).manual_seed(20 + T)
+    for _ in range(3):
+        d = {"hidden_states": torch.randn((T, H), generator=g, device=cuda_dev).to(torch.bfloat16),
+             "router_logits": torch.randn((T, E), generator=g, device=cuda_dev)}
+        want, ids_w, tw_w = m.kernel_fn(d, chain, return_routing=True)
+        got, ids_g, tw_g = m.kernel_fn(d, both, return_routing=True)
+        torch.cuda.synchronize()
+        assert torch.equal(ids_g, ids_w) and torch.equal(tw_g, tw_w)
+        assert torch.equal(got, want)
+        vw, vg = m.workspace_views(chain, T), m.workspace_views(both, T)
+        for key in ("cnt", "off", "perm", "inv"):
+            assert torch.equal(vg[key], vw[key]), key
+    assert m.read_status(both) == 0 and m.read_status(chain) == 0
+
+
 def test_okc_ext_runs_the_decode_layer_call_site(cuda_dev):
     """The decode layer's call (muse_decode_layer/py/06_kernel_fn.py:140-149): local ids with -1 for
     another GPU's expert, lo = 0, an output slice filled in place, in chunks."""
