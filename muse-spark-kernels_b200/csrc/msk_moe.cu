@@ -539,10 +539,12 @@ static Plan make_plan(const MskMoeCfg* c, int T) {
     p.N = c->token_tile;
   } else {
     const double rpe = static_cast<double>(T) * c->top_k / c->n_experts;  // mean tokens per expert
-    // measured at H4096 I1536 E128: T = 128 (rpe 8): 270 / 290 / 296 us with 16 / 32 / 64-token tiles;
-    // T = 256 (rpe 16): 375 / 326 / 314 us; T = 512 (rpe 32): 618 / 506 / 345 us. A tile costs about the
-    // same up to 64 tokens (the weight decode bounds it), so past a few rows per expert wider is better
-    p.N = rpe <= 8 ? 16 : rpe <= 12 ? 32 : rpe <= 32 ? 64 : 128;
+    // measured at H4096 I1536 E128 (us a step with 16 / 32 / 64-token tiles; the narrow ones with both GEMMs
+    // in one launch): T = 160 (rpe 10): 281 / 313 / 307; T = 192 (rpe 12): 301 / 321 / 311; T = 256 (rpe 16):
+    // 381 / 334 / 317; T = 384: 526 / 372 / 338; T = 512 (rpe 32): 648 / 510 / 352. The 16-token tile is the
+    // fastest per K stage and wins while most experts fit one tile; past that the 64-token tile does; the
+    // 32-token tile never wins at these shapes (it stays selectable with cfg.token_tile)
+    p.N = rpe <= 12 ? 16 : rpe <= 32 ? 64 : 128;
   }
   const long long rows = static_cast<long long>(T) * c->top_k;
   // Flat shares are an option, off by default: measured on B200 a cut unit's pieces cost about 6 us of

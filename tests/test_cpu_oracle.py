@@ -295,7 +295,10 @@ def test_plan_is_a_function_of_the_configuration_only():
     cfg.decode_path = 3
     assert lib.msk_moe_plan(ctypes.byref(cfg), 32, plan) == 0 and tuple(plan) == (16, 0, 0, 148)
     cfg.decode_path = 4
+    assert lib.msk_moe_plan(ctypes.byref(cfg), 190, plan) == 0 and tuple(plan) == (16, 4, 0, 148)
+    cfg.token_tile = 32
     assert lib.msk_moe_plan(ctypes.byref(cfg), 190, plan) == 0 and tuple(plan) == (32, 4, 0, 148)
+    cfg.token_tile = 0
     assert lib.msk_moe_plan(ctypes.byref(cfg), 256, plan) == 0 and tuple(plan) == (64, 1, 0, 148)   # wide tile: the chain
     cfg.decode_path = 1
     cfg.num_ctas = 37
