@@ -2,8 +2,10 @@
 // Warp = (K half kh, tile g, lane quarter). Thread `row` of a quarter owns one weight row of
 // tile g. Per K stage the warps of half kh fill one A slot (128 K): four 16-byte code chunks
 // and eight scale bytes -> 4 x 16 BF16x2 registers -> four tcgen05.st, each issued right after
-// its chunk is decoded. A slot is handed to the MMA warp (`retire`) after the
-// first chunk of the following slot has been decoded, so the store latency hides behind it.
+// its chunk is decoded. With three slots per tile a slot is handed to the MMA warp (`retire`) after
+// the first chunk of the following slot has been decoded, so the store latency hides behind it; with
+// two slots right behind its stores (see below). Slots of half the size (64 K, twice as many
+// hand-overs) were measured too: 10 - 20 % slower at every size, the hand-over itself is what costs.
     const int didx = warp - 8;
     const int g = (didx >> 2) & 1;
     const int kh = didx >> 3;
@@ -100,6 +102,12 @@
             if (!ok) break;
             pending = true;
             pending_slot = as;
+            // Two-slot rings (the wide token tiles): this K half's slot is refilled every stage, and the refill
+            // has to wait until the MMAs of the stage before have drained it. Handing the slot over right
+            // here, instead of behind the first decode of the next stage, lets those MMAs start a decode
+            // earlier (8192 tokens: gate/up GEMM 1.47 -> 1.34 ms; 256 tokens 309 -> 300 us a step). With three
+            // slots (the narrow tiles) it changes nothing, and the deferred hand-over hides the store latency.
+            if (NSLOT == 2) retire();
             if (it == 0 && tid == 256) MSK_TR(TR_FIRST_AFULL);
             // the other K half takes the next ring slot; this warp's next one is two further
             as += 2;
