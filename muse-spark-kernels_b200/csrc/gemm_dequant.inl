@@ -107,6 +107,8 @@
             // here, instead of behind the first decode of the next stage, lets those MMAs start a decode
             // earlier (8192 tokens: gate/up GEMM 1.47 -> 1.34 ms; 256 tokens 309 -> 300 us a step). With three
             // slots (the narrow tiles) it changes nothing, and the deferred hand-over hides the store latency.
+            // (Letting both warp groups of a tile decode the same slot, so that a slot fills in half the time,
+            // was measured on top of this: no change.)
             if (NSLOT == 2) retire();
             if (it == 0 && tid == 256) MSK_TR(TR_FIRST_AFULL);
             // the other K half takes the next ring slot; this warp's next one is two further
