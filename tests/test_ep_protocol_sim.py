@@ -12,17 +12,35 @@ import pytest
 
 
 def build_rank_program(r, n, chunks, steps):
-    """The two operation lists of rank r for `steps` steps, in the order step() enqueues them."""
-    m = n // chunks
+    """The two operation lists of rank r for `steps` steps, in the order step() enqueues them.
+    chunks: None (the default layout), a number of equal chunks, or the chunk sizes (chunk_sizes)."""
+    from muse_moe_w4a16.ep import chunk_sizes
+
+    sizes = chunk_sizes(n, chunks)
+    bounds = [0]
+    for m in sizes:
+        bounds.append(bounds[-1] + m)
     s0, s1 = [], []
     for e in range(1, steps + 1):
         b = e & 1
         ev = lambda name: (r, e, name)
+
+        def run_chunk(c):
+            reads = [("gx", r, b, j) for j in range(bounds[c], bounds[c + 1])]
+            writes = [("part", r, b, j) for j in range(bounds[c], bounds[c + 1])]
+            s0.append(("kernel", reads, writes, e))
+            for j in range(max(bounds[c], 1), bounds[c + 1]):
+                s0.append(("flag_write", (r + j) % n, 2 * n + 2 * r + b, e))
+
         # main stream: inputs into slot 0, tell the peers
         s0.append(("produce", ("gx", r, b, 0), e))
         s0.append(("record", ev("in")))
         for j in range(1, n):
             s0.append(("flag_write", (r + j) % n, 2 * r + b, e))
+        # a first chunk of the own rows alone is issued before the copy stream's calls
+        own_first = sizes[0] == 1
+        if own_first:
+            run_chunk(0)
         # copy stream: pull the other ranks' rows
         s1.append(("wait_event", ev("in")))
         ready = {}
@@ -30,18 +48,15 @@ def build_rank_program(r, n, chunks, steps):
             p = (r + j) % n
             s1.append(("flag_wait", 2 * p + b, e))
             s1.append(("copy", ("gx", p, b, 0), ("gx", r, b, j), e))
-            if (j + 1) % m == 0:
-                ready[j // m] = ev(("ready", j // m))
-                s1.append(("record", ready[j // m]))
-        # main stream: the expert chunks
-        for c in range(chunks):
+            if j + 1 in bounds:
+                c = bounds.index(j + 1) - 1
+                ready[c] = ev(("ready", c))
+                s1.append(("record", ready[c]))
+        # main stream: the other expert chunks
+        for c in range(1 if own_first else 0, len(sizes)):
             if c in ready:
                 s0.append(("wait_event", ready[c]))
-            reads = [("gx", r, b, j) for j in range(c * m, (c + 1) * m)]
-            writes = [("part", r, b, j) for j in range(c * m, (c + 1) * m)]
-            s0.append(("kernel", reads, writes, e))
-            for j in range(max(c * m, 1), (c + 1) * m):
-                s0.append(("flag_write", (r + j) % n, 2 * n + 2 * r + b, e))
+            run_chunk(c)
         # copy stream: pull this rank's partial rows back
         for j in range(1, n):
             q = (r - j) % n
@@ -127,7 +142,8 @@ def simulate(n, chunks, steps, seed):
         assert progressed, "deadlock: " + str({k: q[0] for k, q in queues.items() if q})
 
 
-@pytest.mark.parametrize("n,chunks", [(2, 1), (2, 2), (4, 1), (4, 2), (4, 4), (8, 2), (8, 4), (8, 8), (6, 3)])
+@pytest.mark.parametrize("n,chunks", [(2, 1), (2, 2), (4, 1), (4, 2), (4, 4), (8, 2), (8, 4), (8, 8), (6, 3),
+                                      (3, None), (4, None), (5, None), (8, None), (8, (1, 3, 3, 1)), (8, (3, 4, 1))])
 def test_exchange_protocol_neither_deadlocks_nor_mixes_steps(n, chunks):
     for seed in range(6):
         simulate(n, chunks, steps=4, seed=seed)
