@@ -563,6 +563,7 @@ static Plan make_plan(const MskMoeCfg* c, int T) {
     // against 57 / 72 / 94 / 135 for the chain; at 16 and 32 tokens 195 / 268 against 197 / 249
     switch (c->decode_path) {
       case 1: p.path = 1; break;
+      case 4: p.path = 1; break;   // becomes 4 below
       case 2: p.path = 2; break;
       case 3: p.path = 0; break;
       default: p.path = T <= ONE_LAUNCH_MAX_TOKENS ? 0 : 1; break;
