@@ -67,8 +67,8 @@ typedef struct MskMoeCfg {
                             4 = sort launch(es), both GEMMs in one cooperative launch, combine */
   int32_t no_pdl;        /* non-zero: launches are not chained with programmatic dependent launch (the reference's
                             okc_set_pdl(0), muse_moe_w4a16/cuda/moe.cu:2348,2565) */
-  int32_t token_tile;    /* MMA N (tokens per tile): 16/32/64/128, or 8 = the single-launch kernel for
-                            up to 8 tokens; 0 = chosen from n_tokens */
+  int32_t token_tile;    /* MMA N (tokens per tile): 16/32/64/128; 0 = chosen from the mean rows per expert
+                            (up to 12: 16, up to 32: 64, beyond: 128) */
   int32_t max_tokens;    /* token capacity the workspace is sized for (msk_moe_forward rejects more) */
   int32_t trace;         /* non-zero: the GEMM kernels stamp %globaltimer per CTA into the workspace (view 6) */
   int32_t stop_after;    /* measuring aid: 0 = whole step; 1/2/3 = return after sort / gate-up GEMM / down GEMM */

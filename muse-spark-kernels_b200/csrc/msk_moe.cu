@@ -491,6 +491,9 @@ static int check_cfg(const MskMoeCfg* c) {
   if (c->local_count < 1 || c->local_count > MAX_LOCAL_EXPERTS) return MSK_ERR_SHAPE;
   if (c->n_experts < 1 || c->n_experts > MAX_EXPERTS) return MSK_ERR_SHAPE;
   if (c->local_start < 0 || c->local_start + c->local_count > c->n_experts) return MSK_ERR_RANGE;
+  if (c->token_tile != 0 && c->token_tile != 16 && c->token_tile != 32 && c->token_tile != 64 && c->token_tile != 128)
+    return MSK_ERR_SHAPE;
+  if (c->decode_path < 0 || c->decode_path > 4) return MSK_ERR_SHAPE;
   return MSK_OK;
 }
 

@@ -163,7 +163,8 @@ def test_host_side_validation_rejects_bad_arguments():
     assert a.value == 8 * (2 * 256 // 128) * (512 // 256) * 18432 and b.value == 8 * (512 // 128) * 1 * 18432
     assert lib.msk_moe_packed_bytes(None, ctypes.byref(a), ctypes.byref(b)) == -1
     for bad in (dict(hidden=500), dict(inter=128), dict(top_k=0), dict(top_k=17), dict(local_count=0),
-                dict(local_count=300), dict(n_experts=600)):
+                dict(local_count=300), dict(n_experts=600), dict(token_tile=8), dict(token_tile=48),
+                dict(decode_path=5), dict(decode_path=-1)):
         c = _lib.MskMoeCfg(**{**good, **bad})
         assert lib.msk_moe_packed_bytes(ctypes.byref(c), ctypes.byref(a), ctypes.byref(b)) == -2, bad
     c = _lib.MskMoeCfg(**{**good, "local_start": 4})
@@ -182,7 +183,7 @@ def test_host_side_validation_rejects_bad_arguments():
     assert lib.msk_moe_forward(ctypes.byref(cfg), odd, fake, fake, fake, None, fake, fake, fake, fake, fake,
                                ws.value, 4, None) == -3
     plan = (ctypes.c_int * 4)()
-    assert lib.msk_moe_plan(ctypes.byref(cfg), 4, plan) == 0 and plan[0] in (8, 16, 32, 64, 128)
+    assert lib.msk_moe_plan(ctypes.byref(cfg), 4, plan) == 0 and plan[0] in (16, 32, 64, 128)
 
 
 def _pieces(lib, n_base, nst, shares, mode, cta, heavy=0, skip=0):
