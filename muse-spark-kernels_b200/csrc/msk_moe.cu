@@ -268,7 +268,9 @@ template <> struct YQuad<true> {
   }
 };
 
-template <int G, bool YB, int MINB>
+// NF4 = float4 slots per thread per row that the kernel is built for: 4 (H <= 8192) or 2 (H <= 4096, half
+// the registers per row in flight, which is what lets all eight rows of a token be loaded at once).
+template <int G, bool YB, int MINB, int NF4 = COMBINE_MAX_F4>
 __global__ void __launch_bounds__(COMBINE_THREADS, MINB)
     combine_kernel(const float* __restrict__ y, const int32_t* __restrict__ inv, const float* __restrict__ tw,
                    __nv_bfloat16* __restrict__ out, int H, int k, int post_norm, float eps) {
@@ -292,9 +294,9 @@ __global__ void __launch_bounds__(COMBINE_THREADS, MINB)
   __syncthreads();
   const int nv = s_n;
   const int n4 = H / 4;  // float4 per row; thread tid owns indices i*512 + tid
-  float4 acc[COMBINE_MAX_F4];
+  float4 acc[NF4];
 #pragma unroll
-  for (int i = 0; i < COMBINE_MAX_F4; ++i) acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int i = 0; i < NF4; ++i) acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
   for (int s0 = 0; s0 < nv; s0 += G) {
     int q[G];
     float wgt[G];
@@ -304,14 +306,14 @@ __global__ void __launch_bounds__(COMBINE_THREADS, MINB)
       q[g] = in ? s_q[s0 + g] : -1;
       wgt[g] = in ? s_w[s0 + g] : 0.f;
     }
-    YQuad<YB> v[G][COMBINE_MAX_F4];
+    YQuad<YB> v[G][NF4];
     float ss[G];
 #pragma unroll
     for (int g = 0; g < G; ++g) {
       ss[g] = 0.f;
       const size_t r = static_cast<size_t>(q[g] < 0 ? 0 : q[g]) * H;
 #pragma unroll
-      for (int i = 0; i < COMBINE_MAX_F4; ++i) {
+      for (int i = 0; i < NF4; ++i) {
         v[g][i].zero();
         if (q[g] >= 0 && i * COMBINE_THREADS + tid < n4) v[g][i].load(y, r, i * COMBINE_THREADS + tid);
       }
@@ -320,7 +322,7 @@ __global__ void __launch_bounds__(COMBINE_THREADS, MINB)
 #pragma unroll
       for (int g = 0; g < G; ++g) {
 #pragma unroll
-        for (int i = 0; i < COMBINE_MAX_F4; ++i) {
+        for (int i = 0; i < NF4; ++i) {
           const float4 f = v[g][i].get();
           ss[g] += f.x * f.x + f.y * f.y + f.z * f.z + f.w * f.w;
         }
@@ -345,7 +347,7 @@ __global__ void __launch_bounds__(COMBINE_THREADS, MINB)
     for (int g = 0; g < G; ++g) {  // slot order within the group
       if (q[g] < 0) continue;
 #pragma unroll
-      for (int i = 0; i < COMBINE_MAX_F4; ++i) {
+      for (int i = 0; i < NF4; ++i) {
         const float4 f = v[g][i].get();
         acc[i].x += f.x * wgt[g]; acc[i].y += f.y * wgt[g];
         acc[i].z += f.z * wgt[g]; acc[i].w += f.w * wgt[g];
@@ -353,7 +355,7 @@ __global__ void __launch_bounds__(COMBINE_THREADS, MINB)
     }
   }
 #pragma unroll
-  for (int i = 0; i < COMBINE_MAX_F4; ++i) {
+  for (int i = 0; i < NF4; ++i) {
     if (i * COMBINE_THREADS + tid < n4) {
       __nv_bfloat162 lo = __floats2bfloat162_rn(acc[i].x, acc[i].y);
       __nv_bfloat162 hi = __floats2bfloat162_rn(acc[i].z, acc[i].w);
@@ -1237,7 +1239,9 @@ static int forward_impl(const MskMoeCfg* cfg, const void* packed13, const void* 
     lc.attrs = at;
     lc.numAttrs = 1;
     const bool wide = n_tokens >= COMBINE_WIDE_TOKENS;
-    auto* kern = p.y_bf16 ? combine_kernel<4, true, 2> : (wide ? combine_kernel<2, false, 2> : combine_kernel<4, false, 1>);
+    const bool narrow_rows = cfg->hidden <= COMBINE_THREADS * 2 * 4;   // two float4 slots per thread hold a row
+    auto* kern = p.y_bf16 ? (narrow_rows ? combine_kernel<8, true, 2, 2> : combine_kernel<4, true, 2>)
+                          : (wide ? combine_kernel<2, false, 2> : combine_kernel<4, false, 1>);
     e = static_cast<int>(cudaLaunchKernelEx(&lc, kern, static_cast<const float*>(y),
                                             static_cast<const int32_t*>(inv), topk_weights,
                                             static_cast<__nv_bfloat16*>(out), static_cast<int>(cfg->hidden),
