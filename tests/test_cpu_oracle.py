@@ -93,7 +93,7 @@ def test_quantiser_round_trip_and_tie_rule():
     dq = orc.dequant(c.numpy(), s.numpy(), float(gs))
     blk = w.float().view(64, 16, 16).abs().amax(-1).numpy().repeat(16, -1).reshape(64, 256)
     assert np.all(np.abs(dq - w.float().numpy()) <= 0.26 * blk + 1e-12)  # half an E2M1 step at the block top
-    assert 0x08 <= int(s.min()) and int(s.max()) <= 0x7E                  # normal scale bytes, as the survey found
+    assert 0x08 <= int(s.min()) and int(s.max()) <= 0x7E                  # normal scale bytes only (neither zero, subnormal nor NaN)
 
 
 def test_route_topk_tie_rule_and_weights():
