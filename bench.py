@@ -289,7 +289,8 @@ def measure(moe, inputs, state, spec, steps, warmup, peaks, dev, flush_fn, with_
         if T <= HOST_MAPPED_MAX_TOKENS:
             # the other transport: the kernels read the pinned host inputs and write the pinned host output
             # themselves (no copy launches); the same bytes cross PCIe inside the timed region
-            hstep = moe.HostMappedStep(state, host_pool[0])
+            hstep = moe.HostMappedStep(state, host_pool[0])   # raises (and the run with it) if it cannot be built:
+            # a benchmark that silently dropped one of its two transports would not be the same benchmark
 
             def e2e_steps_mapped(n):
                 evs = []
