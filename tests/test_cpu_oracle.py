@@ -424,3 +424,20 @@ def test_combine_matches_reference_pexp_norm_sum():
     same = _trunc_bf16(out) == want
     assert float(same.float().mean()) > 0.995          # the rest straddle a BF16 boundary in their last FP32 bits
     assert float((out - want).abs().max()) <= 2.0 ** -7 * float(want.abs().max())
+
+
+def test_timeline_stamp_slots_follow_the_kernel_enum():
+    """muse_moe_w4a16.timeline names the kernels' trace slots by number; the numbers must be the positions
+    of the TR_* enumerators in csrc/gemm.cuh."""
+    import re
+
+    from muse_moe_w4a16 import timeline
+
+    src = open(os.path.join(ROOT, "muse-spark-kernels_b200", "csrc", "gemm.cuh")).read()
+    body = re.search(r"enum\s*:\s*int\s*\{\s*(TR_START\s*=\s*0.*?)\};", src, re.S).group(1)
+    names = [n.strip().split("=")[0].strip() for n in body.replace("\n", " ").split(",") if n.strip()]
+    slots = {n[3:]: i for i, n in enumerate(names)}
+    assert len(slots) <= 16                      # 16 stamps per CTA in the workspace
+    for name, slot in timeline.STAMPS:
+        assert slots[name] == slot, name
+    assert {n for n, _ in timeline.STAMPS} == set(slots)
